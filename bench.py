@@ -1,0 +1,401 @@
+"""Benchmark of the TQ4 split-K paged decode (Llama-3-8B shape) on 1..8 B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one attention-layer decode call over the whole batch: 32 sequences x 4096 cached
+tokens, 32 query heads / 8 KV heads, head_dim 128, pages of 16 tokens, 8 splits; the call
+includes the query rotation, the streaming kernel, the split-K merge and the output
+rotation.  With N > 1 (launched by torchrun, one rank per GPU) every rank decodes its own
+batch of the same shape - sequences are independent, so there is no collective on the data
+path (weak scaling) - and the time is the maximum over ranks.
+
+One JSON line is printed by rank 0; see DESIGN.md for the meaning of every key.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "tq4_paged_decode_tokens_per_s"
+UNIT = "tokens/s"
+NUM_SEQS, CONTEXT, HQ, HKV, D, BS, SPLITS = 32, 4096, 32, 8, 128, 16, 8
+CACHE_COPIES = 3  # 3 x 142.6 MB of packed cache are cycled so that no step finds its pages in L2
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "configs[1]: Llama-3-8B-shaped paged decode, batch 32 x context 4096, "
+                    "32 q / 8 kv heads, head_dim 128, block 16, K=TurboQuantProd(3-bit codes), "
+                    "V=TurboQuantMSE 4-bit, 8 splits, seed-2 block table",
+        "num_seqs_per_gpu": NUM_SEQS, "context": CONTEXT, "num_splits": SPLITS,
+        "sharding": f"sequences, {n_gpus} independent rank(s), no collective",
+        "l2": f"{CACHE_COPIES} cache copies of 142.6 MB cycled (> 126 MB L2), no flush needed",
+        "seeds": {"rotation": 0, "qjl": 1, "K": 1001, "V": 2001, "Q": 3001, "block_table": 2},
+    }
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """Polls SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: report nulls
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# --------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------
+def run_ours(args):
+    import flashquant_b200 as fq
+    from flashquant_b200 import _native, kernels as K, workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path to time)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _native.load()
+
+    # ---- constants and inputs ------------------------------------------------------------
+    q3, q4 = fq.TurboQuantProd(D, 4, seed=0), fq.TurboQuantMSE(D, 4, seed=0)
+    rot = q4.rotation.to(dev)
+    S = q3.qjl_matrix.to(dev)
+    bk, ck = q3.mse_quantizer.boundaries.to(dev), q3.mse_quantizer.centroids.to(dev)
+    bv, cv = q4.boundaries.to(dev), q4.centroids.to(dev)
+    w = W.decode_workload(NUM_SEQS, CONTEXT, HQ, HKV, D, BS, cfg=1)
+    k_cpu, v_cpu = W.make_kv(w.total_tokens, HKV, D, cfg=1)
+    caches, planes = [], []
+    slots = w.slot_mapping.to(dev)
+    kd, vd = k_cpu.to(dev), v_cpu.to(dev)
+    for _ in range(CACHE_COPIES):
+        c = torch.zeros(w.num_blocks, BS, HKV * (D + 8), dtype=torch.uint8, device=dev)
+        p = torch.zeros(w.num_blocks, BS, HKV * (D // 8 + 4), dtype=torch.uint8, device=dev)
+        K.tq4_compress_append_qjl(kd, vd, c, p, slots, rot, bk, ck, bv, S)
+        caches.append(c)
+        planes.append(p)
+    del kd, vd
+    q = w.q.to(dev)
+    bt, sl = w.block_table.to(dev), w.seq_lens.to(dev)
+    out = torch.empty_like(q)
+    ws = K.decode_workspace(dev, NUM_SEQS, HQ, D, SPLITS)
+    torch.cuda.synchronize()
+
+    def decode(i):
+        return K.split_k_paged_decode(q, caches[i % CACHE_COPIES], bt, sl, ck, cv, rot, HKV, D, BS,
+                                      out=out, num_splits=SPLITS, workspace=ws)
+
+    # ---- graphs: one captured decode call per cache copy ------------------------------
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(CACHE_COPIES):
+            decode(i)
+    side.synchronize()
+    launches_per_step = None
+    graphs = []
+    for i in range(CACHE_COPIES):
+        g = torch.cuda.CUDAGraph()
+        n0 = lib.fq_launch_count()
+        with torch.cuda.graph(g):
+            decode(i)
+        launches_per_step = lib.fq_launch_count() - n0
+        graphs.append(g)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    with sampler:
+        for i in range(args.warmup):
+            graphs[i % CACHE_COPIES].replay()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.steps):
+            graphs[i % CACHE_COPIES].replay()
+        t1.record()
+        barrier()
+        ms = t0.elapsed_time(t1)
+
+        # ---- dominant kernel alone (the streaming kernel), same inputs ------------------
+        q_rot16 = (q.float() @ rot.T).to(q.dtype).to(torch.float16).contiguous()
+        parts = torch.empty(NUM_SEQS, HQ, SPLITS, D + 4, dtype=torch.float32, device=dev)
+
+        def stream_only(i):
+            _native.check(lib.fq_paged_decode_partials_rotated(
+                _native.ptr(q_rot16), _native.ptr(caches[i % CACHE_COPIES]), _native.ptr(bt),
+                bt.stride(0), _native.ptr(sl), _native.ptr(ck), ck.numel(), _native.ptr(cv),
+                cv.numel(), NUM_SEQS, HQ, HKV, D, BS, w.num_blocks, 1.0 / D ** 0.5, SPLITS,
+                _native.ptr(parts), _native.ptr(ws), ws.numel(), _native.stream_ptr(dev)))
+
+        with torch.cuda.stream(side):
+            stream_only(0)
+        side.synchronize()
+        kg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kg):
+            for i in range(CACHE_COPIES):
+                stream_only(i)
+        reps = max(8, args.steps // CACHE_COPIES)
+        for _ in range(3):
+            kg.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(reps):
+            kg.replay()
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / (reps * CACHE_COPIES)
+
+    # ---- end to end: host buffers in, host buffer out, every step -----------------------
+    e2e_steps = min(args.steps, 200)
+    hq_ = w.q.pin_memory()
+    new_k = k_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
+    new_v = v_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
+    new_slots = w.slot_mapping.reshape(NUM_SEQS, CONTEXT)[:, -1].contiguous().pin_memory()
+    hbt, hsl = w.block_table.pin_memory(), w.seq_lens.pin_memory()
+    hout = torch.empty_like(hq_).pin_memory()
+    dq, dk, dv = torch.empty_like(q), new_k.to(dev), new_v.to(dev)
+    dslots, dbt, dsl = new_slots.to(dev), bt.clone(), sl.clone()
+    h2d = sum(t.numel() * t.element_size() for t in (hq_, new_k, new_v, new_slots, hbt, hsl))
+    d2h = hout.numel() * hout.element_size()
+
+    def e2e_step(i):
+        c, p = caches[i % CACHE_COPIES], planes[i % CACHE_COPIES]
+        dq.copy_(hq_, non_blocking=True)
+        dk.copy_(new_k, non_blocking=True)
+        dv.copy_(new_v, non_blocking=True)
+        dslots.copy_(new_slots, non_blocking=True)
+        dbt.copy_(hbt, non_blocking=True)
+        dsl.copy_(hsl, non_blocking=True)
+        K.tq4_compress_append_qjl(dk, dv, c, p, dslots, rot, bk, ck, bv, S)
+        K.split_k_paged_decode(dq, c, dbt, dsl, ck, cv, rot, HKV, D, BS, out=out,
+                               num_splits=SPLITS, workspace=ws)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    n0 = lib.fq_launch_count()
+    tw = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_s = time.perf_counter() - tw
+    e2e_launches = lib.fq_launch_count() - n0
+    barrier()
+
+    # ---- reductions over ranks ----------------------------------------------------------
+    vals = torch.tensor([ms, kernel_ms, e2e_s], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms, kernel_ms, e2e_s = (float(x) for x in vals.cpu())
+    status = K.workspace_status(ws)
+    if status:
+        raise SystemExit(f"device status word is {status}: results invalid")
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        alg = w.algorithmic_bytes()
+        achieved = alg / (kernel_ms * 1e-3) / 1e9
+        tokens = NUM_SEQS * world
+        line = {
+            "metric": METRIC, "value": tokens * args.steps / (ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16 mma operands, fp32 accumulate, bf16 in/out",
+            "data": "synthetic", "config": workload_config(world),
+            "hbm_tb_s_per_gpu_whole_call": alg / (ms / args.steps * 1e-3) / 1e12,
+            "clocks": sampler.summary(),
+            "gpu_launches": launches_per_step * args.steps,
+            "launches_per_step": launches_per_step,
+            "e2e": {"value": tokens * e2e_steps / e2e_s, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "gpu_launches": e2e_launches,
+                    "what": "pinned host q / new K,V token / slot / block table / lengths -> "
+                            "device, compress-on-append, decode, output -> pinned host, "
+                            "synchronise; the packed cache itself stays in HBM"},
+            "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel<128>",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak,
+                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                         "algorithmic_bytes": alg, "kernel_ms": kernel_ms,
+                         "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "traffic": args.traffic},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w, caches[0].cpu(), ck.cpu(), cv.cpu(), rot.cpu(),
+                                                budget_s=20.0)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# CPU legs: the oracle port of the reference's pure-PyTorch path
+# --------------------------------------------------------------------------------------
+def cpu_decode_sample(w, cache, ck, cv, rot, n_seq):
+    from oracle import tq_oracle as O
+    return O.split_k_paged_decode(w.q[:n_seq], cache, w.block_table[:n_seq], w.seq_lens[:n_seq],
+                                  ck, cv, rot, HKV, D, BS)
+
+
+def cpu_baseline(w, cache, ck, cv, rot, budget_s):
+    torch.set_num_threads(os.cpu_count() or 1)
+    t = time.perf_counter()
+    cpu_decode_sample(w, cache, ck, cv, rot, 1)
+    one = time.perf_counter() - t
+    n_seq = int(max(1, min(NUM_SEQS, budget_s / max(one, 1e-3))))
+    t = time.perf_counter()
+    cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
+    dt = time.perf_counter() - t
+    return {"value": n_seq / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n_seq} of the {NUM_SEQS} sequences (context {CONTEXT}), one pass of the "
+                      f"vectorised oracle restatement of the reference's CPU decode, {dt:.2f} s"}
+
+
+def run_reference(args):
+    """Times the oracle port of the reference's CPU path (the reference is pure PyTorch and
+    cannot travel to the GPU box) on a bounded sample of the same workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from flashquant_b200 import workloads as W
+    from flashquant_b200.quantizer import TurboQuantMSE, TurboQuantProd
+    from oracle import tq_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    q3, q4 = TurboQuantProd(D, 4, seed=0), TurboQuantMSE(D, 4, seed=0)
+    rot = q4.rotation
+    bk, ck = q3.mse_quantizer.boundaries, q3.mse_quantizer.centroids
+    bv, cv = q4.boundaries, q4.centroids
+    n_seq = 2
+    w = W.decode_workload(n_seq, CONTEXT, HQ, HKV, D, BS, cfg=1)
+    k, v = W.make_kv(w.total_tokens, HKV, D, cfg=1)
+    cache = torch.zeros(w.num_blocks, BS, HKV * (D + 8), dtype=torch.uint8)
+    O.compress_and_store(k, v, cache, w.slot_mapping, rot, bk, bv)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
+    steps = args.steps
+    t = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
+        done += 1
+        if time.perf_counter() - t > 120.0:  # keep the whole run within a few minutes
+            break
+    dt = time.perf_counter() - t
+    value = n_seq * done / dt
+    sample = (f"{n_seq} sequences x context {CONTEXT} per step (of the 32 in the workload), "
+              f"{done} steps timed")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": done, "warmup": args.warmup, "ms_per_step": dt / done * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the streaming kernel from an ncu capture")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

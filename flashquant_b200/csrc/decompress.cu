@@ -1,0 +1,88 @@
+// TQ4 decompress for sm_100a: nibble codes + fp32 norm -> c[code] * norm in rotated space.
+//
+// Pure streaming work (68 B in, 2*D or 4*D bytes out per vector).  A thread takes 4 packed
+// bytes (one 32-bit load) and produces 8 output values (one or two 16-byte stores), so a
+// warp reads 128 contiguous bytes and writes 512 or 1024 contiguous bytes per step.
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int kDecompressThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kDecompressThreads) decompress_kernel(
+    const uint8_t* __restrict__ packed, const float* __restrict__ norms,
+    const float* __restrict__ centroids, int n_centroids, T* __restrict__ out,
+    int64_t n_words, int words_per_vec) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = threadIdx.x < n_centroids ? centroids[threadIdx.x] : 0.f;
+  __syncthreads();
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t w = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; w < n_words; w += stride) {
+    const uint32_t word = reinterpret_cast<const uint32_t*>(packed)[w];
+    const float n = norms[w / words_per_vec];
+    float v[8];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t byte = (word >> (8 * b)) & 0xffu;
+      v[2 * b] = lut[byte >> 4] * n;
+      v[2 * b + 1] = lut[byte & 15u] * n;
+    }
+    T* o = out + w * 8;
+    if constexpr (sizeof(T) == 4) {
+      reinterpret_cast<float4*>(o)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4*>(o)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      T h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = from_f32<T>(v[i]);
+      *reinterpret_cast<uint4*>(o) = *reinterpret_cast<uint4*>(h);
+    }
+  }
+}
+
+}  // namespace fq
+
+using namespace fq;
+
+extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
+                                 const float* centroids, int n_centroids, void* out,
+                                 fq_dtype out_dtype, int64_t n_vectors, int head_dim,
+                                 fq_stream_t stream) {
+  FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
+  if (n_vectors == 0) return FQ_OK;
+  FQ_REQUIRE(packed && norms && centroids && out, FQ_ERR_INVALID_ARGUMENT,
+             "fq_tq4_decompress: null pointer");
+  FQ_REQUIRE(n_centroids >= 1 && n_centroids <= 16, FQ_ERR_INVALID_ARGUMENT,
+             "n_centroids %d outside [1, 16]", n_centroids);
+  FQ_REQUIRE(head_dim > 0 && head_dim % 8 == 0, FQ_ERR_UNSUPPORTED,
+             "head_dim %d is not a multiple of 8", head_dim);
+  FQ_REQUIRE(aligned(packed, 4) && aligned(out, 16) && aligned(norms, 4), FQ_ERR_ALIGNMENT,
+             "fq_tq4_decompress: packed must be 4-byte and out 16-byte aligned");
+  const int words_per_vec = head_dim / 8;
+  const int64_t n_words = n_vectors * words_per_vec;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t want = (n_words + kDecompressThreads - 1) / kDecompressThreads;
+  const int grid = int(want < int64_t(sms) * 8 ? want : int64_t(sms) * 8);
+  cudaStream_t s = stream;
+  switch (out_dtype) {
+    case FQ_F32:
+      decompress_kernel<float><<<grid, kDecompressThreads, 0, s>>>(
+          packed, norms, centroids, n_centroids, static_cast<float*>(out), n_words, words_per_vec);
+      break;
+    case FQ_F16:
+      decompress_kernel<__half><<<grid, kDecompressThreads, 0, s>>>(
+          packed, norms, centroids, n_centroids, static_cast<__half*>(out), n_words, words_per_vec);
+      break;
+    case FQ_BF16:
+      decompress_kernel<__nv_bfloat16><<<grid, kDecompressThreads, 0, s>>>(
+          packed, norms, centroids, n_centroids, static_cast<__nv_bfloat16*>(out), n_words,
+          words_per_vec);
+      break;
+    default:
+      return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", int(out_dtype));
+  }
+  return check_launch("decompress kernel launch");
+}

@@ -1,0 +1,337 @@
+"""Host-side mirror of the reference's kernel dispatch layer for the TurboQuant hot path.
+
+The four functions ``tq4_compress``, ``tq4_decompress``, ``fused_tq_attention`` and
+``split_k_paged_decode`` keep the names, argument order and return shapes of
+``flashquant.kernels`` (reference: src/flashquant/kernels/{compress,decompress,attention,
+paged_decode}.py); the remaining ones are the fused entry points this project adds.  Every
+call goes through the C ABI of ``libflashquant_b200.so`` with raw device pointers.  There is
+no CPU branch: tensors must be CUDA tensors.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+_PART_PAD = 4  # a partial row holds head_dim + 4 floats (acc, m, l, 2 pads)
+
+
+def _contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _f32(t: torch.Tensor, device) -> torch.Tensor:
+    return _contig(t.to(device=device, dtype=torch.float32))
+
+
+# --------------------------------------------------------------------------------------
+# compress / decompress (contiguous)
+# --------------------------------------------------------------------------------------
+
+def tq4_compress(
+    x: torch.Tensor,
+    rotation: torch.Tensor,
+    boundaries: torch.Tensor,
+    *,
+    rotation_T_even: Optional[torch.Tensor] = None,
+    rotation_T_odd: Optional[torch.Tensor] = None,
+    out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(N, H, D)`` float -> packed ``(N, H, D/2)`` uint8, norms ``(N, H, 1)`` fp32.
+
+    Same contract as the reference's ``tq4_compress`` (src/flashquant/kernels/compress.py:51-95).
+    """
+    N.require_cuda(x)
+    n, h, d = x.shape
+    dev = x.device
+    if rotation_T_even is None or rotation_T_odd is None:
+        rt = rotation.to(dev).T.contiguous()
+        rotation_T_even = rt[:, 0::2].contiguous()
+        rotation_T_odd = rt[:, 1::2].contiguous()
+    even, odd = _f32(rotation_T_even, dev), _f32(rotation_T_odd, dev)
+    bnd = _f32(boundaries, dev)
+    x = _contig(x)
+    if out is not None:
+        packed, norms = out
+        if packed.shape != (n, h, d // 2) or norms.numel() != n * h:
+            raise ValueError("out buffers have the wrong shape")
+    else:
+        packed = torch.empty(n, h, d // 2, dtype=torch.uint8, device=dev)
+        norms = torch.empty(n, h, 1, dtype=torch.float32, device=dev)
+    lib = N.load()
+    N.check(lib.fq_tq4_compress(N.ptr(x), N.dtype_code(x.dtype), N.ptr(even), N.ptr(odd),
+                                N.ptr(bnd), bnd.numel(), N.ptr(packed), N.ptr(norms), n * h, d,
+                                N.stream_ptr(dev)))
+    return packed, norms
+
+
+def tq4_decompress(
+    packed: torch.Tensor,
+    norms: torch.Tensor,
+    centroids: torch.Tensor,
+    dtype: torch.dtype = torch.float16,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """packed ``(N, H, D/2)`` + norms ``(N, H, 1)`` -> ``(N, H, D)`` in ``dtype``, rotated space.
+
+    Same contract as the reference's ``tq4_decompress``
+    (src/flashquant/kernels/decompress.py:49-86).
+    """
+    N.require_cuda(packed, norms)
+    n, h, half = packed.shape
+    dev = packed.device
+    cent = _f32(centroids, dev)
+    packed, norms = _contig(packed), _contig(norms)
+    if out is None:
+        out = torch.empty(n, h, 2 * half, dtype=dtype, device=dev)
+    elif out.shape != (n, h, 2 * half) or out.dtype != dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous (N, H, D) tensor of the requested dtype")
+    lib = N.load()
+    N.check(lib.fq_tq4_decompress(N.ptr(packed), N.ptr(norms), N.ptr(cent), cent.numel(),
+                                  N.ptr(out), N.dtype_code(dtype), n * h, 2 * half,
+                                  N.stream_ptr(dev)))
+    return out
+
+
+def tq_prod_quantize(x, rotation, boundaries, centroids, qjl_matrix):
+    """Two-stage quantiser on ``(..., D)``: packed codes, norms, packed sign bits, gamma.
+
+    Arithmetic of ``TurboQuantProd.quantize`` (src/flashquant/core/quantizer.py:270-304);
+    the signs come back as bits (bit j%8 of byte j//8 set <=> sign_j = +1).
+    """
+    N.require_cuda(x)
+    d = x.shape[-1]
+    dev = x.device
+    if qjl_matrix.shape != (d, d):
+        raise ValueError("qjl_dim must equal head_dim")
+    flat = _contig(x.reshape(-1, d))
+    nv = flat.shape[0]
+    rot, bnd = _f32(rotation, dev), _f32(boundaries, dev)
+    cent, s = _f32(centroids, dev), _f32(qjl_matrix, dev)
+    packed = torch.empty(nv, d // 2, dtype=torch.uint8, device=dev)
+    norms = torch.empty(nv, dtype=torch.float32, device=dev)
+    bits = torch.empty(nv, d // 8, dtype=torch.uint8, device=dev)
+    gamma = torch.empty(nv, dtype=torch.float32, device=dev)
+    lib = N.load()
+    N.check(lib.fq_tq_prod_quantize(N.ptr(flat), N.dtype_code(flat.dtype), N.ptr(rot),
+                                    N.ptr(bnd), bnd.numel(), N.ptr(cent), N.ptr(s),
+                                    N.ptr(packed), N.ptr(norms), N.ptr(bits), N.ptr(gamma), nv, d,
+                                    N.stream_ptr(dev)))
+    lead = x.shape[:-1]
+    return (packed.reshape(*lead, d // 2), norms.reshape(*lead, 1),
+            bits.reshape(*lead, d // 8), gamma.reshape(*lead, 1))
+
+
+# --------------------------------------------------------------------------------------
+# compress-on-append into the paged cache
+# --------------------------------------------------------------------------------------
+
+def _append_common(key, value, kv_cache, slot_mapping):
+    N.require_cuda(key, value, kv_cache, slot_mapping)
+    n, h, d = key.shape
+    if value.shape != key.shape or value.dtype != key.dtype:
+        raise ValueError("key and value must have the same shape and dtype")
+    if kv_cache.dtype != torch.uint8 or kv_cache.shape[-1] != h * (d + 8) or \
+            not kv_cache.is_contiguous():
+        raise ValueError("kv_cache must be contiguous uint8 (num_blocks, block_size, H*(D+8))")
+    if slot_mapping.dtype not in (torch.int32, torch.int64):
+        raise ValueError("slot_mapping must be int32 or int64")
+
+    def strided(t):
+        # a view whose token stride differs (e.g. a slice of a fused qkv tensor) is fine
+        if t.stride(2) == 1 and t.stride(1) == d and t.stride(0) % 4 == 0:
+            return t, t.stride(0)
+        t = t.contiguous()
+        return t, h * d
+
+    key, ks = strided(key)
+    value, vs = strided(value)
+    if ks != vs:
+        key, value, ks = key.contiguous(), value.contiguous(), h * d
+    num_slots = kv_cache.shape[0] * kv_cache.shape[1]
+    return key, value, ks, n, h, d, num_slots, _contig(slot_mapping)
+
+
+def tq4_compress_append(key, value, kv_cache, slot_mapping, rotation, boundaries_k,
+                        boundaries_v=None) -> None:
+    """Compress K and V of new tokens and write their packed rows at ``slot_mapping``.
+
+    One launch for what ``FlashQuantAttentionImpl._compress_and_store`` does with two
+    compress calls, eight slice copies and an index_put (src/flashquant/vllm/impl.py:220-263).
+    Negative slots are skipped.
+    """
+    key, value, stride, n, h, d, num_slots, slots = _append_common(key, value, kv_cache,
+                                                                   slot_mapping)
+    dev = key.device
+    rot = _f32(rotation, dev)
+    bk = _f32(boundaries_k, dev)
+    bv = bk if boundaries_v is None else _f32(boundaries_v, dev)
+    lib = N.load()
+    N.check(lib.fq_tq4_compress_append(
+        N.ptr(key), N.ptr(value), N.dtype_code(key.dtype), n, h, d, stride, N.ptr(rot),
+        N.ptr(bk), bk.numel(), N.ptr(bv), bv.numel(), N.ptr(kv_cache), num_slots, N.ptr(slots),
+        int(slots.dtype == torch.int64), N.stream_ptr(dev)))
+
+
+def tq4_compress_append_qjl(key, value, kv_cache, kq_cache, slot_mapping, rotation,
+                            boundaries_k, centroids_k, boundaries_v, qjl_matrix) -> None:
+    """As ``tq4_compress_append`` with K through the two-stage quantiser.
+
+    Sign bits and residual norm of every K vector go to the side plane ``kq_cache``
+    ``(num_blocks, block_size, H*(D/8+4))`` = [sign bits | gamma], heads in order.
+    """
+    key, value, stride, n, h, d, num_slots, slots = _append_common(key, value, kv_cache,
+                                                                   slot_mapping)
+    dev = key.device
+    if kq_cache.dtype != torch.uint8 or kq_cache.shape[-1] != h * (d // 8 + 4) or \
+            not kq_cache.is_contiguous() or \
+            kq_cache.shape[0] * kq_cache.shape[1] != num_slots:
+        raise ValueError("kq_cache must be contiguous uint8 (num_blocks, block_size, H*(D/8+4))")
+    if qjl_matrix.shape != (d, d):
+        raise ValueError("qjl_dim must equal head_dim")
+    rot, s = _f32(rotation, dev), _f32(qjl_matrix, dev)
+    bk, ck, bv = _f32(boundaries_k, dev), _f32(centroids_k, dev), _f32(boundaries_v, dev)
+    if ck.numel() != bk.numel() + 1:
+        raise ValueError("centroids_k must have one entry more than boundaries_k")
+    lib = N.load()
+    N.check(lib.fq_tq4_compress_append_qjl(
+        N.ptr(key), N.ptr(value), N.dtype_code(key.dtype), n, h, d, stride, N.ptr(rot),
+        N.ptr(bk), bk.numel(), N.ptr(ck), N.ptr(bv), bv.numel(), N.ptr(s), N.ptr(kv_cache),
+        N.ptr(kq_cache), num_slots, N.ptr(slots), int(slots.dtype == torch.int64),
+        N.stream_ptr(dev)))
+
+
+# --------------------------------------------------------------------------------------
+# split-K paged decode
+# --------------------------------------------------------------------------------------
+
+_workspaces = {}
+
+
+def decode_workspace(device, num_seqs: int, num_q_heads: int, head_dim: int,
+                     num_splits: int) -> torch.Tensor:
+    """A zero-initialised, cached workspace tensor large enough for the given decode shape."""
+    lib = N.load()
+    need = lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, head_dim, num_splits)
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(ws: torch.Tensor) -> int:
+    """Device status word of a decode workspace (0 = no error); synchronises the stream."""
+    st = C.c_uint32(0)
+    N.check(N.load().fq_workspace_status(N.ptr(ws), C.byref(st), N.stream_ptr(ws.device)))
+    return st.value
+
+
+def _decode_args(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
+                 num_kv_heads, head_dim, block_size):
+    N.require_cuda(q, kv_cache, block_table, seq_lens)
+    dev = q.device
+    num_seqs, hq, d = q.shape
+    if d != head_dim:
+        raise ValueError("q's last dimension must equal head_dim")
+    if kv_cache.dtype != torch.uint8 or not kv_cache.is_contiguous() or \
+            kv_cache.shape[1] != block_size or kv_cache.shape[2] != num_kv_heads * (d + 8):
+        raise ValueError("kv_cache must be contiguous uint8 (num_blocks, block_size, H*(D+8))")
+    if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise ValueError("block_table and seq_lens must be int32")
+    if block_table.stride(-1) != 1:
+        block_table = block_table.contiguous()
+    return (dev, num_seqs, hq, d, _contig(q), block_table, _contig(seq_lens),
+            _f32(centroids_k, dev), _f32(centroids_v, dev), _f32(rotation, dev))
+
+
+def split_k_paged_decode(
+    q: torch.Tensor,
+    kv_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    centroids_k: torch.Tensor,
+    centroids_v: torch.Tensor,
+    rotation: torch.Tensor,
+    num_kv_heads: int,
+    head_dim: int,
+    block_size: int,
+    sm_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    num_splits: int = 0,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Decode attention of one query token per sequence over the packed paged cache.
+
+    Same contract as the reference's ``split_k_paged_decode``
+    (src/flashquant/kernels/paged_decode.py:56-128): un-rotated ``q`` in, output in the
+    original space, ``num_splits = 0`` picks the partition count.
+    """
+    dev, num_seqs, hq, d, q, block_table, seq_lens, ck, cv, rot = _decode_args(
+        q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation, num_kv_heads,
+        head_dim, block_size)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of q's shape and dtype")
+    if workspace is None:
+        workspace = decode_workspace(dev, num_seqs, hq, d, num_splits)
+    lib = N.load()
+    N.check(lib.fq_split_k_paged_decode(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
+        block_table.stride(0), N.ptr(seq_lens), N.ptr(ck), ck.numel(), N.ptr(cv), cv.numel(),
+        N.ptr(rot), num_seqs, hq, num_kv_heads, d, block_size, kv_cache.shape[0],
+        float(sm_scale), N.ptr(out), int(num_splits), N.ptr(workspace), workspace.numel(),
+        N.stream_ptr(dev)))
+    return out
+
+
+def paged_decode_partials(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
+                          num_kv_heads, head_dim, block_size, num_splits, sm_scale=None,
+                          partials=None, workspace=None) -> torch.Tensor:
+    """Per-split (acc, m, l) rows ``(num_seqs, H_q, num_splits, D+4)`` fp32, no merge."""
+    dev, num_seqs, hq, d, q, block_table, seq_lens, ck, cv, rot = _decode_args(
+        q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation, num_kv_heads,
+        head_dim, block_size)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    if partials is None:
+        partials = torch.empty(num_seqs, hq, num_splits, d + _PART_PAD, dtype=torch.float32,
+                               device=dev)
+    if workspace is None:
+        workspace = decode_workspace(dev, num_seqs, hq, d, 1)
+    lib = N.load()
+    N.check(lib.fq_paged_decode_partials(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
+        block_table.stride(0), N.ptr(seq_lens), N.ptr(ck), ck.numel(), N.ptr(cv), cv.numel(),
+        N.ptr(rot), num_seqs, hq, num_kv_heads, d, block_size, kv_cache.shape[0],
+        float(sm_scale), int(num_splits), N.ptr(partials), N.ptr(workspace), workspace.numel(),
+        N.stream_ptr(dev)))
+    return partials
+
+
+def split_k_merge(partials: torch.Tensor, rotation: torch.Tensor, dtype: torch.dtype,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Merge ``(n_groups, num_seqs, H_q, n_splits, D+4)`` partials, round, rotate back."""
+    N.require_cuda(partials)
+    if partials.dim() == 4:
+        partials = partials.unsqueeze(0)
+    ng, num_seqs, hq, ns, dp = partials.shape
+    d = dp - _PART_PAD
+    dev = partials.device
+    partials = _contig(partials)
+    rot = _f32(rotation, dev)
+    if out is None:
+        out = torch.empty(num_seqs, hq, d, dtype=dtype, device=dev)
+    lib = N.load()
+    N.check(lib.fq_split_k_merge(N.ptr(partials), ng, ns, N.ptr(rot), num_seqs, hq, d,
+                                 N.ptr(out), N.dtype_code(dtype), N.stream_ptr(dev)))
+    return out

@@ -1,0 +1,218 @@
+/*
+ * flashquant_b200 - C ABI of the B200 (sm_100a) TurboQuant KV-cache kernels.
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and a CUDA stream, allocates
+ * nothing, never synchronises the stream and never aborts: it returns FQ_OK (0) or a
+ * negative fq_status, and fq_last_error_string() describes the last failure of the
+ * calling thread.  All launches are asynchronous on `stream`.
+ *
+ * Each declaration names the interface of ayinedjimi/flashquant it stands in for
+ * (paths relative to that repository).
+ */
+#ifndef FLASHQUANT_B200_H_
+#define FLASHQUANT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* fq_stream_t; /* same type as cudaStream_t */
+
+typedef enum fq_dtype {
+  FQ_F32 = 0,
+  FQ_F16 = 1,
+  FQ_BF16 = 2
+} fq_dtype;
+
+typedef enum fq_status {
+  FQ_OK = 0,
+  FQ_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, bad enum            */
+  FQ_ERR_UNSUPPORTED = -2,      /* shape outside what the kernels are built for     */
+  FQ_ERR_WORKSPACE = -3,        /* workspace missing, misaligned or too small       */
+  FQ_ERR_CUDA = -4,             /* a CUDA runtime call failed (launch, attribute)   */
+  FQ_ERR_ALIGNMENT = -5         /* a pointer or stride breaks an alignment rule     */
+} fq_status;
+
+/* Bits of the device-side status word kept at the start of a decode workspace. */
+#define FQ_DEV_BAD_BLOCK_INDEX 1u /* a block_table entry was outside [0, num_blocks) */
+#define FQ_DEV_WAIT_TIMEOUT 2u    /* a bounded wait on a shared-memory barrier ran out */
+
+int fq_version(void);
+const char* fq_last_error_string(void);
+/* Number of kernels this library has launched in the process so far (all threads). */
+uint64_t fq_launch_count(void);
+
+/*
+ * TQ4 compress, contiguous outputs.
+ * Replaces tq4_compress_cuda (csrc/cuda/compress.cuh:38-48) as reached from
+ * flashquant.kernels.compress.tq4_compress (src/flashquant/kernels/compress.py:83-92);
+ * arithmetic of compress_reference (src/flashquant/kernels/cpu_reference.py:22-61):
+ * n = |x|, y = (x/(n+1e-10)) Pi^T, code = #{b : b < y}, byte j = code[2j]<<4 | code[2j+1].
+ *   x            n_vectors x head_dim values of `dtype`, row stride head_dim
+ *   rot_T_even   (head_dim, head_dim/2) fp32: columns 0,2,4.. of Pi^T
+ *   rot_T_odd    (head_dim, head_dim/2) fp32: columns 1,3,5.. of Pi^T
+ *   boundaries   n_boundaries (<= 15) ascending fp32
+ *   packed       n_vectors x head_dim/2 bytes out
+ *   norms        n_vectors fp32 out
+ * head_dim is 64 or 128.
+ */
+int fq_tq4_compress(const void* x, fq_dtype dtype, const float* rot_T_even,
+                    const float* rot_T_odd, const float* boundaries, int n_boundaries,
+                    uint8_t* packed, float* norms, int64_t n_vectors, int head_dim,
+                    fq_stream_t stream);
+
+/*
+ * Stage-1 + stage-2 (QJL) quantiser, contiguous outputs.
+ * Arithmetic of TurboQuantProd.quantize (src/flashquant/core/quantizer.py:270-304):
+ * codes/norm as above with the (bits-1)-bit tables, r = x - (c[code] Pi) n,
+ * gamma = |r|, sign_j = sgn(sum_k r_k S[j][k]) with 0 -> +1.
+ *   rotation     (head_dim, head_dim) fp32 row-major Pi
+ *   centroids    n_boundaries + 1 fp32
+ *   qjl          (head_dim, head_dim) fp32 row-major S (qjl_dim must equal head_dim)
+ *   sign_bits    n_vectors x head_dim/8 bytes out; bit (j%8) of byte j/8 is 1 iff sign_j=+1
+ *   gamma        n_vectors fp32 out
+ */
+int fq_tq_prod_quantize(const void* x, fq_dtype dtype, const float* rotation,
+                        const float* boundaries, int n_boundaries, const float* centroids,
+                        const float* qjl, uint8_t* packed, float* norms, uint8_t* sign_bits,
+                        float* gamma, int64_t n_vectors, int head_dim, fq_stream_t stream);
+
+/*
+ * TQ4 decompress (rotated space): out[v][2j] = c[byte>>4]*n, out[v][2j+1] = c[byte&15]*n.
+ * Replaces tq4_decompress_cuda (csrc/cuda/decompress.cuh:40-48) as reached from
+ * flashquant.kernels.decompress.tq4_decompress (src/flashquant/kernels/decompress.py:75-77);
+ * arithmetic of decompress_reference (src/flashquant/kernels/cpu_reference.py:64-94).
+ * head_dim must be a multiple of 8; `out` holds n_vectors x head_dim values of out_dtype.
+ */
+int fq_tq4_decompress(const uint8_t* packed, const float* norms, const float* centroids,
+                      int n_centroids, void* out, fq_dtype out_dtype, int64_t n_vectors,
+                      int head_dim, fq_stream_t stream);
+
+/*
+ * Compress-on-append: K and V of n_tokens new tokens are compressed and their packed
+ * rows written straight into the paged cache at row slot_mapping[token].
+ * Replaces FlashQuantAttentionImpl._compress_and_store (src/flashquant/vllm/impl.py:220-263):
+ * two tq4_compress calls, eight slice copies and one index_put become one launch.
+ * Row layout (src/flashquant/vllm/impl.py:132-138): [K codes H*D/2 | K norms H*4 |
+ * V codes H*D/2 | V norms H*4], heads in order inside each region.
+ *   key, value          (n_tokens, num_kv_heads, head_dim) of `dtype`; the stride between
+ *                       tokens is token_stride elements (>= num_kv_heads*head_dim)
+ *   rotation            (head_dim, head_dim) fp32 row-major Pi, shared by K and V
+ *   boundaries_k / _v   ascending fp32 tables (may be the same pointer)
+ *   kv_cache            num_slots rows of num_kv_heads*(head_dim+8) bytes
+ *   slot_mapping        n_tokens entries, int64 if slot_is_int64 else int32; entries < 0 or
+ *                       >= num_slots are skipped (padding)
+ */
+int fq_tq4_compress_append(const void* key, const void* value, fq_dtype dtype,
+                           int64_t n_tokens, int num_kv_heads, int head_dim,
+                           int64_t token_stride, const float* rotation,
+                           const float* boundaries_k, int n_boundaries_k,
+                           const float* boundaries_v, int n_boundaries_v, uint8_t* kv_cache,
+                           int64_t num_slots, const void* slot_mapping, int slot_is_int64,
+                           fq_stream_t stream);
+
+/*
+ * Compress-on-append with K through the two-stage quantiser: as above, and the QJL sign
+ * bits and residual norm of every K vector go to a side plane with one row of
+ * num_kv_heads*(head_dim/8+4) bytes per slot: [sign bits H*D/8 | gamma H*4].
+ * The reference has no packed QJL storage (src/flashquant/vllm/impl.py:109-111 uses the
+ * one-stage quantiser for K); the arithmetic is TurboQuantProd.quantize
+ * (src/flashquant/core/quantizer.py:270-304).
+ */
+int fq_tq4_compress_append_qjl(const void* key, const void* value, fq_dtype dtype,
+                               int64_t n_tokens, int num_kv_heads, int head_dim,
+                               int64_t token_stride, const float* rotation,
+                               const float* boundaries_k, int n_boundaries_k,
+                               const float* centroids_k, const float* boundaries_v,
+                               int n_boundaries_v, const float* qjl, uint8_t* kv_cache,
+                               uint8_t* kq_cache, int64_t num_slots,
+                               const void* slot_mapping, int slot_is_int64,
+                               fq_stream_t stream);
+
+/*
+ * Split-K paged decode over the packed cache, un-rotated q in, original-space out.
+ * Replaces paged_tq4_decode_cuda + split_k_reduce_cuda (csrc/cuda/paged_decode.cu:346-421,
+ * csrc/cuda/split_k_reduce.cu:145-181) as reached from
+ * flashquant.kernels.paged_decode.split_k_paged_decode
+ * (src/flashquant/kernels/paged_decode.py:103-110); arithmetic of the CPU branch
+ * (paged_decode.py:112-128 + src/flashquant/kernels/cpu_reference.py:230-368):
+ * q_rot = round(q Pi^T), softmax(sm_scale q_rot K^T) V in rotated space with
+ * K = c_k[code] n_k and V = c_v[code] n_v, rounded, then out = round(o_rot Pi).
+ *   q, out         (num_seqs, num_q_heads, head_dim), FQ_F16 or FQ_BF16
+ *   kv_cache       (num_blocks, block_size, num_kv_heads*(head_dim+8)) bytes, 16-byte aligned
+ *   block_table    (num_seqs, block_table_stride) int32
+ *   seq_lens       (num_seqs) int32; a length of 0 gives a zero output row
+ *   num_splits     partitions of each sequence (>= 1); 0 picks one from the batch size
+ *   workspace      caller-owned, 256-byte aligned, at least
+ *                  fq_paged_decode_workspace_bytes(...) bytes; its first word is a status
+ *                  word that must be zero before the first call (FQ_DEV_* bits are OR-ed in)
+ * head_dim 128 (or 64), block_size a multiple of 16, num_kv_heads in {1,2,4,8},
+ * num_q_heads/num_kv_heads <= 8.
+ */
+size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads, int head_dim,
+                                       int num_splits);
+int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                            const int32_t* block_table, int64_t block_table_stride,
+                            const int32_t* seq_lens, const float* centroids_k,
+                            int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                            const float* rotation, int num_seqs, int num_q_heads,
+                            int num_kv_heads, int head_dim, int block_size,
+                            int64_t num_blocks, float sm_scale, void* out, int num_splits,
+                            void* workspace, size_t workspace_bytes, fq_stream_t stream);
+
+/*
+ * The two halves of the call above, for a sequence whose tokens are spread over several
+ * GPUs: each GPU produces partials over its own pages, the partials are exchanged (one
+ * all-gather) and every GPU merges all of them.
+ *
+ * fq_paged_decode_partials: `partials` (16-byte aligned) receives (num_seqs, num_q_heads,
+ * num_splits, head_dim+4) fp32 rows: head_dim un-normalised accumulator values, then m (the
+ * base-2 reference exponent of the split: the running maximum of logit*log2(e) + log2|v|), l (sum of
+ * 2^(logit-m)) and two zero pads; an empty split holds (0.., -inf, 0).  The workspace only
+ * needs fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, head_dim, 1) bytes here.
+ * The design follows the sketch in csrc/cuda/paged_decode.cu:198-275.
+ *
+ * fq_split_k_merge: `partials` is (n_groups, num_seqs, num_q_heads, n_splits, head_dim+4),
+ * i.e. n_groups buffers of the layout above back to back (n_groups = number of GPUs after an
+ * all-gather, 1 otherwise).  out = round(round(sum w_s acc_s / sum w_s l_s) Pi) with
+ * w_s = 2^(m_s - max m).  Stands in for split_k_reduce_cuda
+ * (csrc/cuda/split_k_reduce.cu:145-181), whose weighting (acc_s * l_s) is not the softmax.
+ */
+int fq_paged_decode_partials(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                             const int32_t* block_table, int64_t block_table_stride,
+                             const int32_t* seq_lens, const float* centroids_k,
+                             int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                             const float* rotation, int num_seqs, int num_q_heads,
+                             int num_kv_heads, int head_dim, int block_size,
+                             int64_t num_blocks, float sm_scale, int num_splits,
+                             float* partials, void* workspace, size_t workspace_bytes,
+                             fq_stream_t stream);
+/*
+ * fq_paged_decode_partials_rotated: as fq_paged_decode_partials for a query that is already
+ * in rotated space and stored as fp16 (num_seqs, num_q_heads, head_dim) - the calling
+ * convention of paged_decode_reference (src/flashquant/kernels/cpu_reference.py:230-241),
+ * which also takes the pre-rotated query.  Launches the streaming kernel only.
+ */
+int fq_paged_decode_partials_rotated(const void* q_rot_f16, const uint8_t* kv_cache,
+                                     const int32_t* block_table, int64_t block_table_stride,
+                                     const int32_t* seq_lens, const float* centroids_k,
+                                     int n_centroids_k, const float* centroids_v,
+                                     int n_centroids_v, int num_seqs, int num_q_heads,
+                                     int num_kv_heads, int head_dim, int block_size,
+                                     int64_t num_blocks, float sm_scale, int num_splits,
+                                     float* partials, void* workspace, size_t workspace_bytes,
+                                     fq_stream_t stream);
+int fq_split_k_merge(const float* partials, int n_groups, int n_splits,
+                     const float* rotation, int num_seqs, int num_q_heads, int head_dim,
+                     void* out, fq_dtype dtype, fq_stream_t stream);
+
+/* Copies the device status word of a decode workspace to *status (synchronises stream). */
+int fq_workspace_status(const void* workspace, uint32_t* status, fq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHQUANT_B200_H_ */

@@ -1,0 +1,62 @@
+"""CPU-only checks of the C-ABI library: it builds, loads and exports what the header declares."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+@pytest.fixture(scope="module")
+def lib_path():
+    from flashquant_b200 import build
+    return build.build_native()
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "flashquant_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    syms = header_symbols()
+    for must in ["fq_tq4_compress", "fq_tq4_decompress", "fq_tq4_compress_append",
+                 "fq_tq4_compress_append_qjl", "fq_split_k_paged_decode",
+                 "fq_paged_decode_partials", "fq_split_k_merge", "fq_last_error_string"]:
+        assert must in syms
+
+
+def test_library_exports_every_declared_symbol(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    for name in header_symbols():
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+
+
+def test_ctypes_table_matches_header(lib_path):
+    from flashquant_b200 import _native
+    assert sorted(_native.SIGNATURES) == header_symbols()
+    lib = _native.load()
+    assert lib.fq_version() >= 100
+
+
+def test_argument_errors_need_no_gpu(lib_path):
+    # argument validation happens before any CUDA call
+    from flashquant_b200 import _native
+    lib = _native.load()
+    rc = lib.fq_tq4_compress(None, 0, None, None, None, 15, None, None, 4, 128, None)
+    assert rc == -1 and b"null" in lib.fq_last_error_string()
+    rc = lib.fq_tq4_compress(None, 0, None, None, None, 15, None, None, -1, 128, None)
+    assert rc == -1
+    assert lib.fq_tq4_compress(None, 0, None, None, None, 15, None, None, 0, 128, None) == 0
+    assert lib.fq_paged_decode_workspace_bytes(32, 32, 128, 8) >= 32 * 32 * 8 * 132 * 4
+
+
+def test_package_refuses_cpu_tensors(lib_path):
+    import torch
+    import flashquant_b200 as fq
+    from flashquant_b200._native import FlashQuantNativeError
+    with pytest.raises(FlashQuantNativeError):
+        fq.tq4_compress(torch.randn(2, 1, 128), torch.eye(128), torch.zeros(15))

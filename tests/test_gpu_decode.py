@@ -1,0 +1,192 @@
+"""GPU parity of the split-K paged decode against the CPU oracle and the golden fixture.
+
+Bar: attention outputs within 2e-3 max-abs of the reference's decompress-then-attend path
+(bf16/fp16 outputs; see parity.attention_close for entries of magnitude >= 0.5).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import flashquant_b200 as fq
+from conftest import bf16_from_bits, load_golden
+from flashquant_b200 import kernels as K
+from flashquant_b200 import workloads as W
+from oracle import tq_oracle as O
+from parity import attention_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def fill_cache_cpu(w, consts, k_bits=3, v_bits=4, dtype=torch.bfloat16):
+    """Packed cache built by the oracle from seeded K/V (K: k_bits table, V: v_bits table)."""
+    d, h = w.head_dim, w.num_kv_heads
+    rot = consts[f"rotation_{d}_0"]
+    bk, bv = consts[f"boundaries_{d}_{k_bits}"], consts[f"boundaries_{d}_{v_bits}"]
+    k, v = W.make_kv(w.total_tokens, h, d, w.cfg, dtype)
+    cache = torch.zeros(w.num_blocks, w.block_size, h * (d + 8), dtype=torch.uint8)
+    O.compress_and_store(k, v, cache, w.slot_mapping, rot, bk, bv)
+    return cache
+
+
+def run_gpu(w, cache, consts, k_bits=3, v_bits=4, num_splits=0, q=None, sm_scale=None):
+    d = w.head_dim
+    q = w.q if q is None else q
+    return K.split_k_paged_decode(
+        q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+        consts[f"centroids_{d}_{k_bits}"], consts[f"centroids_{d}_{v_bits}"],
+        consts[f"rotation_{d}_0"], w.num_kv_heads, d, w.block_size, sm_scale=sm_scale,
+        num_splits=num_splits)
+
+
+def run_oracle(w, cache, consts, k_bits=3, v_bits=4, q=None, sm_scale=None):
+    d = w.head_dim
+    q = w.q if q is None else q
+    return O.split_k_paged_decode(
+        q, cache, w.block_table, w.seq_lens, consts[f"centroids_{d}_{k_bits}"],
+        consts[f"centroids_{d}_{v_bits}"], consts[f"rotation_{d}_0"], w.num_kv_heads, d,
+        w.block_size, sm_scale)
+
+
+def test_golden_fixture(consts):
+    z = load_golden("paged_decode.npz")
+    args = (T(z["kv_cache"]).to(DEV), T(z["block_table"]).to(DEV), T(z["seq_lens"]).to(DEV),
+            consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"],
+            int(z["h_kv"]), int(z["d"]), int(z["block_size"]))
+    for splits in (0, 1, 3, 8):
+        out = K.split_k_paged_decode(bf16_from_bits(z["q_bf16"]).to(DEV), *args, num_splits=splits)
+        attention_close(out, bf16_from_bits(z["out_bf16"]))
+        assert (out[0] == 0).all()  # empty sequence
+    out = K.split_k_paged_decode(T(z["q_f16"]).to(DEV), *args, sm_scale=float(z["sm_scale_f16"]),
+                                 num_splits=2)
+    attention_close(out, T(z["out_f16"]))
+    ws = K.decode_workspace(torch.device(DEV), 6, 8, 128, 0)
+    assert K.workspace_status(ws) == 0
+
+
+@pytest.mark.parametrize("hkv,hq", [(8, 32), (1, 8), (2, 2), (4, 8), (8, 64)])
+def test_ragged_lengths_vs_oracle(consts, hkv, hq):
+    lens = [0, 1, 15, 16, 17, 31, 33, 100, 257, 700]
+    w = W.decode_workload(seq_lens=lens, num_q_heads=hq, num_kv_heads=hkv, cfg=11, spare_blocks=5)
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    for splits in (1, 4, 8):
+        out = run_gpu(w, cache, consts, num_splits=splits)
+        attention_close(out, ref)
+
+
+def test_head_dim_64_and_shared_4bit_tables(consts):
+    w = W.decode_workload(seq_lens=[5, 64, 333], num_q_heads=8, num_kv_heads=2, head_dim=64, cfg=12)
+    cache = fill_cache_cpu(w, consts, k_bits=4, v_bits=4)
+    ref = run_oracle(w, cache, consts, k_bits=4, v_bits=4)
+    attention_close(run_gpu(w, cache, consts, k_bits=4, v_bits=4, num_splits=2), ref)
+
+
+def test_block_size_32_and_fp16_queries(consts):
+    w = W.decode_workload(seq_lens=[40, 129, 512], num_q_heads=16, num_kv_heads=4, block_size=32,
+                          cfg=13, dtype=torch.float16)
+    cache = fill_cache_cpu(w, consts, dtype=torch.float16)
+    ref = run_oracle(w, cache, consts, sm_scale=0.11)
+    attention_close(run_gpu(w, cache, consts, num_splits=3, sm_scale=0.11), ref)
+
+
+def test_split_count_and_page_permutation_invariance(consts):
+    """Size-independent properties: the result does not depend on the number of splits beyond
+    rounding, nor on where the pages physically live."""
+    w = W.decode_workload(num_seqs=4, context=2048, cfg=14)
+    cache = fill_cache_cpu(w, consts)
+    base = run_gpu(w, cache, consts, num_splits=1).float().cpu()
+    for splits in (2, 8, 32):
+        out = run_gpu(w, cache, consts, num_splits=splits).float().cpu()
+        assert (out - base).abs().max().item() <= 2e-3
+    # move every page: new table, same logical content
+    perm = torch.randperm(w.num_blocks, generator=torch.Generator().manual_seed(77))
+    cache2 = torch.empty_like(cache)
+    cache2[perm] = cache
+    w2 = W.decode_workload(num_seqs=4, context=2048, cfg=14)
+    w2.block_table = perm[w.block_table.long()].int()
+    out = run_gpu(w2, cache2, consts, num_splits=8).float().cpu()
+    assert torch.equal(out, run_gpu(w, cache, consts, num_splits=8).float().cpu())
+
+
+def test_partials_then_merge_equals_fused_call(consts):
+    w = W.decode_workload(seq_lens=[90, 1000, 17], cfg=15)
+    cache = fill_cache_cpu(w, consts)
+    args = (w.q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+            consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"], 8, 128, 16)
+    fused = K.split_k_paged_decode(*args, num_splits=4)
+    parts = K.paged_decode_partials(*args, num_splits=4)
+    assert parts.shape == (3, 32, 4, 132)
+    merged = K.split_k_merge(parts, consts["rotation_128_0"], torch.bfloat16)
+    assert torch.equal(merged, fused)
+    # the same partials presented as two groups of two splits (what an all-gather delivers)
+    two = parts.reshape(3, 32, 2, 2, 132).permute(2, 0, 1, 3, 4).contiguous()
+    merged2 = K.split_k_merge(two, consts["rotation_128_0"], torch.bfloat16)
+    assert (merged2.float() - fused.float()).abs().max().item() <= 1e-3
+    # short sequence: splits beyond its pages are empty (m = -inf, l = 0, acc = 0)
+    tail = parts[2, :, 2:, :].cpu()
+    assert torch.isinf(tail[..., 128]).all() and (tail[..., 129] == 0).all() and (tail[..., :128] == 0).all()
+
+
+def test_partials_match_oracle_formulas(consts):
+    w = W.decode_workload(seq_lens=[100], num_q_heads=4, num_kv_heads=1, cfg=16)
+    cache = fill_cache_cpu(w, consts)
+    rot, ck, cv = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    parts = K.paged_decode_partials(w.q.to(DEV), cache.to(DEV), w.block_table.to(DEV),
+                                    w.seq_lens.to(DEV), ck, cv, rot, 1, 128, 16, num_splits=2).cpu()
+    k, v = O.gather_paged(cache, w.block_table[0], 100, 1, 128, 16, ck, cv)
+    q_rot = (w.q.float() @ rot.T).to(torch.bfloat16).float()
+    for h in range(4):
+        for s, (a, b) in enumerate([(0, 64), (64, 100)]):  # 7 pages -> 4 + 3
+            logits = (k[0, a:b] @ q_rot[0, h]) / np.sqrt(128)
+            ref = torch.softmax(logits, 0) @ v[0, a:b]
+            got = parts[0, h, s, :128] / parts[0, h, s, 129]
+            assert (got - ref).abs().max().item() < 3e-3 * ref.abs().max().item() + 1e-4
+
+
+def test_full_size_config1_vs_oracle(consts):
+    """32 sequences x 4096 tokens, 8 KV heads, GQA 4:1, 8 splits, seed-2 block table."""
+    w = W.decode_workload()
+    assert w.num_blocks == 8192 and w.algorithmic_bytes() == 143_163_392
+    cache = fill_cache_cpu(w, consts)
+    out = run_gpu(w, cache, consts, num_splits=8)
+    ref = run_oracle(w, cache, consts)
+    err = attention_close(out, ref)
+    assert err <= 2e-3
+    ws = K.decode_workspace(torch.device(DEV), 32, 32, 128, 8)
+    assert K.workspace_status(ws) == 0
+
+
+def test_bad_block_index_is_reported_not_followed(consts):
+    w = W.decode_workload(seq_lens=[40, 40], num_q_heads=8, num_kv_heads=8, cfg=17)
+    cache = fill_cache_cpu(w, consts)
+    bt = w.block_table.clone()
+    bt[1, 1] = 10_000_000  # far outside the cache
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=DEV)
+    K.split_k_paged_decode(w.q.to(DEV), cache.to(DEV), bt.to(DEV), w.seq_lens.to(DEV),
+                           consts["centroids_128_3"], consts["centroids_128_4"],
+                           consts["rotation_128_0"], 8, 128, 16, num_splits=2, workspace=ws)
+    assert K.workspace_status(ws) & 1  # FQ_DEV_BAD_BLOCK_INDEX
+    torch.cuda.synchronize()
+
+
+def test_argument_errors(consts):
+    from flashquant_b200._native import FlashQuantNativeError
+    w = W.decode_workload(seq_lens=[20], num_q_heads=6, num_kv_heads=3, cfg=18)
+    cache = torch.zeros(w.num_blocks, 16, 3 * 136, dtype=torch.uint8, device=DEV)
+    with pytest.raises(FlashQuantNativeError) as e:
+        run_gpu(w, cache, consts)
+    assert e.value.code == -2  # 3 KV heads: unsupported, reported, no fallback
+    w = W.decode_workload(seq_lens=[20], cfg=18)
+    cache = torch.zeros(w.num_blocks, 16, 8 * 136, dtype=torch.uint8, device=DEV)
+    with pytest.raises(FlashQuantNativeError) as e:
+        K.split_k_paged_decode(w.q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV),
+                               consts["centroids_128_3"], consts["centroids_128_4"],
+                               consts["rotation_128_0"], 8, 128, 16, num_splits=4,
+                               workspace=torch.zeros(1024, dtype=torch.uint8, device=DEV))
+    assert e.value.code == -3
