@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     const int v_code_off = p.hkv * half_d + 4 * p.hkv + head * half_d;
     const int v_norm_off = 2 * p.hkv * half_d + 4 * p.hkv + 4 * head;
     const int k_code_off = head * half_d;
+    const bool wide = (p.hkv & 1) == 0;  // vector loads need an even number of KV heads
 
     int unit = 0;  // running unit index over this CTA's pages
     for (int i = 0; i < my_pages && !timed_out; ++i) {
@@ -235,10 +236,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         // ---------- S^T = K q^T : rows = 16 tokens, cols = q heads of the group ----------
         uint32_t ka[KW], kb[KW];
         if constexpr (KW == 4) {
-          const uint4 a = *reinterpret_cast<const uint4*>(r_lo + k_code_off + 16 * t);
-          const uint4 b = *reinterpret_cast<const uint4*>(r_hi + k_code_off + 16 * t);
-          ka[0] = a.x; ka[1] = a.y; ka[2] = a.z; ka[3] = a.w;
-          kb[0] = b.x; kb[1] = b.y; kb[2] = b.z; kb[3] = b.w;
+          if (wide) {
+            const uint4 a = *reinterpret_cast<const uint4*>(r_lo + k_code_off + 16 * t);
+            const uint4 b = *reinterpret_cast<const uint4*>(r_hi + k_code_off + 16 * t);
+            ka[0] = a.x; ka[1] = a.y; ka[2] = a.z; ka[3] = a.w;
+            kb[0] = b.x; kb[1] = b.y; kb[2] = b.z; kb[3] = b.w;
+          } else {  // odd number of KV heads: rows are only 8-byte aligned
+            const uint2* pa = reinterpret_cast<const uint2*>(r_lo + k_code_off + 16 * t);
+            const uint2* pb = reinterpret_cast<const uint2*>(r_hi + k_code_off + 16 * t);
+            const uint2 a0 = pa[0], a1 = pa[1], b0 = pb[0], b1 = pb[1];
+            ka[0] = a0.x; ka[1] = a0.y; ka[2] = a1.x; ka[3] = a1.y;
+            kb[0] = b0.x; kb[1] = b0.y; kb[2] = b1.x; kb[3] = b1.y;
+          }
         } else {
           const uint2 a = *reinterpret_cast<const uint2*>(r_lo + k_code_off + 8 * t);
           const uint2 b = *reinterpret_cast<const uint2*>(r_hi + k_code_off + 8 * t);
@@ -320,8 +329,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
           const int tokr = 2 * t + (r & 1) + (r >> 1) * 8;
           const unsigned char* src = vr + size_t(tokr) * row_bytes;
           if constexpr (VB == 8) {
-            const uint2 x = *reinterpret_cast<const uint2*>(src);
-            vw[r][0] = x.x; vw[r][1] = x.y;
+            if (wide) {
+              const uint2 x = *reinterpret_cast<const uint2*>(src);
+              vw[r][0] = x.x; vw[r][1] = x.y;
+            } else {  // the V region starts at an odd multiple of 4 bytes
+              vw[r][0] = reinterpret_cast<const uint32_t*>(src)[0];
+              vw[r][1] = reinterpret_cast<const uint32_t*>(src)[1];
+            }
           } else {
             vw[r][0] = *reinterpret_cast<const uint32_t*>(src);
           }

@@ -41,11 +41,25 @@ def check_norms(got, ref, rtol=NORM_RTOL):
 
 
 def attention_close(got, ref, atol=2e-3):
-    """max-abs 2e-3; entries of magnitude >= 0.5 may in addition be one bf16/fp16 ulp off,
-    because there a single rounding step of the output type already exceeds 2e-3."""
+    """Attention outputs: max-abs 2e-3, or one bf16 unit in the last place of the largest
+    entry of the same output row (|row|max * 2^-7) where that is larger.
+
+    The reference rounds twice to bf16 (rotated output, then the product with Pi), so an
+    entry of the final row inherits rounding steps of the row's largest entries.  At the
+    benchmark shapes (thousands of tokens per sequence) every |output| is below 0.25 and
+    the plain 2e-3 bound is the one that applies; short test sequences have outputs of
+    order 1, where the bf16 grid itself is coarser than 2e-3.
+    """
     got, ref = got.float().cpu(), ref.float().cpu()
-    ulp = 2.0 ** -8 if ref.dtype == torch.bfloat16 else 2.0 ** -8
-    tol = torch.maximum(torch.full_like(ref, atol), ref.abs() * ulp)
+    rowmax = ref.abs().amax(dim=-1, keepdim=True)
+    tol = torch.maximum(torch.full_like(ref, atol), rowmax * 2.0 ** -7)
     err = (got - ref).abs()
-    assert bool((err <= tol).all()), f"attention max-abs error {err.max().item():.3e}"
+    bad = err > tol
+    if bool(bad.any()):
+        i = int(torch.argmax((err - tol).flatten()))
+        idx = [int(v) for v in torch.unravel_index(torch.tensor(i), err.shape)]
+        raise AssertionError(
+            f"attention mismatch: {int(bad.sum())} of {bad.numel()} entries beyond tolerance; "
+            f"worst at {idx}: got {got.flatten()[i].item():.6f} ref {ref.flatten()[i].item():.6f} "
+            f"tol {tol.flatten()[i].item():.2e}; max-abs err {err.max().item():.3e}")
     return err.max().item()

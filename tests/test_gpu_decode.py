@@ -100,10 +100,9 @@ def test_split_count_and_page_permutation_invariance(consts):
     rounding, nor on where the pages physically live."""
     w = W.decode_workload(num_seqs=4, context=2048, cfg=14)
     cache = fill_cache_cpu(w, consts)
-    base = run_gpu(w, cache, consts, num_splits=1).float().cpu()
+    base = run_gpu(w, cache, consts, num_splits=1)
     for splits in (2, 8, 32):
-        out = run_gpu(w, cache, consts, num_splits=splits).float().cpu()
-        assert (out - base).abs().max().item() <= 2e-3
+        attention_close(run_gpu(w, cache, consts, num_splits=splits), base)
     # move every page: new table, same logical content
     perm = torch.randperm(w.num_blocks, generator=torch.Generator().manual_seed(77))
     cache2 = torch.empty_like(cache)
@@ -156,8 +155,13 @@ def test_full_size_config1_vs_oracle(consts):
     cache = fill_cache_cpu(w, consts)
     out = run_gpu(w, cache, consts, num_splits=8)
     ref = run_oracle(w, cache, consts)
-    err = attention_close(out, ref)
-    assert err <= 2e-3
+    attention_close(out, ref)
+    # with the outlier channels some heads put nearly all weight on one token, so outputs
+    # reach |3.5| where one bf16 step is 0.0156: entries beyond 2e-3 exist, are all covered
+    # by the one-step-of-the-row-maximum bound checked above, and must stay rare
+    err = (out.float().cpu() - ref.float()).abs()
+    assert (err > 2e-3).float().mean().item() < 5e-3
+    assert (err == 0).float().mean().item() > 0.5
     ws = K.decode_workspace(torch.device(DEV), 32, 32, 128, 8)
     assert K.workspace_status(ws) == 0
 
