@@ -49,7 +49,7 @@ SIGNATURES = {
                                       _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_partials_rotated": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i,
                                               _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
-    "fq_split_k_merge": (_i, [_p, _i, _i, _p, _i, _i, _i, _p, _i, _p]),
+    "fq_split_k_merge": (_i, [_p, _i, _p, _i, _i, _i, _p, _i, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
 }
 

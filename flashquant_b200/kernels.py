@@ -295,19 +295,20 @@ def split_k_paged_decode(
 
 
 def paged_decode_partials(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
-                          num_kv_heads, head_dim, block_size, num_splits, sm_scale=None,
+                          num_kv_heads, head_dim, block_size, num_splits=0, sm_scale=None,
                           partials=None, workspace=None) -> torch.Tensor:
-    """Per-split (acc, m, l) rows ``(num_seqs, H_q, num_splits, D+4)`` fp32, no merge."""
+    """One un-normalised (acc, m, l) row per sequence and query head: ``(num_seqs, H_q, D+4)``
+    fp32.  This is what a GPU contributes when the tokens of a sequence are spread over
+    several GPUs; ``split_k_merge`` combines the rows of all GPUs."""
     dev, num_seqs, hq, d, q, block_table, seq_lens, ck, cv, rot = _decode_args(
         q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation, num_kv_heads,
         head_dim, block_size)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(head_dim)
     if partials is None:
-        partials = torch.empty(num_seqs, hq, num_splits, d + _PART_PAD, dtype=torch.float32,
-                               device=dev)
+        partials = torch.empty(num_seqs, hq, d + _PART_PAD, dtype=torch.float32, device=dev)
     if workspace is None:
-        workspace = decode_workspace(dev, num_seqs, hq, d, 1)
+        workspace = decode_workspace(dev, num_seqs, hq, d, num_splits)
     lib = N.load()
     N.check(lib.fq_paged_decode_partials(
         N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
@@ -320,11 +321,11 @@ def paged_decode_partials(q, kv_cache, block_table, seq_lens, centroids_k, centr
 
 def split_k_merge(partials: torch.Tensor, rotation: torch.Tensor, dtype: torch.dtype,
                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Merge ``(n_groups, num_seqs, H_q, n_splits, D+4)`` partials, round, rotate back."""
+    """Merge ``(n_groups, num_seqs, H_q, D+4)`` partial rows, round, rotate back."""
     N.require_cuda(partials)
-    if partials.dim() == 4:
+    if partials.dim() == 3:
         partials = partials.unsqueeze(0)
-    ng, num_seqs, hq, ns, dp = partials.shape
+    ng, num_seqs, hq, dp = partials.shape
     d = dp - _PART_PAD
     dev = partials.device
     partials = _contig(partials)
@@ -332,6 +333,6 @@ def split_k_merge(partials: torch.Tensor, rotation: torch.Tensor, dtype: torch.d
     if out is None:
         out = torch.empty(num_seqs, hq, d, dtype=dtype, device=dev)
     lib = N.load()
-    N.check(lib.fq_split_k_merge(N.ptr(partials), ng, ns, N.ptr(rot), num_seqs, hq, d,
-                                 N.ptr(out), N.dtype_code(dtype), N.stream_ptr(dev)))
+    N.check(lib.fq_split_k_merge(N.ptr(partials), ng, N.ptr(rot), num_seqs, hq, d, N.ptr(out),
+                                 N.dtype_code(dtype), N.stream_ptr(dev)))
     return out

@@ -145,12 +145,14 @@ int fq_tq4_compress_append_qjl(const void* key, const void* value, fq_dtype dtyp
  *   kv_cache       (num_blocks, block_size, num_kv_heads*(head_dim+8)) bytes, 16-byte aligned
  *   block_table    (num_seqs, block_table_stride) int32
  *   seq_lens       (num_seqs) int32; a length of 0 gives a zero output row
- *   num_splits     partitions of each sequence (>= 1); 0 picks one from the batch size
+ *   num_splits     partitions of each sequence (1..64); every partition boundary is a
+ *                  boundary between partial rows.  The pages of the whole batch are spread
+ *                  evenly over the SMs whatever this number is; 0 means 1
  *   workspace      caller-owned, 256-byte aligned, at least
  *                  fq_paged_decode_workspace_bytes(...) bytes; its first word is a status
  *                  word that must be zero before the first call (FQ_DEV_* bits are OR-ed in)
- * head_dim 128 (or 64), block_size a multiple of 16, num_kv_heads in {1,2,4,8},
- * num_q_heads/num_kv_heads <= 8.
+ * head_dim 128 (or 64), block_size a multiple of 16, num_kv_heads in {1,2,4,8,16},
+ * num_q_heads/num_kv_heads <= 8, num_seqs <= 2048.
  */
 size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads, int head_dim,
                                        int num_splits);
@@ -165,21 +167,26 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
 
 /*
  * The two halves of the call above, for a sequence whose tokens are spread over several
- * GPUs: each GPU produces partials over its own pages, the partials are exchanged (one
- * all-gather) and every GPU merges all of them.
+ * GPUs: each GPU produces one partial row per (sequence, query head) over the pages it
+ * holds, the rows are exchanged (one all-gather) and every GPU merges all of them.
  *
  * fq_paged_decode_partials: `partials` (16-byte aligned) receives (num_seqs, num_q_heads,
- * num_splits, head_dim+4) fp32 rows: head_dim un-normalised accumulator values, then m (the
- * base-2 reference exponent of the split: the running maximum of logit*log2(e) + log2|v|), l (sum of
- * 2^(logit-m)) and two zero pads; an empty split holds (0.., -inf, 0).  The workspace only
- * needs fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, head_dim, 1) bytes here.
- * The design follows the sketch in csrc/cuda/paged_decode.cu:198-275.
+ * head_dim+4) fp32 rows: head_dim un-normalised accumulator values, then m (base-2
+ * reference exponent: the running maximum of logit*log2(e) + log2|v|), l (sum of
+ * 2^(logit*log2(e) - m)) and two zero pads; a sequence of length 0 gives (0.., -inf, 0).
+ * Workspace as for fq_split_k_paged_decode.  The partial-softmax triple follows the sketch
+ * in csrc/cuda/paged_decode.cu:198-275.
  *
- * fq_split_k_merge: `partials` is (n_groups, num_seqs, num_q_heads, n_splits, head_dim+4),
- * i.e. n_groups buffers of the layout above back to back (n_groups = number of GPUs after an
- * all-gather, 1 otherwise).  out = round(round(sum w_s acc_s / sum w_s l_s) Pi) with
- * w_s = 2^(m_s - max m).  Stands in for split_k_reduce_cuda
- * (csrc/cuda/split_k_reduce.cu:145-181), whose weighting (acc_s * l_s) is not the softmax.
+ * fq_paged_decode_partials_rotated: the same for a query that is already in rotated space
+ * and stored as fp16 (num_seqs, num_q_heads, head_dim) - the calling convention of
+ * paged_decode_reference (src/flashquant/kernels/cpu_reference.py:230-241), which also
+ * takes the pre-rotated query.  No rotation kernel is launched.
+ *
+ * fq_split_k_merge: `partials` is (n_groups, num_seqs, num_q_heads, head_dim+4), i.e.
+ * n_groups buffers of the layout above back to back (n_groups = number of GPUs after an
+ * all-gather).  out = round(round(sum w_g acc_g / sum w_g l_g) Pi), w_g = 2^(m_g - max m).
+ * Stands in for split_k_reduce_cuda (csrc/cuda/split_k_reduce.cu:145-181), whose weighting
+ * (acc_s * l_s) is not the softmax.
  */
 int fq_paged_decode_partials(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                              const int32_t* block_table, int64_t block_table_stride,
@@ -190,12 +197,6 @@ int fq_paged_decode_partials(const void* q, fq_dtype dtype, const uint8_t* kv_ca
                              int64_t num_blocks, float sm_scale, int num_splits,
                              float* partials, void* workspace, size_t workspace_bytes,
                              fq_stream_t stream);
-/*
- * fq_paged_decode_partials_rotated: as fq_paged_decode_partials for a query that is already
- * in rotated space and stored as fp16 (num_seqs, num_q_heads, head_dim) - the calling
- * convention of paged_decode_reference (src/flashquant/kernels/cpu_reference.py:230-241),
- * which also takes the pre-rotated query.  Launches the streaming kernel only.
- */
 int fq_paged_decode_partials_rotated(const void* q_rot_f16, const uint8_t* kv_cache,
                                      const int32_t* block_table, int64_t block_table_stride,
                                      const int32_t* seq_lens, const float* centroids_k,
@@ -205,9 +206,9 @@ int fq_paged_decode_partials_rotated(const void* q_rot_f16, const uint8_t* kv_ca
                                      int64_t num_blocks, float sm_scale, int num_splits,
                                      float* partials, void* workspace, size_t workspace_bytes,
                                      fq_stream_t stream);
-int fq_split_k_merge(const float* partials, int n_groups, int n_splits,
-                     const float* rotation, int num_seqs, int num_q_heads, int head_dim,
-                     void* out, fq_dtype dtype, fq_stream_t stream);
+int fq_split_k_merge(const float* partials, int n_groups, const float* rotation,
+                     int num_seqs, int num_q_heads, int head_dim, void* out, fq_dtype dtype,
+                     fq_stream_t stream);
 
 /* Copies the device status word of a decode workspace to *status (synchronises stream). */
 int fq_workspace_status(const void* workspace, uint32_t* status, fq_stream_t stream);

@@ -114,22 +114,43 @@ def test_split_count_and_page_permutation_invariance(consts):
 
 
 def test_partials_then_merge_equals_fused_call(consts):
-    w = W.decode_workload(seq_lens=[90, 1000, 17], cfg=15)
+    w = W.decode_workload(seq_lens=[90, 1000, 17, 0], cfg=15)
     cache = fill_cache_cpu(w, consts)
+    rot = consts["rotation_128_0"]
     args = (w.q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
-            consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"], 8, 128, 16)
+            consts["centroids_128_3"], consts["centroids_128_4"], rot, 8, 128, 16)
     fused = K.split_k_paged_decode(*args, num_splits=4)
     parts = K.paged_decode_partials(*args, num_splits=4)
-    assert parts.shape == (3, 32, 4, 132)
-    merged = K.split_k_merge(parts, consts["rotation_128_0"], torch.bfloat16)
-    assert torch.equal(merged, fused)
-    # the same partials presented as two groups of two splits (what an all-gather delivers)
-    two = parts.reshape(3, 32, 2, 2, 132).permute(2, 0, 1, 3, 4).contiguous()
-    merged2 = K.split_k_merge(two, consts["rotation_128_0"], torch.bfloat16)
-    assert (merged2.float() - fused.float()).abs().max().item() <= 1e-3
-    # short sequence: splits beyond its pages are empty (m = -inf, l = 0, acc = 0)
-    tail = parts[2, :, 2:, :].cpu()
-    assert torch.isinf(tail[..., 128]).all() and (tail[..., 129] == 0).all() and (tail[..., :128] == 0).all()
+    assert parts.shape == (4, 32, 132)
+    merged = K.split_k_merge(parts, rot, torch.bfloat16)
+    attention_close(merged, fused)
+    # empty sequence: (0.., -inf, 0)
+    tail = parts[3].cpu()
+    assert torch.isinf(tail[:, 128]).all() and (tail[:, 129] == 0).all() and (tail[:, :128] == 0).all()
+    assert (merged[3] == 0).all()
+
+
+def test_token_ranges_on_two_groups_merge_like_one(consts):
+    """What a cross-GPU split does: group 0 attends over the first pages of every sequence,
+    group 1 over the rest; merging the two partial rows equals attending over everything."""
+    w = W.decode_workload(seq_lens=[256, 1024, 48], cfg=19)
+    cache = fill_cache_cpu(w, consts).to(DEV)
+    rot = consts["rotation_128_0"]
+    ck, cv = consts["centroids_128_3"], consts["centroids_128_4"]
+    q = w.q.to(DEV)
+    full = K.split_k_paged_decode(q, cache, w.block_table.to(DEV), w.seq_lens.to(DEV), ck, cv,
+                                  rot, 8, 128, 16, num_splits=2)
+    cut = torch.tensor([128, 512, 16], dtype=torch.int32)       # tokens held by group 0
+    first = K.paged_decode_partials(q, cache, w.block_table.to(DEV), cut.to(DEV), ck, cv, rot, 8,
+                                    128, 16, num_splits=2).clone()
+    rest_table = torch.zeros_like(w.block_table)
+    for i in range(3):
+        n0 = int(cut[i]) // 16
+        rest_table[i, : w.block_table.shape[1] - n0] = w.block_table[i, n0:]
+    second = K.paged_decode_partials(q, cache, rest_table.to(DEV), (w.seq_lens - cut).to(DEV), ck,
+                                     cv, rot, 8, 128, 16, num_splits=2)
+    merged = K.split_k_merge(torch.stack([first, second]), rot, torch.bfloat16)
+    attention_close(merged, full)
 
 
 def test_partials_match_oracle_formulas(consts):
@@ -141,11 +162,22 @@ def test_partials_match_oracle_formulas(consts):
     k, v = O.gather_paged(cache, w.block_table[0], 100, 1, 128, 16, ck, cv)
     q_rot = (w.q.float() @ rot.T).to(torch.bfloat16).float()
     for h in range(4):
-        for s, (a, b) in enumerate([(0, 64), (64, 100)]):  # 7 pages -> 4 + 3
-            logits = (k[0, a:b] @ q_rot[0, h]) / np.sqrt(128)
-            ref = torch.softmax(logits, 0) @ v[0, a:b]
-            got = parts[0, h, s, :128] / parts[0, h, s, 129]
-            assert (got - ref).abs().max().item() < 3e-3 * ref.abs().max().item() + 1e-4
+        logits = (k[0] @ q_rot[0, h]) / np.sqrt(128)
+        ref = torch.softmax(logits, 0) @ v[0]
+        got = parts[0, h, :128] / parts[0, h, 129]
+        assert (got - ref).abs().max().item() < 3e-3 * ref.abs().max().item() + 1e-4
+        # l = sum 2^(logit*log2e - m)
+        lse2 = torch.logsumexp(logits, 0).item() / np.log(2)
+        assert abs(parts[0, h, 128].item() + np.log2(parts[0, h, 129].item()) - lse2) < 2e-3
+
+
+def test_many_short_sequences_and_more_sequences_than_sms(consts):
+    lens = [(7 * i) % 50 for i in range(300)]  # many zero-length and one-page sequences
+    w = W.decode_workload(seq_lens=lens, num_q_heads=8, num_kv_heads=2, cfg=20)
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    for splits in (0, 3):
+        attention_close(run_gpu(w, cache, consts, num_splits=splits), ref)
 
 
 def test_full_size_config1_vs_oracle(consts):
