@@ -151,7 +151,7 @@ def run_ours(args):
     q = w.q.to(dev)
     bt, sl = w.block_table.to(dev), w.seq_lens.to(dev)
     out = torch.empty_like(q)
-    ws = K.decode_workspace(dev, NUM_SEQS, HQ, D, SPLITS)
+    ws = K.decode_workspace(dev, NUM_SEQS, HQ, HKV, D, SPLITS)
     torch.cuda.synchronize()
 
     def decode(i):
@@ -194,14 +194,13 @@ def run_ours(args):
 
         # ---- dominant kernel alone (the streaming kernel), same inputs ------------------
         q_rot16 = (q.float() @ rot.T).to(q.dtype).to(torch.float16).contiguous()
-        parts = torch.empty(NUM_SEQS, HQ, SPLITS, D + 4, dtype=torch.float32, device=dev)
 
         def stream_only(i):
-            _native.check(lib.fq_paged_decode_partials_rotated(
+            _native.check(lib.fq_paged_decode_stream(
                 _native.ptr(q_rot16), _native.ptr(caches[i % CACHE_COPIES]), _native.ptr(bt),
                 bt.stride(0), _native.ptr(sl), _native.ptr(ck), ck.numel(), _native.ptr(cv),
                 cv.numel(), NUM_SEQS, HQ, HKV, D, BS, w.num_blocks, 1.0 / D ** 0.5, SPLITS,
-                _native.ptr(parts), _native.ptr(ws), ws.numel(), _native.stream_ptr(dev)))
+                _native.ptr(ws), ws.numel(), _native.stream_ptr(dev)))
 
         with torch.cuda.stream(side):
             stream_only(0)
@@ -295,7 +294,7 @@ def run_ours(args):
                     "what": "pinned host q / new K,V token / slot / block table / lengths -> "
                             "device, compress-on-append, decode, output -> pinned host, "
                             "synchronise; the packed cache itself stays in HBM"},
-            "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel<128>",
+            "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel<128, true>",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",

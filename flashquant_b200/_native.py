@@ -42,13 +42,15 @@ SIGNATURES = {
                                     _i64, _p, _i, _p]),
     "fq_tq4_compress_append_qjl": (_i, [_p, _p, _i, _i64, _i, _i, _i64, _p, _p, _i, _p, _p, _i,
                                         _p, _p, _p, _i64, _p, _i, _p]),
-    "fq_paged_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "fq_paged_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fq_split_k_paged_decode": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i, _i,
                                      _i, _i, _i64, _f, _p, _i, _p, _sz, _p]),
     "fq_paged_decode_partials": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i, _i,
                                       _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_partials_rotated": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i,
                                               _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
+    "fq_paged_decode_stream": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i,
+                                    _i64, _f, _i, _p, _sz, _p]),
     "fq_split_k_merge": (_i, [_p, _i, _p, _i, _i, _i, _p, _i, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
 }

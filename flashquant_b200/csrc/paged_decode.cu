@@ -3,9 +3,9 @@
 // Three launches per call:
 //   1. rotate_q_kernel      q_rot = round_to_q_dtype(q Pi^T), stored as fp16
 //   2. paged_decode_kernel  persistent, one CTA per SM: the pages of all sequences form one
-//                           flat list that is cut into equal runs, one per CTA; a run is
-//                           processed as segments that never cross a boundary of the
-//                           caller's split partition, and every segment leaves one
+//                           flat list that is cut into equal runs, one per team of warps; a
+//                           run is processed as segments that never cross a boundary of
+//                           the caller's split partition, and every segment leaves one
 //                           (acc, m, l) partial row per query head
 //   3. merge_rotate_kernel  merges the partial rows of a sequence, rounds to the output type,
 //                           multiplies by Pi
@@ -16,29 +16,29 @@
 // sustain at 7 TB/s.  So the multiply-adds go to the tensor pipe (mma.sync m16n8k16, the N
 // dimension being the query heads of the group) and a byte is turned into two fp16
 // centroids by ONE shared-memory look-up in a 256-entry table of fp16 pairs, replicated per
-// lane so that look-ups never conflict.  Operand fragments are built directly in registers
+// lane so that look-ups never conflict (with at most 8 key centroids the key side needs no
+// table at all: two byte permutes on a register-resident table do four look-ups).  Operand fragments are built directly in registers
 // in the order the look-ups deliver them; the k-dimension of the QK product and the row
 // dimension of the PV product are permuted accordingly (the query fragment and the
 // write-back apply the same permutation).
 //
-// Pages reach shared memory by 1-D bulk copies issued by a producer warp into a ring of
-// stages guarded by full/empty mbarriers; every wait is bounded and reports through the
-// status word instead of spinning forever.
+// Pages reach shared memory by 1-D bulk copies into per-team rings of stages guarded by
+// full/empty mbarriers; every wait is bounded and reports through the status word instead
+// of spinning forever.
 #include "fq_common.cuh"
 
 namespace fq {
 
-constexpr int kCW = 16;                         // compute warps per CTA
-constexpr int kDecodeThreads = (kCW + 1) * 32;  // + one producer warp
-constexpr int kComputeThreads = kCW * 32;
-constexpr int kLutBytes = 256 * 32 * 4;         // one table, one copy per lane
-constexpr int kMaxStages = 24;
+constexpr int kCW = 16;                  // warps per CTA (16 keeps 128 registers per thread)
+constexpr int kDecodeThreads = kCW * 32;
+constexpr int kLutBytes = 256 * 256;     // 256 entries x (32 lanes x 4 B for K + the same for V)
+constexpr int kMaxStages = 16;           // per team; the descriptor ring relies on <= 16
 constexpr int kMaxSeqs = 2048;                  // page-count prefix lives in shared memory
 constexpr int kMaxSplits = 64;
 constexpr int kPartPad = 4;                     // partial row = D + 4 floats (acc, m, l, 0, 0)
 constexpr float kPScaleLog2 = 14.f;             // fp16 weights are scaled by 2^14
 
-enum : int { kSegStart = 1, kSegEnd = 2, kQNew = 4, kLast = 8 };
+enum : int { kSegStart = 1, kSegEnd = 2, kQNew = 4 };
 
 struct DecodeArgs {
   const __half* q_rot;  // (num_seqs, Hq, D)
@@ -55,13 +55,9 @@ struct DecodeArgs {
   float scale_log2;
   int num_splits;
   int stages;
-  float* slots;  // (num_seqs * S + gridDim.x, Hq, D+4)
+  float* slots;  // (num_seqs * S + workers, Hq, D+4), workers = gridDim.x * teams
   uint32_t* status;
-  uint32_t off_ring, off_mbuf, off_q, off_prefix, off_desc, off_bar;
-};
-
-struct PageDesc {  // 32 bytes, written by the producer, read by every compute warp
-  int seq, tok0, seq_len, flags, slot, qslot, pad0, pad1;
+  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar;
 };
 
 // ------------------------------------------------------------------------------------
@@ -153,161 +149,158 @@ __global__ void __launch_bounds__(256) rotate_q_kernel(const T* __restrict__ q,
 
 // ------------------------------------------------------------------------------------
 // 2. streaming kernel
+//
+// A CTA of 16 warps hosts T = 16 / H_kv independent teams of H_kv warps (one warp per KV
+// head).  The flat page list of the batch is cut into C*T equal runs, one per team; a team
+// walks its run page by page through its own ring of shared-memory stages.  The first warp
+// of a team is also its producer: its lane 0 issues the bulk copies, without ever blocking,
+// whenever the warp is about to wait for a page ("pump"), and the whole warp prepares the
+// page descriptors (physical page, valid tokens, segment flags, partial-row slot) 32 at a
+// time, one chunk ahead.  Warps of a team never synchronise with each other except through
+// the stage barriers, and every warp writes its own partial rows.
 // ------------------------------------------------------------------------------------
-__device__ __forceinline__ void compute_barrier() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+constexpr uint32_t kLutStride = 256;  // bytes per table entry: K copy per lane, then V copy
+constexpr int kDescRing = 64;
+
+__device__ __forceinline__ uint32_t lds_u32(const unsigned char* smem, uint32_t off) {
+  return *reinterpret_cast<const uint32_t*>(smem + off);
 }
 
-template <int D>
+// (byte i of w) * 256 + lane4 in one instruction (lane4 < 128 sits in byte 0)
+template <int I>
+__device__ __forceinline__ uint32_t lut_addr(uint32_t w, uint32_t lane4) {
+  return prmt(w, lane4, 0x5504u | (uint32_t(I) << 4));
+}
+
+template <int D, bool KPRMT>
 __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeArgs p) {
   constexpr int KS = D / 16;  // k-steps of the QK product = m-tiles of the PV product
   constexpr int KW = D / 32;  // 32-bit words of K codes per lane and row
   constexpr int VB = D / 16;  // bytes of V codes per lane and row
+  constexpr int VW = (VB + 3) / 4;
   constexpr int ROWF = D + kPartPad;
 
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t half_d = D / 2;
   const uint32_t row_bytes = uint32_t(p.hkv) * (D + 8);
   const uint32_t page_bytes = uint32_t(p.block_size) * row_bytes;
-  int* prefix = reinterpret_cast<int*>(smem + p.off_prefix);
-  PageDesc* descs = reinterpret_cast<PageDesc*>(smem + p.off_desc);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.off_bar);
-  uint64_t* empty_bar = full_bar + p.stages;
-  uint64_t* qfull_bar = empty_bar + p.stages;
-  uint64_t* qempty_bar = qfull_bar + 2;
-  float* mbuf = reinterpret_cast<float*>(smem + p.off_mbuf);
-
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group = p.hq / p.hkv;  // q heads per KV head (<= 8)
   const uint32_t q_bytes = uint32_t(p.hq) * D * 2;
+  const int teams = kCW / p.hkv;
+  const int team = warp / p.hkv;
+  const int head = warp - team * p.hkv;
+  const bool leader = head == 0;
+  const int stages = p.stages;
 
-  // ---- set-up: barriers, page prefix (producer warp), look-up tables (compute warps) ---
-  if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) {
+  int* prefix = reinterpret_cast<int*>(smem + p.off_prefix);
+  int4* desc_ring = reinterpret_cast<int4*>(smem + p.off_desc) + team * kDescRing;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.off_bar) + team * (2 * stages + 2);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* qfull_bar = empty_bar + stages;
+  uint64_t* qempty_bar = qfull_bar + 1;
+  const uint32_t ring_off = p.off_ring + uint32_t(team) * stages * page_bytes;
+  const uint32_t q_off = p.off_q + uint32_t(team) * q_bytes;
+
+  // ---- set-up: barriers, page prefix (warp 0), look-up table (all warps) ---------------
+  if (leader && lane == 0) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + s, 1);
-      mbar_init(empty_bar + s, kCW);
+      mbar_init(empty_bar + s, p.hkv);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(qfull_bar + s, 1);
-      mbar_init(qempty_bar + s, kCW);
-    }
+    mbar_init(qfull_bar, 1);
+    mbar_init(qempty_bar, p.hkv);
     mbar_fence_init();
   }
-  if (warp == kCW) {
-    build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
-  } else {
-    for (int i = tid; i < 256 * 32; i += kComputeThreads) {
-      const int e = i >> 5;
-      const int hi = e >> 4, lo = e & 15;
-      const float kh = hi < p.nck ? p.cent_k[hi] : 0.f, kl = lo < p.nck ? p.cent_k[lo] : 0.f;
-      const float vh = hi < p.ncv ? p.cent_v[hi] : 0.f, vl = lo < p.ncv ? p.cent_v[lo] : 0.f;
-      reinterpret_cast<uint32_t*>(smem)[i] = pack_half2(kh, kl);  // low half: even coordinate
-      reinterpret_cast<uint32_t*>(smem + kLutBytes)[i] = pack_half2(vh, vl);
-    }
+  if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
+  for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
+    const int e = i >> 5, l = i & 31;
+    const int hi = e >> 4, lo = e & 15;
+    const float kh = hi < p.nck ? p.cent_k[hi] : 0.f, kl = lo < p.nck ? p.cent_k[lo] : 0.f;
+    const float vh = hi < p.ncv ? p.cent_v[hi] : 0.f, vl = lo < p.ncv ? p.cent_v[lo] : 0.f;
+    // K entry: byte of one token -> (even coordinate, odd coordinate)
+    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) = pack_half2(kh, kl);
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) = pack_half2(vl, vh);
   }
   __syncthreads();
 
-  // ---- this CTA's run of the flat page list -------------------------------------------------
+  // ---- this team's run of the flat page list ------------------------------------------------
   const int64_t total = prefix[p.num_seqs];
-  const int64_t active = total < int64_t(gridDim.x) ? total : int64_t(gridDim.x);
-  const int cta = blockIdx.x;
-  if (cta >= active) return;
-  const int64_t f0 = total * cta / active, f1 = total * (cta + 1) / active;
-  if (f0 >= f1) return;
+  const int64_t workers = int64_t(gridDim.x) * teams;
+  const int64_t active = total < workers ? total : workers;
+  const int64_t wk = int64_t(blockIdx.x) * teams + team;
+  if (wk >= active) return;
+  const int64_t f0 = total * wk / active, f1 = total * (wk + 1) / active;
+  const int n_run = int(f1 - f0);
+  if (n_run <= 0) return;
 
-  if (warp == kCW) {
-    // ================= producer (lane 0 waits and issues, the warp fetches table entries) ==
-    int lo = 0, hi = p.num_seqs - 1;  // the sequence that holds flat page f0
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (prefix[mid] <= f0) lo = mid; else hi = mid - 1;
-    }
-    int seq = lo;
-    int stage = 0, ephase = 1, it = 0, cur_q_seq = -1, qn = 0;
-    int64_t f = f0;
-    bool dead = false;
-    while (f < f1 && !dead) {
-      const int p0 = prefix[seq];
-      const int n_pages = prefix[seq + 1] - p0;
-      int pg = int(f - p0);
+  // ---- producer state (used by the leader warp only) ---------------------------------------
+  int issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0;
+
+  // descriptors of run pages [base, base + 32): x = physical page, y = valid tokens |
+  // flags << 8, z = sequence, w = partial-row slot
+  auto produce_chunk = [&](int base) {
+    const int i = base + lane;
+    if (i < n_run) {
+      const int64_t f = f0 + i;
+      int lo = 0, hi = p.num_seqs - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
+      }
+      const int seq = lo;
+      const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
+      const int pg = int(f - p0);
       const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
       const int s = pg / pps;
-      int seg_pages_end = (s + 1) * pps;
-      if (seg_pages_end > n_pages) seg_pages_end = n_pages;
-      int64_t seg_end = int64_t(p0) + seg_pages_end;
-      if (seg_end > f1) seg_end = f1;
-      const int slot = seq * p.num_splits + s + cta;
-      const int seq_len = p.seq_lens[seq];
-      const bool qnew = seq != cur_q_seq;
-      int qslot = (qn - 1) & 1;
-      if (qnew) {
-        qslot = qn & 1;
-        int ok = 1;
-        if (lane == 0) {
-          if (qn >= 2 && !mbar_wait(qempty_bar + qslot, ((qn >> 1) & 1) ^ 1)) {
-            atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
-            ok = 0;
-          } else {
-            mbar_expect_tx(qfull_bar + qslot, q_bytes);
-            bulk_g2s(smem + p.off_q + qslot * q_bytes, p.q_rot + int64_t(seq) * p.hq * D,
-                     q_bytes, qfull_bar + qslot);
-          }
-        }
-        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-        cur_q_seq = seq;
-        ++qn;
+      int split_end = (s + 1) * pps;
+      if (split_end > n_pages) split_end = n_pages;
+      const bool seg_first = (pg == s * pps) || (i == 0);
+      const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
+      const bool q_new = (i == 0) || (pg == 0);
+      int64_t phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
+      if (phys < 0 || phys >= p.num_blocks) {
+        atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
+        phys = 0;
       }
-      bool first = true;
-      while (f < seg_end && !dead) {
-        const int chunk = int(seg_end - f < 32 ? seg_end - f : 32);
-        int my_phys = 0;
-        if (lane < chunk) my_phys = p.block_table[int64_t(seq) * p.bt_stride + pg + lane];
-        for (int k = 0; k < chunk; ++k, ++f, ++pg) {
-          int64_t phys = __shfl_sync(0xffffffffu, my_phys, k);
-          int ok = 1;
-          if (lane == 0) {
-            if (it >= p.stages && !mbar_wait(empty_bar + stage, ephase)) {
-              atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
-              ok = 0;
-            } else {
-              if (phys < 0 || phys >= p.num_blocks) {
-                atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
-                phys = 0;
-              }
-              PageDesc d;
-              d.seq = seq; d.tok0 = pg * p.block_size; d.seq_len = seq_len;
-              d.flags = (first ? kSegStart : 0) | ((first && qnew) ? kQNew : 0) |
-                        (f + 1 == seg_end ? kSegEnd : 0) | (f + 1 == f1 ? kLast : 0);
-              d.slot = slot; d.qslot = qslot; d.pad0 = 0; d.pad1 = 0;
-              descs[stage] = d;
-              mbar_expect_tx(full_bar + stage, page_bytes);
-              bulk_g2s(smem + p.off_ring + uint32_t(stage) * page_bytes,
-                       p.kv_cache + phys * int64_t(page_bytes), page_bytes, full_bar + stage);
-            }
-          }
-          if (!__shfl_sync(0xffffffffu, ok, 0)) {
-            dead = true;
-            break;
-          }
-          if (++stage == p.stages) { stage = 0; ephase ^= 1; }
-          ++it;
-          first = false;
-        }
-      }
-      if (f == prefix[seq + 1]) {
-        ++seq;
-        while (seq < p.num_seqs - 1 && prefix[seq + 1] == prefix[seq]) ++seq;
-      }
+      int n_valid = p.seq_lens[seq] - pg * p.block_size;
+      if (n_valid > p.block_size) n_valid = p.block_size;
+      const int flags = (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
+      desc_ring[i & (kDescRing - 1)] =
+          make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
     }
-    return;
+    __syncwarp();
+  };
+
+  // lane 0 of the leader: issue every page whose stage is free; never blocks
+  auto pump = [&]() {
+    while (issue_idx < n_run) {
+      if (issue_idx >= stages && !mbar_try_wait(empty_bar + issue_stage, issue_phase)) break;
+      const int4 d = desc_ring[issue_idx & (kDescRing - 1)];
+      if ((d.y >> 8) & kQNew) {
+        if (q_issued > 0 && !mbar_try_wait(qempty_bar, (q_issued - 1) & 1)) break;
+        mbar_expect_tx(qfull_bar, q_bytes);
+        bulk_g2s(smem + q_off, p.q_rot + int64_t(d.z) * p.hq * D, q_bytes, qfull_bar);
+        ++q_issued;
+      }
+      mbar_expect_tx(full_bar + issue_stage, page_bytes);
+      bulk_g2s(smem + ring_off + uint32_t(issue_stage) * page_bytes,
+               p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
+               full_bar + issue_stage);
+      ++issue_idx;
+      if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
+    }
+  };
+
+  if (leader) {
+    produce_chunk(0);
+    if (lane == 0) pump();
   }
 
-  // ================= consumers =================
-  const int wph = kCW / p.hkv;  // warps per KV head (power of two)
-  const int head = warp & (p.hkv - 1);
-  const int sub = warp / p.hkv;
+  // ---- per-warp constants -------------------------------------------------------------------
   const uint32_t lane4 = uint32_t(lane) * 4;
   const bool wide = (p.hkv & 1) == 0;  // 16-byte row alignment needs an even head count
   const uint32_t k_code_off = head * half_d;
@@ -315,6 +308,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const uint32_t v_code_off = p.hkv * half_d + 4 * p.hkv + head * half_d;
   const uint32_t v_norm_off = 2 * p.hkv * half_d + 4 * p.hkv + 4 * head;
   const int units_per_page = p.block_size >> 4;
+
+  // 8-entry K table in registers (K by byte permute): low and high bytes of the fp16 values
+  uint32_t tl0 = 0, tl1 = 0, th0 = 0, th1 = 0;
+  if constexpr (KPRMT) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float c = i < p.nck ? p.cent_k[i] : 0.f;
+      const uint32_t h = uint32_t(__half_as_ushort(__float2half_rn(c)));
+      const uint32_t lo8 = (h & 0xffu) << (8 * (i & 3)), hi8 = (h >> 8) << (8 * (i & 3));
+      if (i < 4) { tl0 |= lo8; th0 |= hi8; } else { tl1 |= lo8; th1 |= hi8; }
+    }
+  }
 
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
@@ -327,16 +332,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     for (int c = 0; c < 4; ++c) oacc[j][c] = 0.f;
   }
 
-  int stage = 0, fphase = 0, qcnt = 0, unit_ctr = 0;
+  int stage = 0, fphase = 0, qcnt = 0;
   bool timed_out = false;
-  while (true) {
-    if (!mbar_wait(full_bar + stage, fphase)) {
+  for (int it = 0; it < n_run; ++it) {
+    // ---- wait for the page (the leader keeps the copies going while it waits) -----------
+    if (leader) {
+      // chunk k (pages 32k..32k+31) is written while the team is at page 32k-16: the ring
+      // slots it overwrites held pages < 32k-32, which every warp has left (a warp is never
+      // more than `stages` <= 16 pages behind), and the pump never looks further than 16
+      // pages ahead
+      if ((it & 31) == 16) produce_chunk(it + 16);
+      uint32_t spins = 0;
+      while (true) {
+        if (lane == 0) pump();
+        if (mbar_try_wait(full_bar + stage, fphase)) break;
+        if (++spins > kSpinLimit) {
+          timed_out = true;
+          break;
+        }
+      }
+      __syncwarp();
+    } else if (!mbar_wait(full_bar + stage, fphase)) {
       timed_out = true;
-      break;
     }
-    const int4 d0 = *reinterpret_cast<const int4*>(descs + stage);
-    const int2 d1 = *reinterpret_cast<const int2*>(reinterpret_cast<const int*>(descs + stage) + 4);
-    const int tok_page0 = d0.y, seq_len = d0.z, flags = d0.w;
+    if (timed_out) break;
+    const int4 d = desc_ring[it & (kDescRing - 1)];
+    const int n_valid = d.y & 0xff, flags = d.y >> 8;
 
     if (flags & kSegStart) {
       m_run[0] = m_run[1] = -INFINITY;
@@ -346,32 +367,34 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 #pragma unroll
         for (int c = 0; c < 4; ++c) oacc[j][c] = 0.f;
       if (flags & kQNew) {
-        const int qslot = d1.y;
-        if (!mbar_wait(qfull_bar + qslot, (qcnt >> 1) & 1)) {
+        if (!mbar_wait(qfull_bar, qcnt & 1)) {
           timed_out = true;
           break;
         }
         // lane (g,t), k-step s: coordinates of cache bytes (D/8)t + 2s, +1 of q head head*G+g
         const bool valid = g < group;
-        const uint32_t qoff = p.off_q + qslot * q_bytes +
-                              uint32_t(head * group + (valid ? g : 0)) * D * 2 + (D / 8) * t * 4;
+        const uint32_t qoff =
+            q_off + uint32_t(head * group + (valid ? g : 0)) * D * 2 + (D / 8) * t * 4;
 #pragma unroll
         for (int s = 0; s < KS; ++s) {
-          const uint2 v = *reinterpret_cast<const uint2*>(smem + qoff + 8 * s);
+          uint2 v = *reinterpret_cast<const uint2*>(smem + qoff + 8 * s);
+          if constexpr (KPRMT) {  // the byte-permute path delivers (odd, even) pairs
+            v.x = prmt(v.x, v.x, 0x1032);
+            v.y = prmt(v.y, v.y, 0x1032);
+          }
           qf[s][0] = valid ? v.x : 0u;
           qf[s][1] = valid ? v.y : 0u;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(qempty_bar + qslot);
+        if (lane == 0) mbar_arrive(qempty_bar);
         ++qcnt;
       }
     }
 
-    const uint32_t page_off = p.off_ring + uint32_t(stage) * page_bytes;
-    for (int u = 0; u < units_per_page; ++u, ++unit_ctr) {
-      if ((unit_ctr & (wph - 1)) != sub) continue;
-      const int tok0 = tok_page0 + u * 16;
-      if (tok0 >= seq_len) continue;
+    const uint32_t page_off = ring_off + uint32_t(stage) * page_bytes;
+    for (int u = 0; u < units_per_page; ++u) {
+      const int tok0 = u * 16;
+      if (tok0 >= n_valid) break;
       const uint32_t rows = page_off + uint32_t(u) * 16 * row_bytes;
       const uint32_t r_lo = rows + uint32_t(g) * row_bytes;
       const uint32_t r_hi = r_lo + 8 * row_bytes;
@@ -397,26 +420,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         ka[0] = a.x; ka[1] = a.y;
         kb[0] = b.x; kb[1] = b.y;
       }
-      // value codes: lane (g,t) needs tokens 2t, 2t+1, 2t+8, 2t+9, cache bytes VB*g .. +VB-1
-      uint32_t vw[4][(VB + 3) / 4];
-      {
-        const uint32_t vbase = rows + v_code_off + VB * g + uint32_t(2 * t) * row_bytes;
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const uint32_t src = vbase + uint32_t((r & 1) + (r >> 1) * 8) * row_bytes;
-          if constexpr (VB == 8) {
-            if (wide) {
-              const uint2 x = *reinterpret_cast<const uint2*>(smem + src);
-              vw[r][0] = x.x; vw[r][1] = x.y;
-            } else {  // the V region starts at an odd multiple of 4 bytes
-              vw[r][0] = *reinterpret_cast<const uint32_t*>(smem + src);
-              vw[r][1] = *reinterpret_cast<const uint32_t*>(smem + src + 4);
-            }
-          } else {
-            vw[r][0] = *reinterpret_cast<const uint32_t*>(smem + src);
-          }
-        }
-      }
       const float nk_lo = *reinterpret_cast<const float*>(smem + r_lo + k_norm_off);
       const float nk_hi = *reinterpret_cast<const float*>(smem + r_hi + k_norm_off);
       const float nv_lo = *reinterpret_cast<const float*>(smem + r_lo + v_norm_off);
@@ -424,30 +427,36 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 
       float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-      for (int s = 0; s < KS; ++s) {
-        const int w = s >> 1;
-        const uint32_t wa = ka[w], wb = kb[w];
-        uint32_t i0, i1, i2, i3;
-        if ((s & 1) == 0) {
-          i0 = ((wa << 7) & 0x7f80u) | lane4;
-          i1 = ((wb << 7) & 0x7f80u) | lane4;
-          i2 = ((wa >> 1) & 0x7f80u) | lane4;
-          i3 = ((wb >> 1) & 0x7f80u) | lane4;
+      for (int w = 0; w < KW; ++w) {
+        // word w of the lane's chunk = cache bytes 4w..4w+3 = k-steps 2w (bytes 0,1), 2w+1
+        uint32_t a[2][4];
+        if constexpr (KPRMT) {
+#pragma unroll
+          for (int hw = 0; hw < 2; ++hw) {
+            const uint32_t sa = hw ? (ka[w] >> 16) : ka[w], sb = hw ? (kb[w] >> 16) : kb[w];
+            const uint32_t la = prmt(tl0, tl1, sa), ha = prmt(th0, th1, sa);
+            const uint32_t lb = prmt(tl0, tl1, sb), hb = prmt(th0, th1, sb);
+            a[hw][0] = prmt(la, ha, 0x5140);  // row g, first byte: (odd, even) coordinate
+            a[hw][1] = prmt(lb, hb, 0x5140);  // row g+8
+            a[hw][2] = prmt(la, ha, 0x7362);  // row g, second byte
+            a[hw][3] = prmt(lb, hb, 0x7362);
+          }
         } else {
-          i0 = ((wa >> 9) & 0x7f80u) | lane4;
-          i1 = ((wb >> 9) & 0x7f80u) | lane4;
-          i2 = ((wa >> 17) & 0x7f80u) | lane4;
-          i3 = ((wb >> 17) & 0x7f80u) | lane4;
+          a[0][0] = lds_u32(smem, lut_addr<0>(ka[w], lane4));
+          a[0][1] = lds_u32(smem, lut_addr<0>(kb[w], lane4));
+          a[0][2] = lds_u32(smem, lut_addr<1>(ka[w], lane4));
+          a[0][3] = lds_u32(smem, lut_addr<1>(kb[w], lane4));
+          a[1][0] = lds_u32(smem, lut_addr<2>(ka[w], lane4));
+          a[1][1] = lds_u32(smem, lut_addr<2>(kb[w], lane4));
+          a[1][2] = lds_u32(smem, lut_addr<3>(ka[w], lane4));
+          a[1][3] = lds_u32(smem, lut_addr<3>(kb[w], lane4));
         }
-        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(smem + i0);
-        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(smem + i1);
-        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(smem + i2);
-        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(smem + i3);
-        mma_f16(sacc[s & 1], a0, a1, a2, a3, qf[s][0], qf[s][1]);  // two accumulator chains
+        mma_f16(sacc[0], a[0][0], a[0][1], a[0][2], a[0][3], qf[2 * w][0], qf[2 * w][1]);
+        mma_f16(sacc[1], a[1][0], a[1][1], a[1][2], a[1][3], qf[2 * w + 1][0], qf[2 * w + 1][1]);
       }
 
       // ---------- online softmax in the accumulator layout ---------------------------------
-      const bool ok_lo = tok0 + g < seq_len, ok_hi = tok0 + g + 8 < seq_len;
+      const bool ok_lo = tok0 + g < n_valid, ok_hi = tok0 + g + 8 < n_valid;
       // log2 of the value norm is folded into the exponent so that the fp16 weights stay in
       // range whatever the norms are; the running reference clamps it below so that l
       // cannot overflow
@@ -486,8 +495,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       for (int c = 0; c < 2; ++c) {
         const float mref = (m_run[c] == -INFINITY) ? 0.f : m_run[c];
         // lg2(0) = -inf makes the weight of a zero-norm value exactly 0
-        w_lo[c] = ok_lo ? fast_exp2(s_lo[c] + lg_lo - mref + kPScaleLog2) : 0.f;
-        w_hi[c] = ok_hi ? fast_exp2(s_hi[c] + lg_hi - mref + kPScaleLog2) : 0.f;
+        w_lo[c] = ok_lo ? fast_exp2(s_lo[c] + (lg_lo - mref + kPScaleLog2)) : 0.f;
+        w_hi[c] = ok_hi ? fast_exp2(s_hi[c] + (lg_hi - mref + kPScaleLog2)) : 0.f;
         const float p_lo = ok_lo ? fast_exp2(s_lo[c] - mref) : 0.f;
         const float p_hi = ok_hi ? fast_exp2(s_hi[c] - mref) : 0.f;
         l_run[c] += p_lo + p_hi;
@@ -497,100 +506,80 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       const uint32_t pb1 = movmatrix_trans(pack_half2(w_hi[0], w_hi[1]));
 
       // ---------- O^T += V^T P^T : rows = value coordinates, cols = q heads ------------------
+      // lane (g,t) takes the codes of tokens 2t, 2t+1 (and 2t+8, 2t+9), cache bytes
+      // VB*g .. VB*g+VB-1, and pairs equal nibbles of the two tokens into one table index
+      const uint32_t vbase = rows + v_code_off + VB * g + uint32_t(2 * t) * row_bytes;
 #pragma unroll
-      for (int j = 0; j < KS; ++j) {
-        const int w = j >> 2;
-        uint32_t i0, i1, i2, i3;
-        if ((j & 3) == 0) {
-          i0 = ((vw[0][w] << 7) & 0x7f80u) | lane4;
-          i1 = ((vw[1][w] << 7) & 0x7f80u) | lane4;
-          i2 = ((vw[2][w] << 7) & 0x7f80u) | lane4;
-          i3 = ((vw[3][w] << 7) & 0x7f80u) | lane4;
+      for (int w = 0; w < VW; ++w) {
+        uint32_t c0, c1, c2, c3;  // tokens 2t, 2t+1, 2t+8, 2t+9
+        if constexpr (VB == 8) {
+          if (wide) {
+            // both words of a row come with one 8-byte load
+            const uint2 x0 = *reinterpret_cast<const uint2*>(smem + vbase);
+            const uint2 x1 = *reinterpret_cast<const uint2*>(smem + vbase + row_bytes);
+            const uint2 x2 = *reinterpret_cast<const uint2*>(smem + vbase + 8 * row_bytes);
+            const uint2 x3 = *reinterpret_cast<const uint2*>(smem + vbase + 9 * row_bytes);
+            c0 = w ? x0.y : x0.x; c1 = w ? x1.y : x1.x;
+            c2 = w ? x2.y : x2.x; c3 = w ? x3.y : x3.x;
+          } else {
+            c0 = lds_u32(smem, vbase + 4 * w);
+            c1 = lds_u32(smem, vbase + row_bytes + 4 * w);
+            c2 = lds_u32(smem, vbase + 8 * row_bytes + 4 * w);
+            c3 = lds_u32(smem, vbase + 9 * row_bytes + 4 * w);
+          }
         } else {
-          const int sh = 8 * (j & 3) - 7;
-          i0 = ((vw[0][w] >> sh) & 0x7f80u) | lane4;
-          i1 = ((vw[1][w] >> sh) & 0x7f80u) | lane4;
-          i2 = ((vw[2][w] >> sh) & 0x7f80u) | lane4;
-          i3 = ((vw[3][w] >> sh) & 0x7f80u) | lane4;
+          c0 = lds_u32(smem, vbase);
+          c1 = lds_u32(smem, vbase + row_bytes);
+          c2 = lds_u32(smem, vbase + 8 * row_bytes);
+          c3 = lds_u32(smem, vbase + 9 * row_bytes);
         }
-        const uint32_t l0 = *reinterpret_cast<const uint32_t*>(smem + kLutBytes + i0);
-        const uint32_t l1 = *reinterpret_cast<const uint32_t*>(smem + kLutBytes + i1);
-        const uint32_t l2 = *reinterpret_cast<const uint32_t*>(smem + kLutBytes + i2);
-        const uint32_t l3 = *reinterpret_cast<const uint32_t*>(smem + kLutBytes + i3);
-        const uint32_t a0 = prmt(l0, l1, 0x5410);  // even coordinate, tokens 2t, 2t+1
-        const uint32_t a1 = prmt(l0, l1, 0x7632);  // odd coordinate
-        const uint32_t a2 = prmt(l2, l3, 0x5410);  // even coordinate, tokens 2t+8, 2t+9
-        const uint32_t a3 = prmt(l2, l3, 0x7632);
-        mma_f16(oacc[j], a0, a1, a2, a3, pb0, pb1);
+        // even coordinates sit in the high nibbles, odd ones in the low nibbles
+        const uint32_t ev01 = ((c0 >> 4) & 0x0f0f0f0fu) | (c1 & 0xf0f0f0f0u);
+        const uint32_t od01 = (c0 & 0x0f0f0f0fu) | ((c1 << 4) & 0xf0f0f0f0u);
+        const uint32_t ev23 = ((c2 >> 4) & 0x0f0f0f0fu) | (c3 & 0xf0f0f0f0u);
+        const uint32_t od23 = (c2 & 0x0f0f0f0fu) | ((c3 << 4) & 0xf0f0f0f0u);
+#define FQ_PV_STEP(I)                                                                   \
+  if (4 * w + I < VB) {                                                                 \
+    const uint32_t a0 = lds_u32(smem, lut_addr<I>(ev01, lane4) + 128);                  \
+    const uint32_t a1 = lds_u32(smem, lut_addr<I>(od01, lane4) + 128);                  \
+    const uint32_t a2 = lds_u32(smem, lut_addr<I>(ev23, lane4) + 128);                  \
+    const uint32_t a3 = lds_u32(smem, lut_addr<I>(od23, lane4) + 128);                  \
+    mma_f16(oacc[4 * w + I], a0, a1, a2, a3, pb0, pb1);                                 \
+  }
+        FQ_PV_STEP(0)
+        FQ_PV_STEP(1)
+        FQ_PV_STEP(2)
+        FQ_PV_STEP(3)
+#undef FQ_PV_STEP
       }
     }
 
     if (flags & kSegEnd) {
-      // ---- fold the warps that shared a KV head, then write this segment's partial rows --
+      // ---- this warp's partial rows of the segment --------------------------------------------
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
       }
-      const bool c_ok[2] = {2 * t < group, 2 * t + 1 < group};
-      float* rowp[2] = {mbuf + (head * group + (c_ok[0] ? 2 * t : 0)) * ROWF,
-                        mbuf + (head * group + (c_ok[1] ? 2 * t + 1 : 0)) * ROWF};
-      for (int r = 0; r < wph; ++r) {
-        if (sub == r) {
-          float a_old[2] = {0.f, 0.f}, a_me[2] = {1.f, 1.f}, m_n[2], l_n[2];
+      const float unscale = 1.f / 16384.f;  // 2^-kPScaleLog2
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            m_n[c] = m_run[c];
-            l_n[c] = l_run[c];
-            if (r > 0) {
-              const float m_o = rowp[c][D], l_o = rowp[c][D + 1];
-              m_n[c] = fmaxf(m_o, m_run[c]);
-              a_old[c] = (m_o == -INFINITY) ? 0.f : fast_exp2(m_o - m_n[c]);
-              a_me[c] = (m_run[c] == -INFINITY) ? 0.f : fast_exp2(m_run[c] - m_n[c]);
-              l_n[c] = l_o * a_old[c] + l_run[c] * a_me[c];
-            }
-          }
-          __syncwarp();
+      for (int c = 0; c < 2; ++c) {
+        const int col = 2 * t + c;
+        if (col >= group) continue;
+        float* row = p.slots + (int64_t(d.w) * p.hq + head * group + col) * ROWF;
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            if (!c_ok[c]) continue;
-#pragma unroll
-            for (int j = 0; j < KS; ++j) {
-              const int b = VB * g + j;  // cache byte -> coordinates 2b (row g), 2b+1 (row g+8)
-              float e = oacc[j][c] * a_me[c], o = oacc[j][2 + c] * a_me[c];
-              if (r > 0) {
-                e = fmaf(rowp[c][2 * b], a_old[c], e);
-                o = fmaf(rowp[c][2 * b + 1], a_old[c], o);
-              }
-              *reinterpret_cast<float2*>(rowp[c] + 2 * b) = make_float2(e, o);
-            }
-            if (g == 0) *reinterpret_cast<float2*>(rowp[c] + D) = make_float2(m_n[c], l_n[c]);
-          }
+        for (int j = 0; j < KS; ++j) {
+          const int b = VB * g + j;  // cache byte -> coordinates 2b (row g), 2b+1 (row g+8)
+          *reinterpret_cast<float2*>(row + 2 * b) =
+              make_float2(oacc[j][c] * unscale, oacc[j][2 + c] * unscale);
         }
-        compute_barrier();
+        if (g == 0) *reinterpret_cast<float4*>(row + D) = make_float4(m_run[c], l_run[c], 0.f, 0.f);
       }
-      {
-        float4* dst = reinterpret_cast<float4*>(p.slots + int64_t(d1.x) * p.hq * ROWF);
-        const float4* src = reinterpret_cast<const float4*>(mbuf);
-        const int n4 = p.hq * (ROWF / 4);
-        const float unscale = 1.f / 16384.f;  // 2^-kPScaleLog2
-        for (int i = tid; i < n4; i += kComputeThreads) {
-          float4 v = src[i];
-          if (i % (ROWF / 4) < D / 4) {
-            v.x *= unscale; v.y *= unscale; v.z *= unscale; v.w *= unscale;
-          } else {
-            v.z = 0.f; v.w = 0.f;
-          }
-          dst[i] = v;
-        }
-      }
-      compute_barrier();
     }
 
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar + stage);
-    if (flags & kLast) break;
-    if (++stage == p.stages) { stage = 0; fphase ^= 1; }
+    if (++stage == stages) { stage = 0; fphase ^= 1; }
   }
   if (timed_out && lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
 }
@@ -609,7 +598,7 @@ struct MergeArgs {
   const float* rows;
   int n_groups;    // !kFromSlots
   int num_splits;  // kFromSlots
-  int num_ctas;    // kFromSlots: grid size of the streaming kernel
+  int num_workers; // kFromSlots: teams of the streaming kernel (grid size x teams per CTA)
   const int32_t* seq_lens;
   int block_size;
   const float* rotation;
@@ -654,7 +643,7 @@ __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs 
       build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
       if (lane == 0) {
         const int64_t total = prefix[p.num_seqs];
-        const int64_t active = total < p.num_ctas ? total : int64_t(p.num_ctas);
+        const int64_t active = total < p.num_workers ? total : int64_t(p.num_workers);
         const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
         int n = 0;
         if (n_pages > 0) {
@@ -774,8 +763,9 @@ struct WorkspaceLayout {
 static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 // `splits` <= 0 sizes for the largest split count
-static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits, int ctas) {
+static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits, int workers) {
   if (splits <= 0) splits = kMaxSplits;
+  const int ctas = workers;
   WorkspaceLayout w;
   w.q_rot_off = 256;
   w.slots_off = up256(w.q_rot_off + size_t(num_seqs) * hq * d * sizeof(__half));
@@ -789,40 +779,36 @@ static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits,
 static int auto_splits() { return 1; }
 
 struct SmemPlan {
-  int stages;
-  uint32_t off_ring, off_mbuf, off_q, off_prefix, off_desc, off_bar, total;
+  int stages;  // per team
+  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, total;
 };
 
 static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size) {
   SmemPlan s{};
+  const uint32_t teams = uint32_t(kCW / hkv);
   const uint32_t page_bytes = uint32_t(block_size) * hkv * (d + 8);
   auto up16 = [](uint32_t v) { return (v + 15u) & ~15u; };
-  const uint32_t mbuf = up16(uint32_t(hq) * (d + kPartPad) * 4);
-  const uint32_t qring = 2 * up16(uint32_t(hq) * d * 2);
+  const uint32_t q_all = teams * up16(uint32_t(hq) * d * 2);
   const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
-  const uint32_t fixed = 2 * kLutBytes + mbuf + qring + prefix;
+  const uint32_t desc = teams * kDescRing * 16;
+  const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16;
   const uint32_t budget = 227 * 1024 - 512;
   int stages = 0;
-  if (budget > fixed)
-    stages = int((budget - fixed) / (page_bytes + uint32_t(sizeof(PageDesc)) + 16));
-  // enough bytes in flight per SM to cover HBM latency, no more
-  const int want = int((112 * 1024 + page_bytes - 1) / page_bytes);
-  if (stages > want) stages = want;
+  if (budget > fixed) stages = int((budget - fixed) / (teams * (page_bytes + 16)));
   if (stages > kMaxStages) stages = kMaxStages;
   s.stages = stages;
-  s.off_ring = 2 * kLutBytes;
-  s.off_mbuf = s.off_ring + uint32_t(stages < 0 ? 0 : stages) * page_bytes;
-  s.off_q = s.off_mbuf + mbuf;
-  s.off_prefix = s.off_q + qring;
+  s.off_ring = kLutBytes;
+  s.off_q = s.off_ring + teams * uint32_t(stages < 0 ? 0 : stages) * page_bytes;
+  s.off_prefix = s.off_q + q_all;
   s.off_desc = s.off_prefix + prefix;
-  s.off_bar = s.off_desc + uint32_t(stages) * uint32_t(sizeof(PageDesc));
-  s.total = s.off_bar + (2 * uint32_t(stages) + 4) * 8;
+  s.off_bar = s.off_desc + desc;
+  s.total = s.off_bar + teams * (2 * uint32_t(stages) + 2) * 8;
   return s;
 }
 
-template <int D>
-static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
-  auto kern = paged_decode_kernel<D>;
+template <int D, bool KPRMT>
+static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
+  auto kern = paged_decode_kernel<D, KPRMT>;
   // opt in once per (thread, device, size): the attribute call is not free
   static thread_local int set_dev = -1;
   static thread_local size_t set_bytes = 0;
@@ -838,10 +824,20 @@ static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream
     set_bytes = sp.total;
   }
   a.stages = sp.stages;
-  a.off_ring = sp.off_ring; a.off_mbuf = sp.off_mbuf; a.off_q = sp.off_q;
+  a.off_ring = sp.off_ring; a.off_q = sp.off_q;
   a.off_prefix = sp.off_prefix; a.off_desc = sp.off_desc; a.off_bar = sp.off_bar;
   kern<<<ctas, kDecodeThreads, sp.total, stream>>>(a);
   return check_launch("paged decode kernel launch");
+}
+
+static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, int head_dim,
+                         cudaStream_t stream) {
+  const bool kprmt = a.nck <= 8;  // key codes fit a register-resident 8-entry table
+  if (head_dim == 128)
+    return kprmt ? launch_stream_t<128, true>(a, sp, ctas, stream)
+                 : launch_stream_t<128, false>(a, sp, ctas, stream);
+  return kprmt ? launch_stream_t<64, true>(a, sp, ctas, stream)
+               : launch_stream_t<64, false>(a, sp, ctas, stream);
 }
 
 template <int D>
@@ -924,8 +920,8 @@ static int validate_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cach
              "paged decode: num_kv_heads %d (built for 1, 2, 4, 8, 16)", hkv);
   FQ_REQUIRE(hq % hkv == 0 && hq / hkv <= 8, FQ_ERR_UNSUPPORTED,
              "paged decode: %d q heads per KV head (at most 8, and a whole number)", hq / hkv);
-  FQ_REQUIRE(block_size >= 16 && block_size % 16 == 0, FQ_ERR_UNSUPPORTED,
-             "paged decode: block_size %d is not a multiple of 16", block_size);
+  FQ_REQUIRE(block_size >= 16 && block_size % 16 == 0 && block_size <= 128, FQ_ERR_UNSUPPORTED,
+             "paged decode: block_size %d (a multiple of 16, at most 128)", block_size);
   FQ_REQUIRE(num_seqs <= kMaxSeqs, FQ_ERR_UNSUPPORTED,
              "paged decode: %d sequences per call (at most %d)", num_seqs, kMaxSeqs);
   FQ_REQUIRE(num_splits <= kMaxSplits, FQ_ERR_UNSUPPORTED,
@@ -945,7 +941,7 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                         int ctas, cudaStream_t stream) {
   FQ_REQUIRE(workspace && aligned(workspace, 256), FQ_ERR_WORKSPACE,
              "paged decode: workspace is null or not 256-byte aligned");
-  const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas);
+  const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv));
   FQ_REQUIRE(workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
              "paged decode: workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
   const SmemPlan sp = plan_smem(num_seqs, hq, hkv, head_dim, block_size);
@@ -976,18 +972,18 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.num_splits = num_splits;
   a.slots = reinterpret_cast<float*>(ws + w.slots_off);
   a.status = reinterpret_cast<uint32_t*>(ws);
-  return head_dim == 128 ? launch_stream<128>(a, sp, ctas, stream)
-                         : launch_stream<64>(a, sp, ctas, stream);
+  return launch_stream(a, sp, ctas, head_dim, stream);
 }
 
-static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int head_dim,
+static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int hkv, int head_dim,
                                  int num_splits, int ctas, const int32_t* seq_lens,
                                  int block_size) {
-  const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas);
+  const int workers = ctas * (kCW / hkv);
+  const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, workers);
   MergeArgs m{};
   m.rows = reinterpret_cast<const float*>(static_cast<unsigned char*>(workspace) + w.slots_off);
   m.num_splits = num_splits;
-  m.num_ctas = ctas;
+  m.num_workers = workers;
   m.seq_lens = seq_lens;
   m.block_size = block_size;
   m.num_seqs = num_seqs;
@@ -999,10 +995,14 @@ static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int head
 
 using namespace fq;
 
-extern "C" size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads, int head_dim,
+extern "C" size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads,
+                                                  int num_kv_heads, int head_dim,
                                                   int num_splits) {
-  if (num_seqs < 0 || num_q_heads < 0 || head_dim < 0) return 0;
-  return workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, 256).total;
+  if (num_seqs < 0 || num_q_heads < 0 || head_dim < 0 || num_kv_heads < 1 || num_kv_heads > kCW)
+    return 0;
+  // sized for any current device: up to 192 SMs
+  return workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, 192 * (kCW / num_kv_heads))
+      .total;
 }
 
 extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
@@ -1027,8 +1027,8 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
                     num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
                     workspace, workspace_bytes, ctas, stream);
   if (rc != FQ_OK) return rc;
-  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, head_dim, num_splits, ctas,
-                                seq_lens, block_size);
+  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                num_splits, ctas, seq_lens, block_size);
   m.rotation = rotation;
   m.out = out;
   return launch_merge<true, true>(m, head_dim, dtype, stream);
@@ -1052,8 +1052,8 @@ static int partials_common(const void* q, fq_dtype dtype, const uint8_t* kv_cach
                         num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
                         sm_scale, num_splits, workspace, workspace_bytes, ctas, stream);
   if (rc != FQ_OK) return rc;
-  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, head_dim, num_splits, ctas,
-                                seq_lens, block_size);
+  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                num_splits, ctas, seq_lens, block_size);
   m.row_out = partials;
   return launch_merge<true, false>(m, head_dim, FQ_F16, stream);
 }
@@ -1094,6 +1094,29 @@ extern "C" int fq_paged_decode_partials_rotated(
                          centroids_k, n_centroids_k, centroids_v, n_centroids_v, nullptr,
                          num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
                          sm_scale, num_splits, partials, workspace, workspace_bytes, stream);
+}
+
+extern "C" int fq_paged_decode_stream(const void* q_rot_f16, const uint8_t* kv_cache,
+                                      const int32_t* block_table, int64_t block_table_stride,
+                                      const int32_t* seq_lens, const float* centroids_k,
+                                      int n_centroids_k, const float* centroids_v,
+                                      int n_centroids_v, int num_seqs, int num_q_heads,
+                                      int num_kv_heads, int head_dim, int block_size,
+                                      int64_t num_blocks, float sm_scale, int num_splits,
+                                      void* workspace, size_t workspace_bytes,
+                                      fq_stream_t stream) {
+  alignas(16) static const float kDummy[4] = {0.f, 0.f, 0.f, 0.f};  // validate wants non-null
+  int rc = validate_decode(q_rot_f16, FQ_F16, kv_cache, block_table, seq_lens, centroids_k,
+                           n_centroids_k, centroids_v, n_centroids_v, kDummy, num_seqs,
+                           num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
+                           num_splits);
+  if (rc != FQ_OK) return rc;
+  if (num_seqs == 0) return FQ_OK;
+  if (num_splits == 0) num_splits = auto_splits();
+  return decode_front(q_rot_f16, FQ_F16, kv_cache, block_table, block_table_stride, seq_lens,
+                      centroids_k, n_centroids_k, centroids_v, n_centroids_v, nullptr, num_seqs,
+                      num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, sm_scale,
+                      num_splits, workspace, workspace_bytes, device_sm_count(), stream);
 }
 
 extern "C" int fq_split_k_merge(const float* partials, int n_groups, const float* rotation,

@@ -213,11 +213,12 @@ def tq4_compress_append_qjl(key, value, kv_cache, kq_cache, slot_mapping, rotati
 _workspaces = {}
 
 
-def decode_workspace(device, num_seqs: int, num_q_heads: int, head_dim: int,
+def decode_workspace(device, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int,
                      num_splits: int) -> torch.Tensor:
     """A zero-initialised, cached workspace tensor large enough for the given decode shape."""
     lib = N.load()
-    need = lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, head_dim, num_splits)
+    need = lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                               num_splits)
     key = (device.type, device.index)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
@@ -283,7 +284,7 @@ def split_k_paged_decode(
     elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
         raise ValueError("out must be a contiguous tensor of q's shape and dtype")
     if workspace is None:
-        workspace = decode_workspace(dev, num_seqs, hq, d, num_splits)
+        workspace = decode_workspace(dev, num_seqs, hq, num_kv_heads, d, num_splits)
     lib = N.load()
     N.check(lib.fq_split_k_paged_decode(
         N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
@@ -308,7 +309,7 @@ def paged_decode_partials(q, kv_cache, block_table, seq_lens, centroids_k, centr
     if partials is None:
         partials = torch.empty(num_seqs, hq, d + _PART_PAD, dtype=torch.float32, device=dev)
     if workspace is None:
-        workspace = decode_workspace(dev, num_seqs, hq, d, num_splits)
+        workspace = decode_workspace(dev, num_seqs, hq, num_kv_heads, d, num_splits)
     lib = N.load()
     N.check(lib.fq_paged_decode_partials(
         N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),

@@ -154,8 +154,8 @@ int fq_tq4_compress_append_qjl(const void* key, const void* value, fq_dtype dtyp
  * head_dim 128 (or 64), block_size a multiple of 16, num_kv_heads in {1,2,4,8,16},
  * num_q_heads/num_kv_heads <= 8, num_seqs <= 2048.
  */
-size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads, int head_dim,
-                                       int num_splits);
+size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
+                                       int head_dim, int num_splits);
 int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                             const int32_t* block_table, int64_t block_table_stride,
                             const int32_t* seq_lens, const float* centroids_k,
@@ -206,6 +206,18 @@ int fq_paged_decode_partials_rotated(const void* q_rot_f16, const uint8_t* kv_ca
                                      int64_t num_blocks, float sm_scale, int num_splits,
                                      float* partials, void* workspace, size_t workspace_bytes,
                                      fq_stream_t stream);
+/*
+ * The streaming stage alone (rotated fp16 query in, per-segment partial rows left in the
+ * workspace): what a profiler or a benchmark times when it wants the memory-bound kernel
+ * without the two small kernels around it.  No counterpart in the reference.
+ */
+int fq_paged_decode_stream(const void* q_rot_f16, const uint8_t* kv_cache,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const int32_t* seq_lens, const float* centroids_k,
+                           int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                           int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                           int block_size, int64_t num_blocks, float sm_scale, int num_splits,
+                           void* workspace, size_t workspace_bytes, fq_stream_t stream);
 int fq_split_k_merge(const float* partials, int n_groups, const float* rotation,
                      int num_seqs, int num_q_heads, int head_dim, void* out, fq_dtype dtype,
                      fq_stream_t stream);

@@ -51,7 +51,7 @@ def test_argument_errors_need_no_gpu(lib_path):
     rc = lib.fq_tq4_compress(None, 0, None, None, None, 15, None, None, -1, 128, None)
     assert rc == -1
     assert lib.fq_tq4_compress(None, 0, None, None, None, 15, None, None, 0, 128, None) == 0
-    assert lib.fq_paged_decode_workspace_bytes(32, 32, 128, 8) >= 32 * 32 * 8 * 132 * 4
+    assert lib.fq_paged_decode_workspace_bytes(32, 32, 8, 128, 8) >= 32 * 32 * 8 * 132 * 4
 
 
 def test_package_refuses_cpu_tensors(lib_path):

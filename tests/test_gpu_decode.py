@@ -65,7 +65,7 @@ def test_golden_fixture(consts):
     out = K.split_k_paged_decode(T(z["q_f16"]).to(DEV), *args, sm_scale=float(z["sm_scale_f16"]),
                                  num_splits=2)
     attention_close(out, T(z["out_f16"]))
-    ws = K.decode_workspace(torch.device(DEV), 6, 8, 128, 0)
+    ws = K.decode_workspace(torch.device(DEV), 6, 8, 2, 128, 0)
     assert K.workspace_status(ws) == 0
 
 
@@ -194,7 +194,7 @@ def test_full_size_config1_vs_oracle(consts):
     err = (out.float().cpu() - ref.float()).abs()
     assert (err > 2e-3).float().mean().item() < 5e-3
     assert (err == 0).float().mean().item() > 0.5
-    ws = K.decode_workspace(torch.device(DEV), 32, 32, 128, 8)
+    ws = K.decode_workspace(torch.device(DEV), 32, 32, 8, 128, 8)
     assert K.workspace_status(ws) == 0
 
 
@@ -203,7 +203,7 @@ def test_bad_block_index_is_reported_not_followed(consts):
     cache = fill_cache_cpu(w, consts)
     bt = w.block_table.clone()
     bt[1, 1] = 10_000_000  # far outside the cache
-    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(4 << 20, dtype=torch.uint8, device=DEV)
     K.split_k_paged_decode(w.q.to(DEV), cache.to(DEV), bt.to(DEV), w.seq_lens.to(DEV),
                            consts["centroids_128_3"], consts["centroids_128_4"],
                            consts["rotation_128_0"], 8, 128, 16, num_splits=2, workspace=ws)
