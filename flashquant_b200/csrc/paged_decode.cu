@@ -25,6 +25,8 @@
 // Pages reach shared memory by 1-D bulk copies into per-team rings of stages guarded by
 // full/empty mbarriers; every wait is bounded and reports through the status word instead
 // of spinning forever.
+#include <cstdlib>
+
 #include "fq_common.cuh"
 
 namespace fq {
@@ -214,16 +216,30 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     mbar_init(qempty_bar, p.hkv);
     mbar_fence_init();
   }
+  // centroids as fp16, staged where the first ring stage will live later
+  {
+    __half* cstage = reinterpret_cast<__half*>(smem + p.off_ring);
+    if (tid < 32) {
+      const int i = tid & 15;
+      float c = 0.f;
+      if (tid < 16) { if (i < p.nck) c = p.cent_k[i]; } else { if (i < p.ncv) c = p.cent_v[i]; }
+      cstage[tid] = __float2half_rn(c);
+    }
+  }
+  __syncthreads();
   if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
-  for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
-    const int e = i >> 5, l = i & 31;
-    const int hi = e >> 4, lo = e & 15;
-    const float kh = hi < p.nck ? p.cent_k[hi] : 0.f, kl = lo < p.nck ? p.cent_k[lo] : 0.f;
-    const float vh = hi < p.ncv ? p.cent_v[hi] : 0.f, vl = lo < p.ncv ? p.cent_v[lo] : 0.f;
-    // K entry: byte of one token -> (even coordinate, odd coordinate)
-    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) = pack_half2(kh, kl);
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) = pack_half2(vl, vh);
+  {
+    const unsigned short* cs = reinterpret_cast<const unsigned short*>(smem + p.off_ring);
+    for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t hi = e >> 4, lo = e & 15;
+      // K entry: byte of one token -> (even coordinate, odd coordinate)
+      // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
+      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
+          uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
+      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
+          uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
+    }
   }
   __syncthreads();
 
@@ -275,10 +291,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     __syncwarp();
   };
 
-  // lane 0 of the leader: issue every page whose stage is free; never blocks
+  // lane 0 of the leader: issue pages whose stage is free; never blocks.  The answer of an
+  // mbarrier poll takes a few hundred cycles to come back, so the poll for the next stage
+  // is sent early (`pump_poll`, in the middle of a page) and only read here.
+  bool empty_ok = true;  // stage of page `issue_idx` known to be free
+  auto pump_poll = [&]() {
+    if (issue_idx < n_run && !empty_ok)
+      empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
+  };
   auto pump = [&]() {
     while (issue_idx < n_run) {
-      if (issue_idx >= stages && !mbar_try_wait(empty_bar + issue_stage, issue_phase)) break;
+      if (!empty_ok) {
+        empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
+        if (!empty_ok) break;
+      }
       const int4 d = desc_ring[issue_idx & (kDescRing - 1)];
       if ((d.y >> 8) & kQNew) {
         if (q_issued > 0 && !mbar_try_wait(qempty_bar, (q_issued - 1) & 1)) break;
@@ -292,6 +318,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
                full_bar + issue_stage);
       ++issue_idx;
       if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
+      empty_ok = issue_idx < stages;  // the first pass over the ring needs no poll
     }
   };
 
@@ -333,7 +360,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   }
 
   int stage = 0, fphase = 0, qcnt = 0;
-  bool timed_out = false;
+  bool timed_out = false, page_ready = false;
+#pragma unroll 1
   for (int it = 0; it < n_run; ++it) {
     // ---- wait for the page (the leader keeps the copies going while it waits) -----------
     if (leader) {
@@ -342,20 +370,29 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       // more than `stages` <= 16 pages behind), and the pump never looks further than 16
       // pages ahead
       if ((it & 31) == 16) produce_chunk(it + 16);
-      uint32_t spins = 0;
-      while (true) {
-        if (lane == 0) pump();
-        if (mbar_try_wait(full_bar + stage, fphase)) break;
-        if (++spins > kSpinLimit) {
-          timed_out = true;
-          break;
+      if (lane == 0) pump();
+      if (!page_ready) {
+        uint32_t spins = 0;
+#pragma unroll 1
+        while (!mbar_try_wait(full_bar + stage, fphase)) {
+          if (lane == 0) pump();
+          if (++spins > kSpinLimit) {
+            timed_out = true;
+            break;
+          }
         }
       }
       __syncwarp();
-    } else if (!mbar_wait(full_bar + stage, fphase)) {
+    } else if (!page_ready && !mbar_wait(full_bar + stage, fphase)) {
       timed_out = true;
     }
     if (timed_out) break;
+    // the poll for the next page goes out now and is read at the top of the next iteration
+    {
+      int ns = stage + 1, nph = fphase;
+      if (ns == stages) { ns = 0; nph ^= 1; }
+      page_ready = (it + 1 < n_run) && mbar_try_wait(full_bar + ns, nph);
+    }
     const int4 d = desc_ring[it & (kDescRing - 1)];
     const int n_valid = d.y & 0xff, flags = d.y >> 8;
 
@@ -454,6 +491,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         mma_f16(sacc[0], a[0][0], a[0][1], a[0][2], a[0][3], qf[2 * w][0], qf[2 * w][1]);
         mma_f16(sacc[1], a[1][0], a[1][1], a[1][2], a[1][3], qf[2 * w + 1][0], qf[2 * w + 1][1]);
       }
+
+      if (leader && lane == 0) pump_poll();
 
       // ---------- online softmax in the accumulator layout ---------------------------------
       const bool ok_lo = tok0 + g < n_valid, ok_hi = tok0 + g + 8 < n_valid;
@@ -832,7 +871,8 @@ static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStre
 
 static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, int head_dim,
                          cudaStream_t stream) {
-  const bool kprmt = a.nck <= 8;  // key codes fit a register-resident 8-entry table
+  static const bool force_lut = getenv("FQ_DECODE_KLUT") != nullptr;  // experiment knob
+  const bool kprmt = a.nck <= 8 && !force_lut;  // key codes fit a register-resident 8-entry table
   if (head_dim == 128)
     return kprmt ? launch_stream_t<128, true>(a, sp, ctas, stream)
                  : launch_stream_t<128, false>(a, sp, ctas, stream);
