@@ -52,6 +52,9 @@ SIGNATURES = {
     "fq_paged_decode_stream": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i,
                                     _i64, _f, _i, _p, _sz, _p]),
     "fq_split_k_merge": (_i, [_p, _i, _p, _i, _i, _i, _p, _i, _p]),
+    "fq_fused_tq_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "fq_fused_tq_attention": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i,
+                                   _i, _f, _i, _p, _p, _sz, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
 }
 

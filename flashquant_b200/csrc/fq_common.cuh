@@ -220,4 +220,10 @@ __device__ __forceinline__ float fast_log2(float x) {
   return r;
 }
 
+// rotate.cu: row rotations around the prefill kernel
+int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* out,
+                     int64_t n_rows, int head_dim, cudaStream_t stream);
+int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out, int64_t n_rows,
+                int head_dim, cudaStream_t stream);
+
 }  // namespace fq

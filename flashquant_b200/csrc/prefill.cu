@@ -1,0 +1,471 @@
+// Fused causal TQ4 FlashAttention-2 prefill for sm_100a on the 5th-generation tensor cores.
+//
+// One CTA of 128 threads owns 128 query rows of one (batch, query head) and walks the KV
+// sequence in tiles of 64 tokens, skipping tiles above the causal diagonal.  Per tile:
+//   * the packed K and V codes of the tile arrive by 1-D bulk copy (4 KB each, the next
+//     tile's copy is in flight while this one is processed);
+//   * all threads turn codes into fp16 centroids (256-entry table of fp16 pairs) and store
+//     them as tcgen05 shared-memory operands; the norms are NOT applied here: |k| scales the
+//     score column, |v| is folded into the softmax weight, as in the decode kernel;
+//   * one thread issues S = Q K^T (tcgen05.mma, fp16 x fp16 -> fp32 in TMEM);
+//   * thread r reads row r of S from TMEM (tcgen05.ld), applies |k|, the scale and the
+//     causal mask, updates the online softmax and writes the fp16 weights as the A operand
+//     of the second product;
+//   * one thread issues O_tile = P V into TMEM; thread r adds its row, rescaled, to the 128
+//     fp32 accumulators it keeps in registers.
+// Two such CTAs fit an SM (94 KB of shared memory, 256 of the 512 TMEM columns each), so one
+// CTA's softmax overlaps the other's tensor work.
+//
+// Shared-memory operands use the un-swizzled canonical layout: 8 x 16-byte core matrices,
+// laid out [k-chunk of 8 elements][row][16 bytes]; each k-chunk slab is padded by 16 bytes
+// so that the cooperative stores do not conflict.
+//
+// The query arrives already rotated and rounded (fp16 copy of round(q Pi^T)), the output
+// leaves in rotated space as fp32 (the reference rounds only after the multiplication by
+// Pi); rotate.cu does both rotations.
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int kPfM = 128;       // query rows per CTA
+constexpr int kPfN = 64;        // KV tokens per tile
+constexpr int kPfThreads = 128;
+constexpr int kPfTmemCols = 256;
+constexpr float kPfPScaleLog2 = 14.f;
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(holder_smem)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], fp16 inputs, fp32 accumulate; issued by ONE thread
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// all previously issued MMAs of this thread arrive on `bar` when they have completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// lane l of the warp receives 32 consecutive fp32 columns of TMEM lane (lane_base + l)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, no swizzle, descriptor version 1.
+// lbo / sbo in bytes (multiples of 16): for a K-major operand lbo is the distance between
+// the two 8-element k-chunks of one MMA and sbo the distance between 8-row groups; for an
+// MN-major operand sbo is the distance between 8-element groups along M/N and lbo the
+// distance between 8-row groups along K.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return uint64_t((addr >> 4) & 0x3fffu) | (uint64_t((lbo >> 4) & 0x3fffu) << 16) |
+         (uint64_t((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+// Instruction descriptor: fp16 A and B, fp32 D, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
+
+struct PrefillArgs {
+  const __half* q_rot;      // (B, Hq, Nq, D) fp16, rotated and rounded
+  const uint8_t* k_packed;  // (B, Hkv, Nkv, D/2)
+  const float* k_norms;     // (B, Hkv, Nkv)
+  const uint8_t* v_packed;
+  const float* v_norms;
+  const float* cent_k;
+  int nck;
+  const float* cent_v;
+  int ncv;
+  float* o_rot;  // (B, Hq, Nq, D) fp32, rotated space (the reference rounds only after Pi)
+  int batch, hq, hkv, nq, nkv;
+  float scale_log2;
+  int causal;
+  uint32_t* status;
+};
+
+template <int D>
+struct PrefillSmem {
+  static constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
+  static constexpr uint32_t kSlabQ = (kPfM + 1) * 16;             // one k-chunk of the Q tile
+  static constexpr uint32_t kSlabKV = (kPfN + 1) * 16;            // one k-chunk of a K/V tile
+  static constexpr uint32_t kSlabP = (kPfM + 1) * 16;             // one k-chunk of the P tile
+  static constexpr uint32_t kOffQ = 0;
+  static constexpr uint32_t kOffK = kOffQ + kChunks * kSlabQ;
+  static constexpr uint32_t kOffV = kOffK + kChunks * kSlabKV;
+  static constexpr uint32_t kOffP = kOffV + kChunks * kSlabKV;
+  static constexpr uint32_t kOffRaw = kOffP + (kPfN / 8) * kSlabP;  // 2 x (K codes, V codes)
+  static constexpr uint32_t kRawTile = kPfN * (D / 2);
+  static constexpr uint32_t kOffNorm = kOffRaw + 4 * kRawTile;      // nk*scale, lg2 nv, clamped
+  static constexpr uint32_t kOffLut = kOffNorm + 3 * kPfN * 4;
+  static constexpr uint32_t kOffBar = kOffLut + 2 * 256 * 4;
+  static constexpr uint32_t kBytes = kOffBar + 64;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(PrefillArgs p) {
+  using S = PrefillSmem<D>;
+  constexpr uint32_t kIdescS = umma_idesc(kPfM, kPfN, false);
+  constexpr uint32_t kIdescO = umma_idesc(kPfM, D, true);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + S::kOffBar);  // [2]
+  uint64_t* bar_s = bar_raw + 2;
+  uint64_t* bar_o = bar_raw + 3;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_raw + 4);
+  float* nk_s = reinterpret_cast<float*>(smem + S::kOffNorm);
+  float* lg_s = nk_s + kPfN;
+  float* lv_s = lg_s + kPfN;
+  uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem + S::kOffLut);
+  uint32_t* lut_v = lut_k + 256;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // heavy (late) query tiles first: the causal work per tile grows with its index
+  const int m_tile = int(gridDim.x) - 1 - int(blockIdx.x);
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int group = p.hq / p.hkv;
+  const int hkv = hq / group;
+  const int m0 = m_tile * kPfM;
+  const int rows = p.nq - m0 < kPfM ? p.nq - m0 : kPfM;
+
+  int kv_end = p.nkv;
+  if (p.causal && m0 + rows < kv_end) kv_end = m0 + rows;
+  const int n_tiles = (kv_end + kPfN - 1) / kPfN;
+
+  const uint8_t* kc_base = p.k_packed + (int64_t(b) * p.hkv + hkv) * p.nkv * (D / 2);
+  const uint8_t* vc_base = p.v_packed + (int64_t(b) * p.hkv + hkv) * p.nkv * (D / 2);
+  const float* kn_base = p.k_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
+  const float* vn_base = p.v_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
+
+  // ---- set-up ---------------------------------------------------------------------------
+  if (tid == 0) {
+    mbar_init(bar_raw, 1);
+    mbar_init(bar_raw + 1, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, kPfTmemCols);
+    tmem_relinquish();
+  }
+  for (int e = tid; e < 256; e += kPfThreads) {
+    const int hi = e >> 4, lo = e & 15;
+    lut_k[e] = pack_half2(hi < p.nck ? p.cent_k[hi] : 0.f, lo < p.nck ? p.cent_k[lo] : 0.f);
+    lut_v[e] = pack_half2(hi < p.ncv ? p.cent_v[hi] : 0.f, lo < p.ncv ? p.cent_v[lo] : 0.f);
+  }
+  // Q tile -> [k-chunk][row][16 B]
+  {
+    const __half* qsrc = p.q_rot + ((int64_t(b) * p.hq + hq) * p.nq + m0) * D;
+    for (int i = tid; i < kPfM * int(S::kChunks); i += kPfThreads) {
+      const int row = i / int(S::kChunks), kc = i % int(S::kChunks);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < rows) v = *reinterpret_cast<const uint4*>(qsrc + int64_t(row) * D + kc * 8);
+      *reinterpret_cast<uint4*>(smem + S::kOffQ + kc * S::kSlabQ + row * 16) = v;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;        // 64 columns
+  const uint32_t tmem_o = tmem_base + 64;   // D columns
+  const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+
+  auto issue_raw = [&](int tile, int buf) {  // thread 0 only
+    const int t0 = tile * kPfN;
+    const int n_tok = kv_end - t0 < kPfN ? kv_end - t0 : kPfN;
+    const uint32_t bytes = uint32_t(n_tok) * (D / 2);
+    mbar_expect_tx(bar_raw + buf, 2 * bytes);
+    bulk_g2s(smem + S::kOffRaw + (2 * buf) * S::kRawTile, kc_base + int64_t(t0) * (D / 2), bytes,
+             bar_raw + buf);
+    bulk_g2s(smem + S::kOffRaw + (2 * buf + 1) * S::kRawTile, vc_base + int64_t(t0) * (D / 2),
+             bytes, bar_raw + buf);
+  };
+  if (tid == 0 && n_tiles > 0) issue_raw(0, 0);
+
+  float o_acc[D];
+#pragma unroll
+  for (int c = 0; c < D; ++c) o_acc[c] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const int q_pos = m0 + tid;
+  bool dead = false;
+
+  for (int tile = 0; tile < n_tiles && !dead; ++tile) {
+    const int buf = tile & 1;
+    const int t0 = tile * kPfN;
+    const int n_tok = kv_end - t0 < kPfN ? kv_end - t0 : kPfN;
+    // ---- norms of the tile --------------------------------------------------------------
+    if (tid < kPfN) {
+      float nk = 0.f, nv = 0.f;
+      if (tid < n_tok) { nk = kn_base[t0 + tid]; nv = vn_base[t0 + tid]; }
+      const float lg = fast_log2(nv);
+      nk_s[tid] = nk * p.scale_log2;
+      lg_s[tid] = lg;
+      lv_s[tid] = fmaxf(lg, -40.f);
+    }
+    // ---- codes -> fp16 operands ------------------------------------------------------------
+    if (!mbar_wait(bar_raw + buf, (tile >> 1) & 1)) { dead = true; }
+    if (!dead) {
+      const uint32_t* rk = reinterpret_cast<const uint32_t*>(smem + S::kOffRaw + (2 * buf) * S::kRawTile);
+      const uint32_t* rv = reinterpret_cast<const uint32_t*>(smem + S::kOffRaw + (2 * buf + 1) * S::kRawTile);
+      constexpr int kWords = kPfN * (D / 8);  // 4 code bytes = 8 values = one 16-byte chunk
+      for (int i = tid; i < kWords; i += kPfThreads) {
+        const int tok = i / int(S::kChunks), kc = i % int(S::kChunks);
+        uint32_t wk = 0, wv = 0;
+        if (tok < n_tok) { wk = rk[i]; wv = rv[i]; }
+        uint4 ko, vo;
+        ko.x = lut_k[wk & 0xff]; ko.y = lut_k[(wk >> 8) & 0xff];
+        ko.z = lut_k[(wk >> 16) & 0xff]; ko.w = lut_k[wk >> 24];
+        vo.x = lut_v[wv & 0xff]; vo.y = lut_v[(wv >> 8) & 0xff];
+        vo.z = lut_v[(wv >> 16) & 0xff]; vo.w = lut_v[wv >> 24];
+        *reinterpret_cast<uint4*>(smem + S::kOffK + kc * S::kSlabKV + tok * 16) = ko;
+        *reinterpret_cast<uint4*>(smem + S::kOffV + kc * S::kSlabKV + tok * 16) = vo;
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- S = Q K^T ----------------------------------------------------------------------------
+    if (tid == 0 && !dead) {
+      tc_fence_after();
+      if (tile + 1 < n_tiles) issue_raw(tile + 1, buf ^ 1);
+      const uint32_t qa = smem_u32(smem + S::kOffQ), ka = smem_u32(smem + S::kOffK);
+#pragma unroll
+      for (int s = 0; s < D / 16; ++s)
+        umma_f16(tmem_s, smem_desc(qa + 2 * s * S::kSlabQ, S::kSlabQ, 128),
+                 smem_desc(ka + 2 * s * S::kSlabKV, S::kSlabKV, 128), kIdescS, s > 0);
+      umma_commit(bar_s);
+    }
+    if (!mbar_wait(bar_s, tile & 1)) dead = true;
+    tc_fence_after();
+
+    // ---- online softmax on row `tid` ---------------------------------------------------------
+    // pass 1: row maximum of logit*log2e + clamped log2|v| over the tile
+    float mx = -INFINITY;
+    if (!dead) {
+#pragma unroll
+      for (int c0 = 0; c0 < kPfN; c0 += 32) {
+        float s[32];
+        tmem_ld32(tmem_s + lane_sel + c0, s);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c0 + j;
+          const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+          const float e = s[j] * nk_s[col] + lv_s[col];
+          mx = fmaxf(mx, ok ? e : -INFINITY);
+        }
+      }
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float mref = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mref);
+    m_run = m_new;
+    l_run *= alpha;
+    // pass 2: weights -> fp16 A operand of the second product, [token chunk][row][16 B]
+    if (!dead) {
+#pragma unroll
+      for (int c0 = 0; c0 < kPfN; c0 += 32) {
+        float s[32];
+        tmem_ld32(tmem_s + lane_sel + c0, s);
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float w2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c0 + j + u;
+            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+            const float sv = s[j + u] * nk_s[col];
+            w2[u] = ok ? fast_exp2(sv + lg_s[col] - mref + kPfPScaleLog2) : 0.f;
+            l_run += ok ? fast_exp2(sv - mref) : 0.f;
+          }
+          packed[j / 2] = pack_half2(w2[0], w2[1]);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+          *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + tid * 16) =
+              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- O_tile = P V ---------------------------------------------------------------------------
+    if (tid == 0 && !dead) {
+      tc_fence_after();
+      const uint32_t pa = smem_u32(smem + S::kOffP), va = smem_u32(smem + S::kOffV);
+#pragma unroll
+      for (int s = 0; s < kPfN / 16; ++s)
+        umma_f16(tmem_o, smem_desc(pa + 2 * s * S::kSlabP, S::kSlabP, 128),
+                 smem_desc(va + s * 256, 128, S::kSlabKV), kIdescO, s > 0);
+      umma_commit(bar_o);
+    }
+    if (!mbar_wait(bar_o, tile & 1)) dead = true;
+    tc_fence_after();
+    if (!dead) {
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_sel + c0, o);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o_acc[c0 + j] = fmaf(o_acc[c0 + j], alpha, o[j]);
+      }
+    }
+    tc_fence_before();
+  }
+
+  // ---- epilogue: normalise, round, store the rotated-space row -----------------------------
+  if (dead && tid == 0 && p.status) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+  if (tid < rows) {
+    const float inv = l_run > 0.f ? 1.f / (l_run * 16384.f) : 0.f;  // 2^-kPfPScaleLog2
+    float* dst = p.o_rot + ((int64_t(b) * p.hq + hq) * p.nq + q_pos) * D;
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 4)
+      *reinterpret_cast<float4*>(dst + c0) = make_float4(
+          o_acc[c0] * inv, o_acc[c0 + 1] * inv, o_acc[c0 + 2] * inv, o_acc[c0 + 3] * inv);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kPfTmemCols);
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+template <int D>
+static int launch_prefill_t(const PrefillArgs& a, cudaStream_t stream) {
+  using S = PrefillSmem<D>;
+  auto kern = prefill_attention_kernel<D>;
+  static thread_local int set_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (set_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::kBytes));
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "prefill: shared memory opt-in of %u bytes refused: %s", S::kBytes,
+                  cudaGetErrorString(e));
+    set_dev = dev;
+  }
+  dim3 grid((a.nq + kPfM - 1) / kPfM, a.hq, a.batch);
+  kern<<<grid, kPfThreads, S::kBytes, stream>>>(a);
+  return check_launch("prefill attention kernel launch");
+}
+
+struct PrefillWorkspace {
+  size_t q_rot_off, o_rot_off, total;
+};
+static PrefillWorkspace prefill_workspace(int64_t rows, int d) {
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  PrefillWorkspace w;
+  w.q_rot_off = 256;
+  w.o_rot_off = up(w.q_rot_off + size_t(rows) * d * 2);
+  w.total = up(w.o_rot_off + size_t(rows) * d * 4);
+  return w;
+}
+
+}  // namespace fq
+
+using namespace fq;
+
+extern "C" size_t fq_fused_tq_attention_workspace_bytes(int batch, int num_q_heads, int n_q,
+                                                        int head_dim) {
+  if (batch < 0 || num_q_heads < 0 || n_q < 0 || head_dim < 0) return 0;
+  return prefill_workspace(int64_t(batch) * num_q_heads * n_q, head_dim).total;
+}
+
+extern "C" int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                                     const float* k_norms, const uint8_t* v_packed,
+                                     const float* v_norms, const float* centroids_k,
+                                     int n_centroids_k, const float* centroids_v,
+                                     int n_centroids_v, const float* rotation, int batch,
+                                     int num_q_heads, int num_kv_heads, int n_q, int n_kv,
+                                     int head_dim, float sm_scale, int is_causal, void* out,
+                                     void* workspace, size_t workspace_bytes,
+                                     fq_stream_t stream) {
+  FQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && num_kv_heads >= 1 && n_q >= 0 && n_kv >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "fused attention: negative size");
+  FQ_REQUIRE(q && k_packed && k_norms && v_packed && v_norms && centroids_k && centroids_v &&
+                 rotation && out,
+             FQ_ERR_INVALID_ARGUMENT, "fused attention: null pointer");
+  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
+             "fused attention: q must be fp16 or bf16");
+  FQ_REQUIRE(head_dim == 128, FQ_ERR_UNSUPPORTED,
+             "fused attention: head_dim %d (the tensor-core kernel is built for 128)", head_dim);
+  FQ_REQUIRE(num_q_heads % num_kv_heads == 0, FQ_ERR_INVALID_ARGUMENT,
+             "fused attention: q heads not a multiple of KV heads");
+  FQ_REQUIRE(n_centroids_k >= 1 && n_centroids_k <= 16 && n_centroids_v >= 1 &&
+                 n_centroids_v <= 16,
+             FQ_ERR_INVALID_ARGUMENT, "centroid count outside [1, 16]");
+  FQ_REQUIRE(!is_causal || n_q == n_kv || n_q == 1, FQ_ERR_UNSUPPORTED,
+             "fused attention: the causal mask is aligned at the first token (n_q == n_kv)");
+  FQ_REQUIRE(aligned(q, 16) && aligned(out, 16) && aligned(k_packed, 16) && aligned(v_packed, 16),
+             FQ_ERR_ALIGNMENT, "fused attention: q, out and the packed codes must be 16-byte aligned");
+  const int64_t rows = int64_t(batch) * num_q_heads * n_q;
+  if (rows == 0) return FQ_OK;
+  FQ_REQUIRE(n_kv >= 1, FQ_ERR_INVALID_ARGUMENT, "fused attention: no keys");
+  const PrefillWorkspace w = prefill_workspace(rows, head_dim);
+  FQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
+             "fused attention: workspace of %zu bytes needed (256-byte aligned)", w.total);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  __half* q_rot = reinterpret_cast<__half*>(ws + w.q_rot_off);
+  float* o_rot = reinterpret_cast<float*>(ws + w.o_rot_off);
+  int rc = rotate_q_to_half(q, dtype, rotation, q_rot, rows, head_dim, stream);
+  if (rc != FQ_OK) return rc;
+  PrefillArgs a{};
+  a.q_rot = q_rot;
+  a.k_packed = k_packed; a.k_norms = k_norms;
+  a.v_packed = v_packed; a.v_norms = v_norms;
+  a.cent_k = centroids_k; a.nck = n_centroids_k;
+  a.cent_v = centroids_v; a.ncv = n_centroids_v;
+  a.o_rot = o_rot;
+  a.batch = batch; a.hq = num_q_heads; a.hkv = num_kv_heads; a.nq = n_q; a.nkv = n_kv;
+  a.scale_log2 = sm_scale * 1.4426950408889634f;
+  a.causal = (is_causal && n_q > 1) ? 1 : 0;  // a single query token never needs the mask
+  a.status = reinterpret_cast<uint32_t*>(ws);
+  rc = launch_prefill_t<128>(a, stream);
+  if (rc != FQ_OK) return rc;
+  return rotate_back(o_rot, dtype, rotation, out, rows, head_dim, stream);
+}

@@ -337,3 +337,62 @@ def split_k_merge(partials: torch.Tensor, rotation: torch.Tensor, dtype: torch.d
     N.check(lib.fq_split_k_merge(N.ptr(partials), ng, N.ptr(rot), num_seqs, hq, d, N.ptr(out),
                                  N.dtype_code(dtype), N.stream_ptr(dev)))
     return out
+
+
+# --------------------------------------------------------------------------------------
+# fused TQ4 attention (prefill)
+# --------------------------------------------------------------------------------------
+
+_attn_workspaces = {}
+
+
+def fused_tq_attention(
+    q: torch.Tensor,
+    k_packed: torch.Tensor,
+    k_norms: torch.Tensor,
+    v_packed: torch.Tensor,
+    v_norms: torch.Tensor,
+    centroids_k: torch.Tensor,
+    centroids_v: torch.Tensor,
+    rotation: torch.Tensor,
+    sm_scale: Optional[float] = None,
+    is_causal: bool = False,
+) -> torch.Tensor:
+    """Attention over contiguous compressed K and V; un-rotated ``q`` in, original space out.
+
+    Same contract as the reference's ``fused_tq_attention``
+    (src/flashquant/kernels/attention.py:53-107): ``q (B, H_Q, N_Q, D)``, packed codes
+    ``(B, H_KV, N_KV, D/2)``, norms ``(B, H_KV, N_KV, 1)``.
+    """
+    N.require_cuda(q, k_packed, k_norms, v_packed, v_norms)
+    b, hq, nq, d = q.shape
+    _, hkv, nkv, half = k_packed.shape
+    if half * 2 != d or v_packed.shape != k_packed.shape:
+        raise ValueError("packed K/V must be (B, H_KV, N_KV, D/2)")
+    dev = q.device
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    q = _contig(q)
+    kp, vp = _contig(k_packed), _contig(v_packed)
+    kn = _contig(k_norms.reshape(b, hkv, nkv).float())
+    vn = _contig(v_norms.reshape(b, hkv, nkv).float())
+    ck, cv, rot = _f32(centroids_k, dev), _f32(centroids_v, dev), _f32(rotation, dev)
+    out = torch.empty_like(q)
+    lib = N.load()
+    need = lib.fq_fused_tq_attention_workspace_bytes(b, hq, nq, d)
+    key = (dev.type, dev.index)
+    ws = _attn_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+        _attn_workspaces[key] = ws
+    N.check(lib.fq_fused_tq_attention(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(kp), N.ptr(kn), N.ptr(vp), N.ptr(vn), N.ptr(ck),
+        ck.numel(), N.ptr(cv), cv.numel(), N.ptr(rot), b, hq, hkv, nq, nkv, d, float(sm_scale),
+        int(bool(is_causal)), N.ptr(out), N.ptr(ws), ws.numel(), N.stream_ptr(dev)))
+    return out
+
+
+def attention_workspace_status(device) -> int:
+    """Device status word of the cached attention workspace (0 = no error)."""
+    ws = _attn_workspaces.get((device.type, device.index))
+    return 0 if ws is None else workspace_status(ws)

@@ -222,6 +222,30 @@ int fq_split_k_merge(const float* partials, int n_groups, const float* rotation,
                      int num_seqs, int num_q_heads, int head_dim, void* out, fq_dtype dtype,
                      fq_stream_t stream);
 
+/*
+ * Fused TQ4 attention over contiguous (non-paged) compressed K and V, causal or not.
+ * Replaces fused_tq_attention_cuda (csrc/cuda/fused_tq_attention.cu:468-511) as reached from
+ * flashquant.kernels.attention.fused_tq_attention (src/flashquant/kernels/attention.py:91-97);
+ * arithmetic of the CPU branch (attention.py:99-107 +
+ * src/flashquant/kernels/cpu_reference.py:154-227): q_rot = round(q Pi^T), K = c_k[code] n_k,
+ * V = c_v[code] n_v, softmax(sm_scale q_rot K^T [causal: key j > query i masked]) V in fp32,
+ * out = round(o_rot Pi).
+ *   q, out              (batch, num_q_heads, n_q, head_dim), FQ_F16 or FQ_BF16, 16-byte aligned
+ *   k_packed, v_packed  (batch, num_kv_heads, n_kv, head_dim/2) bytes, 16-byte aligned
+ *   k_norms, v_norms    (batch, num_kv_heads, n_kv) fp32
+ *   workspace           caller-owned, 256-byte aligned, fq_fused_tq_attention_workspace_bytes(...)
+ *                       bytes (rotated fp16 query and fp32 rotated output); first word = status
+ * head_dim 128; with is_causal, n_q must equal n_kv (or be 1).
+ */
+size_t fq_fused_tq_attention_workspace_bytes(int batch, int num_q_heads, int n_q, int head_dim);
+int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                          const float* k_norms, const uint8_t* v_packed, const float* v_norms,
+                          const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                          int n_centroids_v, const float* rotation, int batch, int num_q_heads,
+                          int num_kv_heads, int n_q, int n_kv, int head_dim, float sm_scale,
+                          int is_causal, void* out, void* workspace, size_t workspace_bytes,
+                          fq_stream_t stream);
+
 /* Copies the device status word of a decode workspace to *status (synchronises stream). */
 int fq_workspace_status(const void* workspace, uint32_t* status, fq_stream_t stream);
 

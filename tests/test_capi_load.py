@@ -60,3 +60,19 @@ def test_package_refuses_cpu_tensors(lib_path):
     from flashquant_b200._native import FlashQuantNativeError
     with pytest.raises(FlashQuantNativeError):
         fq.tq4_compress(torch.randn(2, 1, 128), torch.eye(128), torch.zeros(15))
+
+
+def test_pybind_module_exports_the_probed_names():
+    """The reference's Python layer looks for these attributes on ``flashquant._C``."""
+    from flashquant_b200 import build
+    build.build_pybind()
+    import torch  # noqa: F401  (the module links against libtorch)
+    from flashquant_b200 import _C
+    for name in ["tq4_compress", "tq4_decompress", "fused_tq_attention", "split_k_paged_decode",
+                 "fused_paged_tq4_decode"]:
+        assert hasattr(_C, name)
+    assert not hasattr(_C, "codebook")  # would hijack the reference's Lloyd-Max solver
+    import pytest
+    with pytest.raises(RuntimeError):
+        _C.tq4_compress(torch.randn(2, 1, 128), torch.zeros(128, 64), torch.zeros(128, 64),
+                        torch.zeros(15), None)

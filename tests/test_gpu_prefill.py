@@ -1,0 +1,96 @@
+"""GPU parity of the fused TQ4 prefill attention (tcgen05 kernel) against the oracle.
+
+Bar: outputs within 2e-3 max-abs of the reference's decompress-then-attend path (see
+parity.attention_close for rows whose entries are of order 1).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import flashquant_b200 as fq
+from conftest import bf16_from_bits, load_golden
+from flashquant_b200 import kernels as K
+from flashquant_b200 import workloads as W
+from oracle import tq_oracle as O
+from parity import attention_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def make_case(consts, b, hq, hkv, n, seed, dtype=torch.bfloat16, k_bits=3, v_bits=4):
+    d = 128
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, hq, n, d, generator=g).to(dtype)
+    k = torch.randn(b * hkv, n, d, generator=g)
+    k[..., W.outlier_channels(d)] *= 10.0
+    v = torch.randn(b * hkv, n, d, generator=g)
+    rot = consts["rotation_128_0"]
+    kp, kn = O.compress(k.to(dtype), rot, consts[f"boundaries_128_{k_bits}"])
+    vp, vn = O.compress(v.to(dtype), rot, consts[f"boundaries_128_{v_bits}"])
+    shape4 = lambda t, last: t.reshape(b, hkv, n, last)
+    return (q, shape4(kp, d // 2), shape4(kn, 1), shape4(vp, d // 2), shape4(vn, 1),
+            consts[f"centroids_128_{k_bits}"], consts[f"centroids_128_{v_bits}"], rot)
+
+
+def run_gpu(case, **kw):
+    q, kp, kn, vp, vn, ck, cv, rot = case
+    out = K.fused_tq_attention(q.to(DEV), kp.to(DEV), kn.to(DEV), vp.to(DEV), vn.to(DEV), ck, cv,
+                               rot, **kw)
+    assert K.attention_workspace_status(torch.device(DEV)) == 0
+    return out
+
+
+def test_golden_fixture(consts):
+    z = load_golden("prefill.npz")
+    case = (bf16_from_bits(z["q_bf16"]), T(z["k_packed"]), T(z["k_norms"]), T(z["v_packed"]),
+            T(z["v_norms"]), consts["centroids_128_3"], consts["centroids_128_4"],
+            consts["rotation_128_0"])
+    attention_close(run_gpu(case, is_causal=True), bf16_from_bits(z["out_causal_bf16"]))
+    attention_close(run_gpu(case, is_causal=False), bf16_from_bits(z["out_full_bf16"]))
+
+
+@pytest.mark.parametrize("b,hq,hkv,n", [(1, 4, 1, 64), (2, 8, 2, 128), (1, 4, 4, 129),
+                                        (1, 2, 1, 1), (1, 8, 2, 333), (1, 4, 2, 640)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_vs_oracle(consts, b, hq, hkv, n, causal):
+    case = make_case(consts, b, hq, hkv, n, seed=100 + n)
+    ref = O.fused_tq_attention(*case, is_causal=causal)
+    attention_close(run_gpu(case, is_causal=causal), ref)
+
+
+def test_fp16_scale_and_4bit_keys(consts):
+    case = make_case(consts, 1, 4, 2, 200, seed=7, dtype=torch.float16, k_bits=4)
+    ref = O.fused_tq_attention(*case, sm_scale=0.07, is_causal=True)
+    attention_close(run_gpu(case, sm_scale=0.07, is_causal=True), ref)
+
+
+def test_causal_first_row_sees_only_first_key(consts):
+    # size-independent property: row 0 of a causal call equals V[0] (rotated back)
+    case = make_case(consts, 1, 4, 2, 300, seed=9)
+    out = run_gpu(case, is_causal=True).float().cpu()
+    q, kp, kn, vp, vn, ck, cv, rot = case
+    v0 = O.decompress(vp[0, :, :1].reshape(2, 1, 64), vn[0, :, :1].reshape(2, 1, 1), cv)  # (2,1,128)
+    want = (v0.reshape(2, 128) @ rot).to(torch.bfloat16).float().repeat_interleave(2, dim=0)
+    attention_close(out[0, :, 0], want)
+
+
+def test_longer_sequence_chunked_oracle(consts):
+    case = make_case(consts, 1, 8, 2, 2048, seed=11)
+    ref = O.fused_tq_attention(*case, is_causal=True, q_chunk=256)
+    attention_close(run_gpu(case, is_causal=True), ref)
+
+
+def test_argument_errors(consts):
+    from flashquant_b200._native import FlashQuantNativeError
+    case = make_case(consts, 1, 4, 2, 64, seed=3)
+    q, kp, kn, vp, vn, ck, cv, rot = case
+    with pytest.raises(FlashQuantNativeError) as e:  # causal mask needs n_q == n_kv
+        K.fused_tq_attention(q[:, :, :32].to(DEV), kp.to(DEV), kn.to(DEV), vp.to(DEV), vn.to(DEV),
+                             ck, cv, rot, is_causal=True)
+    assert e.value.code == -2
