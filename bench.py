@@ -378,6 +378,104 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------------------
+# secondary workloads (one GPU): the other rows of the hot path, for their own profiles
+# --------------------------------------------------------------------------------------
+def _time_loop(fn, steps, warmup):
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / steps
+
+
+def run_prefill(args):
+    """configs[3]: fused causal TQ4 prefill, batch 4 x 8192 tokens, 32 q / 8 kv heads."""
+    import flashquant_b200 as fq
+    from flashquant_b200 import kernels as K, workloads as W
+
+    dev = torch.device("cuda", 0)
+    b, n = args.prefill_batch, args.prefill_seq
+    q3, q4 = fq.TurboQuantProd(D, 4, seed=0), fq.TurboQuantMSE(D, 4, seed=0)
+    rot = q4.rotation.to(dev)
+    bk, ck = q3.mse_quantizer.boundaries.to(dev), q3.mse_quantizer.centroids.to(dev)
+    bv, cv = q4.boundaries.to(dev), q4.centroids.to(dev)
+    k, v = W.make_kv(b * n, HKV, D, cfg=3)
+    # (tokens, H, D) -> (B, H, N, D), compressed with the CUDA kernel
+    kp, kn = K.tq4_compress(k.to(dev).reshape(b, n, HKV, D).transpose(1, 2).reshape(-1, 1, D), rot, bk)
+    vp, vn = K.tq4_compress(v.to(dev).reshape(b, n, HKV, D).transpose(1, 2).reshape(-1, 1, D), rot, bv)
+    kp, vp = kp.reshape(b, HKV, n, D // 2), vp.reshape(b, HKV, n, D // 2)
+    kn, vn = kn.reshape(b, HKV, n, 1), vn.reshape(b, HKV, n, 1)
+    q = torch.randn(b, HQ, n, D, generator=torch.Generator().manual_seed(3003)).to(torch.bfloat16).to(dev)
+    ms = _time_loop(lambda: K.fused_tq_attention(q, kp, kn, vp, vn, ck, cv, rot, is_causal=True),
+                    args.steps, args.warmup)
+    flops = 4.0 * b * HQ * n * n * D / 2
+    peaks = _peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    print(json.dumps({
+        "metric": "tq4_fused_prefill_tflops", "value": tf, "unit": "TFLOP/s (causal half counted)",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "fp16 tcgen05 operands, fp32 accumulate, bf16 in/out",
+        "data": "synthetic",
+        "config": {"workload": f"configs[3]: fused causal TQ4 prefill, batch {b}, seq {n}, "
+                               "32 q / 8 kv heads, head_dim 128; the call includes both rotations"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+                     "frac": tf / peak, "traffic": None,
+                     "peak_source": "measured sustained (MEASURED_PEAKS.json)" if peaks else "fallback"},
+    }), flush=True)
+
+
+def run_append(args):
+    """configs[2]: compress-on-append, 8192 bf16 tokens x 8 heads into a 65536-slot cache."""
+    import flashquant_b200 as fq
+    from flashquant_b200 import kernels as K, workloads as W
+
+    dev = torch.device("cuda", 0)
+    q3, q4 = fq.TurboQuantProd(D, 4, seed=0), fq.TurboQuantMSE(D, 4, seed=0)
+    rot, S = q4.rotation.to(dev), q3.qjl_matrix.to(dev)
+    bk, ck = q3.mse_quantizer.boundaries.to(dev), q3.mse_quantizer.centroids.to(dev)
+    bv = q4.boundaries.to(dev)
+    w = W.append_workload()
+    key, val, slots = w.key.to(dev), w.value.to(dev), w.slot_mapping.to(dev)
+    nb = w.num_slots // w.block_size
+    cache = torch.zeros(nb, BS, HKV * (D + 8), dtype=torch.uint8, device=dev)
+    plane = torch.zeros(nb, BS, HKV * (D // 8 + 4), dtype=torch.uint8, device=dev)
+    ms_qjl = _time_loop(lambda: K.tq4_compress_append_qjl(key, val, cache, plane, slots, rot, bk, ck,
+                                                          bv, S), args.steps, args.warmup)
+    ms_mse = _time_loop(lambda: K.tq4_compress_append(key, val, cache, slots, rot, bk, bv),
+                        args.steps, args.warmup)
+    peaks = _peaks()
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    alg = w.algorithmic_bytes(with_qjl=True)
+    gbs = alg / (ms_qjl * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "tq4_compress_append_tokens_per_s", "value": 8192 / (ms_qjl * 1e-3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_qjl, "ms_per_step_without_qjl": ms_mse, "higher_is_better": True,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[2]: 8192 bf16 tokens x 8 kv heads, K two-stage (3-bit + "
+                               "QJL signs + gamma), V 4-bit, seed-3 slot mapping into 65536 slots"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "algorithmic_bytes": alg, "traffic": None,
+                     "note": "fp32 FMA rotations: 4 x 65536 x 128^2 multiply-adds are the "
+                             "binding resource, not HBM",
+                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback"},
+    }), flush=True)
+
+
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -385,6 +483,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["decode", "prefill", "append"], default="decode",
+                    help="decode is the headline; the others time further rows on one GPU")
+    ap.add_argument("--prefill-batch", type=int, default=4)
+    ap.add_argument("--prefill-seq", type=int, default=8192)
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the streaming kernel from an ncu capture")
     args = ap.parse_args()
@@ -392,6 +494,10 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
+    elif args.workload == "append":
+        run_append(args)
     else:
         run_ours(args)
 

@@ -37,4 +37,5 @@ def bf16_from_bits(a):
 @pytest.fixture(scope="session")
 def consts():
     z = load_golden("constants.npz")
-    return {k: torch.from_numpy(v) for k, v in z.items()}
+    # QR hands back column-major factors; make every constant row-major once
+    return {k: torch.from_numpy(np.ascontiguousarray(v)).contiguous() for k, v in z.items()}
