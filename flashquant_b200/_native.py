@@ -45,6 +45,9 @@ SIGNATURES = {
     "fq_paged_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fq_split_k_paged_decode": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i, _i,
                                      _i, _i, _i64, _f, _p, _i, _p, _sz, _p]),
+    "fq_split_k_paged_decode_static_max_bytes": (_sz, []),
+    "fq_split_k_paged_decode_static": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i,
+                                            _i, _i, _i, _i64, _f, _p, _i, _p]),
     "fq_paged_decode_partials": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i, _i,
                                       _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_partials_rotated": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i,

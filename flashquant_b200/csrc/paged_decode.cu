@@ -26,6 +26,7 @@
 // full/empty mbarriers; every wait is bounded and reports through the status word instead
 // of spinning forever.
 #include <cstdlib>
+#include <mutex>
 
 #include "fq_common.cuh"
 
@@ -1188,4 +1189,89 @@ extern "C" int fq_workspace_status(const void* workspace, uint32_t* status, fq_s
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_workspace_status: %s", cudaGetErrorString(e));
   return FQ_OK;
+}
+
+// ------------------------------------------------------------------------------------
+// Decode without any allocation by the caller or by this library
+// ------------------------------------------------------------------------------------
+// Some callers cannot obtain device memory at the moment they need to decode: a serving
+// engine that has handed its whole memory budget to the KV cache and refuses further
+// cudaMalloc calls, a plugin that runs inside another framework's memory pool, or code on a
+// path where an allocation would synchronise the device.  For them the scratch that
+// fq_split_k_paged_decode takes as `workspace` lives in the array below, which is part of
+// the library image: every GPU that loads the library holds these 16 MiB until the process
+// exits.  All calls on a device share the array, so two calls that overlap on the GPU (two
+// streams, or two host threads) race on it; the status word at its start is cleared by
+// every call.
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of g_decode_scratch on the current device.  The array's name is only a
+// host-side handle; the address a kernel can use has to be asked for, once per device, with
+// that device current.
+int static_scratch(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fq::fail(FQ_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fq::fail(FQ_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || !p)
+      return fq::fail(FQ_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s",
+                      cudaGetErrorString(e));
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return FQ_OK;
+}
+}  // namespace
+
+extern "C" size_t fq_split_k_paged_decode_static_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int fq_split_k_paged_decode_static(
+    const void* q, fq_dtype dtype, const uint8_t* kv_cache, const int32_t* block_table,
+    int64_t block_table_stride, const int32_t* seq_lens, const float* centroids_k,
+    int n_centroids_k, const float* centroids_v, int n_centroids_v, const float* rotation,
+    int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+    int64_t num_blocks, float sm_scale, void* out, int num_splits, fq_stream_t stream) {
+  int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
+                           centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                           num_kv_heads, head_dim, block_size, num_blocks, num_splits);
+  if (rc != FQ_OK) return rc;
+  FQ_REQUIRE(out, FQ_ERR_INVALID_ARGUMENT, "paged decode: out is null");
+  if (num_seqs == 0) return FQ_OK;
+  const int ctas = device_sm_count();
+  if (num_splits == 0) num_splits = auto_splits();
+  const size_t need =
+      workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, ctas * (kCW / num_kv_heads))
+          .total;
+  FQ_REQUIRE(need <= kStaticScratchBytes, FQ_ERR_WORKSPACE,
+             "fq_split_k_paged_decode_static: this shape needs %zu bytes of scratch, the built-in "
+             "array holds %zu; use fq_split_k_paged_decode with a caller-owned workspace",
+             need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  rc = static_scratch(&scratch);
+  if (rc != FQ_OK) return rc;
+  // the array keeps what the previous call left: the status word must start at zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 256, stream);
+  if (e != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "clearing the scratch status word: %s", cudaGetErrorString(e));
+  rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                    num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits, scratch,
+                    kStaticScratchBytes, ctas, stream);
+  if (rc != FQ_OK) return rc;
+  MergeArgs m = slot_merge_args(scratch, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                num_splits, ctas, seq_lens, block_size);
+  m.rotation = rotation;
+  m.out = out;
+  return launch_merge<true, true>(m, head_dim, dtype, stream);
 }

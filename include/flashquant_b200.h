@@ -166,6 +166,28 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
                             void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
 /*
+ * fq_split_k_paged_decode for callers that cannot allocate.  (No counterpart in the
+ * reference.)  Same arguments and result as fq_split_k_paged_decode, minus the workspace:
+ * the scratch is a 16 MiB array built into the library, so nothing is allocated by the
+ * caller or by the call - meant for a serving engine that has given all device memory to
+ * the KV cache, or for code inside another framework's memory pool.
+ *   - shapes whose scratch exceeds fq_split_k_paged_decode_static_max_bytes() are refused
+ *     with FQ_ERR_WORKSPACE (the message names the size needed);
+ *   - the first call on each device looks up the array's device address; make that first
+ *     call outside any stream capture;
+ *   - all calls on a device share the array: calls that overlap on the GPU race on it.
+ */
+size_t fq_split_k_paged_decode_static_max_bytes(void);
+int fq_split_k_paged_decode_static(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                                   const int32_t* block_table, int64_t block_table_stride,
+                                   const int32_t* seq_lens, const float* centroids_k,
+                                   int n_centroids_k, const float* centroids_v,
+                                   int n_centroids_v, const float* rotation, int num_seqs,
+                                   int num_q_heads, int num_kv_heads, int head_dim,
+                                   int block_size, int64_t num_blocks, float sm_scale, void* out,
+                                   int num_splits, fq_stream_t stream);
+
+/*
  * The two halves of the call above, for a sequence whose tokens are spread over several
  * GPUs: each GPU produces one partial row per (sequence, query head) over the pages it
  * holds, the rows are exchanged (one all-gather) and every GPU merges all of them.
