@@ -648,7 +648,8 @@ struct MergeArgs {
 };
 
 constexpr int kMergeHeads = 8;
-constexpr int kMaxParts = 256;
+constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams + splits)
+constexpr int kPartChunk = 128;  // rows merged per pass
 
 template <int D, typename T, bool kFromSlots, bool kFinal>
 __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs p) {
@@ -657,10 +658,10 @@ __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs 
   extern __shared__ __align__(16) unsigned char msm[];
   float* pi_s = reinterpret_cast<float*>(msm);                  // [k][j] (kFinal only)
   float* o_s = pi_s + (kFinal ? D * D : 0);                     // [8][D]
-  float* w_s = o_s + kMergeHeads * D;                           // [parts][8]: m, then weight
-  float* l_s = w_s + kMaxParts * kMergeHeads;                   // [parts][8]
-  float* den_s = l_s + kMaxParts * kMergeHeads;                 // [8] den, [8] m*
-  int* part_row = reinterpret_cast<int*>(den_s + 2 * kMergeHeads);  // [parts]
+  float* w_s = o_s + kMergeHeads * D;                           // [chunk][8]: m, then weight
+  float* l_s = w_s + kPartChunk * kMergeHeads;                  // [chunk][8]
+  float* den_s = l_s + kPartChunk * kMergeHeads;                // [8] den, [8] m*, [8] alpha
+  int* part_row = reinterpret_cast<int*>(den_s + 3 * kMergeHeads);  // [parts]
   int* prefix = part_row + kMaxParts;                           // [num_seqs + 1]
   __shared__ uint64_t pi_bar;
   __shared__ int n_parts_s;
@@ -712,48 +713,60 @@ __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs 
   // (group, sequence))
   auto row_ptr = [&](int i, int h) { return p.rows + (int64_t(part_row[i]) * p.hq + h) * ROWF; };
 
-  // ---- m and l of every (part, head), then the weights ------------------------------------
-  for (int i = tid; i < n_parts * kMergeHeads; i += NT) {
-    const int part = i / kMergeHeads, hh = i % kMergeHeads;
-    float m = -INFINITY, l = 0.f;
-    if (h0 + hh < p.hq) {
-      const float2 ml = *reinterpret_cast<const float2*>(row_ptr(part, h0 + hh) + D);
-      m = ml.x;
-      l = ml.y;
-    }
-    w_s[i] = m;
-    l_s[i] = l;
-  }
-  __syncthreads();
-  if (tid < kMergeHeads) {
-    float m_star = -INFINITY;
-    for (int i = 0; i < n_parts; ++i) m_star = fmaxf(m_star, w_s[i * kMergeHeads + tid]);
-    float den = 0.f;
-    for (int i = 0; i < n_parts; ++i) {
-      const float m = w_s[i * kMergeHeads + tid];
-      const float w = (m == -INFINITY) ? 0.f : exp2f(m - m_star);
-      w_s[i * kMergeHeads + tid] = w;
-      den = fmaf(w, l_s[i * kMergeHeads + tid], den);
-    }
-    den_s[tid] = den;
-    den_s[kMergeHeads + tid] = m_star;
-  }
-  __syncthreads();
-
-  // ---- accumulate: thread (hh, d) ---------------------------------------------------------
+  // ---- online merge over chunks of partial rows; thread (hh, d) owns one output value ------
   const int d = tid % D, hh = tid / D;
   const bool head_ok = h0 + hh < p.hq;
   float num = 0.f;
-  if (head_ok) {
-    for (int i0 = 0; i0 < n_parts; i0 += 8) {
-      float v[8];
+  if (tid < kMergeHeads) {
+    den_s[tid] = 0.f;
+    den_s[kMergeHeads + tid] = -INFINITY;
+  }
+  for (int c0 = 0; c0 < n_parts; c0 += kPartChunk) {
+    const int nc = n_parts - c0 < kPartChunk ? n_parts - c0 : kPartChunk;
+    __syncthreads();  // previous chunk's weights are no longer read
+    for (int i = tid; i < nc * kMergeHeads; i += NT) {
+      const int part = c0 + i / kMergeHeads, h = i % kMergeHeads;
+      float m = -INFINITY, l = 0.f;
+      if (h0 + h < p.hq) {
+        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(part, h0 + h) + D);
+        m = ml.x;
+        l = ml.y;
+      }
+      w_s[i] = m;
+      l_s[i] = l;
+    }
+    __syncthreads();
+    if (tid < kMergeHeads) {
+      const float m_old = den_s[kMergeHeads + tid];
+      float m_new = m_old;
+      for (int i = 0; i < nc; ++i) m_new = fmaxf(m_new, w_s[i * kMergeHeads + tid]);
+      const float alpha = (m_old == -INFINITY) ? 0.f : exp2f(m_old - m_new);
+      float den = den_s[tid] * alpha;
+      for (int i = 0; i < nc; ++i) {
+        const float m = w_s[i * kMergeHeads + tid];
+        const float w = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        w_s[i * kMergeHeads + tid] = w;
+        den = fmaf(w, l_s[i * kMergeHeads + tid], den);
+      }
+      den_s[tid] = den;
+      den_s[kMergeHeads + tid] = m_new;
+      den_s[2 * kMergeHeads + tid] = alpha;
+    }
+    __syncthreads();
+    if (head_ok) {
+      num *= den_s[2 * kMergeHeads + hh];
+      for (int i0 = 0; i0 < nc; i0 += 8) {
+        float v[8];
 #pragma unroll
-      for (int x = 0; x < 8; ++x) v[x] = (i0 + x < n_parts) ? row_ptr(i0 + x, h0 + hh)[d] : 0.f;
+        for (int x = 0; x < 8; ++x)
+          v[x] = (i0 + x < nc) ? row_ptr(c0 + i0 + x, h0 + hh)[d] : 0.f;
 #pragma unroll
-      for (int x = 0; x < 8; ++x)
-        if (i0 + x < n_parts) num = fmaf(w_s[(i0 + x) * kMergeHeads + hh], v[x], num);
+        for (int x = 0; x < 8; ++x)
+          if (i0 + x < nc) num = fmaf(w_s[(i0 + x) * kMergeHeads + hh], v[x], num);
+      }
     }
   }
+  __syncthreads();
 
   if constexpr (!kFinal) {
     if (head_ok) {
@@ -912,7 +925,7 @@ static int rotate_q(const void* q, int dtype, const float* rotation, __half* out
 template <int D, typename T, bool kFromSlots, bool kFinal>
 static int launch_merge_t(const MergeArgs& m, cudaStream_t stream) {
   const size_t smem = (kFinal ? size_t(D) * D * 4 : 0) + kMergeHeads * D * 4 +
-                      2 * kMaxParts * kMergeHeads * 4 + 2 * kMergeHeads * 4 + kMaxParts * 4 +
+                      2 * kPartChunk * kMergeHeads * 4 + 3 * kMergeHeads * 4 + kMaxParts * 4 +
                       (kFromSlots ? size_t(m.num_seqs + 1) * 4 : 0) + 16;
   auto kern = merge_rotate_kernel<D, T, kFromSlots, kFinal>;
   static thread_local int set_dev = -1;

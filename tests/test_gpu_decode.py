@@ -226,3 +226,12 @@ def test_argument_errors(consts):
                                consts["rotation_128_0"], 8, 128, 16, num_splits=4,
                                workspace=torch.zeros(1024, dtype=torch.uint8, device=DEV))
     assert e.value.code == -3
+
+
+def test_long_sequence_spread_over_every_team(consts):
+    """One sequence of 20 000 tokens is cut into ~300 partial rows (one per team of warps)."""
+    w = W.decode_workload(seq_lens=[20000, 40], num_q_heads=8, num_kv_heads=2, cfg=21)
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    for splits in (0, 5):
+        attention_close(run_gpu(w, cache, consts, num_splits=splits), ref)
