@@ -170,6 +170,19 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
       : "memory");
 }
 
+// Orders this thread's earlier generic-proxy accesses (and those it has acquired from other
+// threads) before its later bulk copies, which go through the async proxy.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Counters in global memory that CTAs of one launch signal each other through.
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ------------------------------------------------------------------------------------
 // Warp-level MMA (fp16 operands, fp32 accumulate) and the 8x8 transpose.
 // Fragment layout, lane = 4*g + t:

@@ -1,32 +1,39 @@
 // Split-K paged decode over the packed TQ4 cache for sm_100a.
 //
-// Three launches per call:
-//   1. rotate_q_kernel      q_rot = round_to_q_dtype(q Pi^T), stored as fp16
-//   2. paged_decode_kernel  persistent, one CTA per SM: the pages of all sequences form one
-//                           flat list that is cut into equal runs, one per team of warps; a
-//                           run is processed as segments that never cross a boundary of
-//                           the caller's split partition, and every segment leaves one
-//                           (acc, m, l) partial row per query head
-//   3. merge_rotate_kernel  merges the partial rows of a sequence, rounds to the output type,
-//                           multiplies by Pi
+// fq_split_k_paged_decode is ONE cooperative launch of paged_decode_kernel, one CTA per SM:
+//   a. q rotation     every warp of the grid takes one 16x8 tile of q_rot = round(q Pi^T)
+//                     (bf16 tensor-core products of a three-way split of Pi, fp32 exact to
+//                     ~2^-24), stores it as fp16 and counts it in on the sequence's counter;
+//   b. streaming      the pages of all sequences form one flat list that is cut into equal
+//                     runs, one per team of warps; a run is processed as segments that never
+//                     cross a boundary of the caller's split partition, and every segment
+//                     leaves one (acc, m, l) partial row per query head and counts itself in
+//                     on the sequence's second counter;
+//   c. merge          when its teams are done a CTA takes (sequence, 8 heads) jobs: waits
+//                     until the sequence's segments are all in, merges their rows, rounds to
+//                     the output type and multiplies by Pi.
+// Waits across CTAs (b on a, c on b) are bounded and never circular; the cooperative launch
+// guarantees that all CTAs are resident.  The partial-row entry points run phase b alone
+// (rotate_q_kernel before it, merge_rotate_kernel after it, as separate launches).
 //
-// The streaming kernel is bound by HBM traffic (136 B per token and KV head) only if the
+// The streaming phase is bound by HBM traffic (136 B per token and KV head) only if the
 // per-byte instruction count stays near 3: a nibble code costs two table look-ups and, with
 // 4 query heads per KV head, eight multiply-adds per byte, which the fp32 pipe cannot
 // sustain at 7 TB/s.  So the multiply-adds go to the tensor pipe (mma.sync m16n8k16, the N
 // dimension being the query heads of the group) and a byte is turned into two fp16
 // centroids by ONE shared-memory look-up in a 256-entry table of fp16 pairs, replicated per
 // lane so that look-ups never conflict (with at most 8 key centroids the key side needs no
-// table at all: two byte permutes on a register-resident table do four look-ups).  Operand fragments are built directly in registers
-// in the order the look-ups deliver them; the k-dimension of the QK product and the row
-// dimension of the PV product are permuted accordingly (the query fragment and the
-// write-back apply the same permutation).
+// table at all: two byte permutes on a register-resident table do four look-ups).  Operand
+// fragments are built directly in registers in the order the look-ups deliver them; the
+// k-dimension of the QK product and the row dimension of the PV product are permuted
+// accordingly (the query fragment and the write-back apply the same permutation).
 //
 // Pages reach shared memory by 1-D bulk copies into per-team rings of stages guarded by
 // full/empty mbarriers; every wait is bounded and reports through the status word instead
 // of spinning forever.
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "fq_common.cuh"
 
@@ -40,6 +47,13 @@ constexpr int kMaxSeqs = 2048;                  // page-count prefix lives in sh
 constexpr int kMaxSplits = 64;
 constexpr int kPartPad = 4;                     // partial row = D + 4 floats (acc, m, l, 0, 0)
 constexpr float kPScaleLog2 = 14.f;             // fp16 weights are scaled by 2^14
+
+constexpr int kMergeHeads = 8;                  // query heads per merge job
+constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams + splits)
+constexpr int kPartChunk = 128;  // rows merged per pass
+// shared memory of a merge job of the single-launch form besides Pi: rounded rows, row list
+constexpr uint32_t kMergeScratchBytes =
+    (kMergeHeads * 128 + kMergeHeads * kDecodeThreads / 2 + 64 + kMaxParts + 4) * 4;
 
 enum : int { kSegStart = 1, kSegEnd = 2, kQNew = 4 };
 
@@ -60,7 +74,15 @@ struct DecodeArgs {
   int stages;
   float* slots;  // (num_seqs * S + workers, Hq, D+4), workers = gridDim.x * teams
   uint32_t* status;
-  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar;
+  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent;
+  // single-launch form only
+  const void* q_src;      // (num_seqs, Hq, D) in the caller's type
+  const float* rotation;  // (D, D)
+  void* out;              // (num_seqs, Hq, D) in the caller's type
+  __half* q_rot_w;        // where phase a writes what `q_rot` reads
+  uint32_t* q_count;      // [kMaxSeqs] rotated tiles of a sequence that are stored
+  uint32_t* seg_count;    // [kMaxSeqs] (segment, warp) pairs of a sequence that are stored
+  uint32_t* merge_count;  // [kMaxSeqs] merge jobs of a sequence that are finished
 };
 
 // ------------------------------------------------------------------------------------
@@ -150,6 +172,287 @@ __global__ void __launch_bounds__(256) rotate_q_kernel(const T* __restrict__ q,
   }
 }
 
+// The same rotation for one 16-row x 8-column tile, by one warp on the tensor pipe:
+// rows = q heads 16*mt .. 16*mt+15 of sequence `seq`, columns 8*nt .. 8*nt+7.  Pi is split
+// into three bf16 terms (8 + 8 + 8 significant bits), a bf16 q is used as it is and an fp16
+// q is split into two bf16 terms, so every product is exact and the sum is accumulated in
+// fp32, like the fp32 multiply-adds of rotate_q_kernel.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void split3_bf16(float2 v, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+  const float rx = v.x - __low2float(h), ry = v.y - __high2float(h);
+  const __nv_bfloat162 m = __floats2bfloat162_rn(rx, ry);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  mid = *reinterpret_cast<const uint32_t*>(&m);
+  lo = pack_bf16x2(rx - __low2float(m), ry - __high2float(m));
+}
+
+// Operands of one tile: loaded early (one round trip to L2, all loads in flight together),
+// used late, so that other set-up work runs in the shadow of the loads.  The k index of the
+// products may be permuted freely as long as both operands agree: lane (g,t) takes k = 32c +
+// 8t .. 8t+7 of chunk c with 16-byte loads and spends them on the two k-steps of the chunk.
+template <int D>
+struct RotTileOperands {
+  uint4 a0[D / 32], a1[D / 32];   // q rows r0 and r0+8, 8 values each per chunk
+  float4 b0[D / 32], b1[D / 32];  // Pi row n: first and second four k of the lane's eight
+};
+
+template <int D, typename T>
+__device__ __forceinline__ void rotate_q_tile_load(RotTileOperands<D>& op, const T* __restrict__ q,
+                                                   const float* __restrict__ rotation, int hq,
+                                                   int seq, int mt, int nt, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int r0 = mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < hq, ok1 = r1 < hq;
+  const T* q0 = q + (int64_t(seq) * hq + (ok0 ? r0 : 0)) * D + 8 * t;
+  const T* q1 = q + (int64_t(seq) * hq + (ok1 ? r1 : 0)) * D + 8 * t;
+  const float* pr = rotation + (8 * nt + g) * D + 8 * t;  // B[k][n] = Pi[n][k]
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    op.a0[c] = ok0 ? *reinterpret_cast<const uint4*>(q0 + 32 * c) : zero;
+    op.a1[c] = ok1 ? *reinterpret_cast<const uint4*>(q1 + 32 * c) : zero;
+    op.b0[c] = *reinterpret_cast<const float4*>(pr + 32 * c);
+    op.b1[c] = *reinterpret_cast<const float4*>(pr + 32 * c + 4);
+  }
+}
+
+template <int D, typename T>
+__device__ __forceinline__ void rotate_q_tile_finish(const RotTileOperands<D>& op,
+                                                     __half* __restrict__ out, int hq, int seq,
+                                                     int mt, int nt, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int r0 = mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < hq, ok1 = r1 < hq;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int c = ks >> 1;
+    const bool second = ks & 1;
+    const float4 bv = second ? op.b1[c] : op.b0[c];
+    const uint32_t a[4] = {second ? op.a0[c].z : op.a0[c].x, second ? op.a1[c].z : op.a1[c].x,
+                           second ? op.a0[c].w : op.a0[c].y, second ? op.a1[c].w : op.a1[c].y};
+    uint32_t bh[2], bm[2], bl[2];
+    split3_bf16(make_float2(bv.x, bv.y), bh[0], bm[0], bl[0]);
+    split3_bf16(make_float2(bv.z, bv.w), bh[1], bm[1], bl[1]);
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      mma_bf16(acc, a[0], a[1], a[2], a[3], bl[0], bl[1]);
+      mma_bf16(acc, a[0], a[1], a[2], a[3], bm[0], bm[1]);
+      mma_bf16(acc, a[0], a[1], a[2], a[3], bh[0], bh[1]);
+    } else {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&a[i]));
+        const __nv_bfloat162 h = __floats2bfloat162_rn(f.x, f.y);
+        ah[i] = *reinterpret_cast<const uint32_t*>(&h);
+        al[i] = pack_bf16x2(f.x - __low2float(h), f.y - __high2float(h));  // 3 bits: exact
+      }
+      mma_bf16(acc, al[0], al[1], al[2], al[3], bl[0], bl[1]);
+      mma_bf16(acc, ah[0], ah[1], ah[2], ah[3], bl[0], bl[1]);
+      mma_bf16(acc, al[0], al[1], al[2], al[3], bm[0], bm[1]);
+      mma_bf16(acc, ah[0], ah[1], ah[2], ah[3], bm[0], bm[1]);
+      mma_bf16(acc, al[0], al[1], al[2], al[3], bh[0], bh[1]);
+      mma_bf16(acc, ah[0], ah[1], ah[2], ah[3], bh[0], bh[1]);
+    }
+  }
+  const int col = 8 * nt + 2 * t;
+  if (ok0)
+    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r0) * D + col) = __floats2half2_rn(
+        to_f32(from_f32<T>(acc[0])), to_f32(from_f32<T>(acc[1])));
+  if (ok1)
+    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r1) * D + col) = __floats2half2_rn(
+        to_f32(from_f32<T>(acc[2])), to_f32(from_f32<T>(acc[3])));
+}
+
+// ------------------------------------------------------------------------------------
+// phase c of the single-launch form: (sequence, 8 heads) merge jobs, CTA c takes jobs c,
+// c + grid, ...  The look-up table and the rings are dead by now: Pi goes where the table
+// was, the job's scratch where the first ring stages were.
+// ------------------------------------------------------------------------------------
+template <int D, typename T>
+__device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* smem,
+                                            const int* prefix, int64_t total, int64_t active,
+                                            int teams, int stages) {
+  constexpr int ROWF = D + kPartPad;
+  constexpr int HP = kDecodeThreads / D;  // heads handled at a time
+  constexpr int PASSES = kMergeHeads / HP;
+  constexpr int TPG = kMergeHeads * D / 4;  // threads that cover 8 rows, four values each
+  constexpr int G = kDecodeThreads / TPG;   // groups of such threads
+  constexpr int kBatch = 10;                // rows a thread keeps in flight
+  const int tid = threadIdx.x;
+  const int hgroups = (p.hq + kMergeHeads - 1) / kMergeHeads;
+  const int jobs = p.num_seqs * hgroups;
+  __syncthreads();  // every warp of the CTA has left the table and the rings
+  if (int(blockIdx.x) >= jobs) return;
+
+  float* pi_s = reinterpret_cast<float*>(smem);  // [k][j]
+  float* o_s = reinterpret_cast<float*>(smem + p.off_ring);  // [8][D]
+  float* num_s = o_s + kMergeHeads * D;                      // [G][8][D]
+  float2* ml_s = reinterpret_cast<float2*>(num_s + G * kMergeHeads * D);  // [G][8]: m, den
+  int* part_row = reinterpret_cast<int*>(ml_s + G * kMergeHeads);
+  int* n_parts_s = part_row + kMaxParts;
+  uint64_t* pi_bar = reinterpret_cast<uint64_t*>(smem + p.off_bar) + teams * (2 * stages + 2);
+  if (tid == 0) {
+    fence_proxy_async();  // the table was written by ordinary stores
+    mbar_expect_tx(pi_bar, D * D * 4);
+    bulk_g2s(pi_s, p.rotation, D * D * 4, pi_bar);
+  }
+  bool pi_ready = false;
+  const int d = tid % D, hh0 = tid / D;
+  const int grp = tid / TPG, mh = (tid % TPG) / (D / 4), dq = tid % (D / 4);
+
+  for (int job = blockIdx.x; job < jobs; job += gridDim.x) {
+    const int seq = job / hgroups, h0 = (job - seq * hgroups) * kMergeHeads;
+    // ---- the sequence's partial rows (one lane per split), and the wait until all of them
+    // are stored ---------------------------------------------------------------------------
+    if (tid < 32) {
+      const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
+      const int pps = n_pages > 0 ? (n_pages + p.num_splits - 1) / p.num_splits : 1;
+      int n = 0;
+      for (int sb = 0; sb < p.num_splits; sb += 32) {
+        const int sp = sb + tid;
+        const int a = sp * pps;
+        int b = a + pps;
+        if (b > n_pages) b = n_pages;
+        int c_first = 0, cnt = 0;
+        if (sp < p.num_splits && a < b) {
+          c_first = cta_of_page(int64_t(p0) + a, total, active);
+          cnt = cta_of_page(int64_t(p0) + b - 1, total, active) - c_first + 1;
+        }
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (tid >= o) incl += up;
+        }
+        const int at = n + incl - cnt;
+        for (int c = 0; c < cnt && at + c < kMaxParts; ++c)
+          part_row[at + c] = seq * p.num_splits + sp + c_first + c;
+        n += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (n > kMaxParts) n = kMaxParts;
+      if (tid == 0) {
+        *n_parts_s = n;
+        const uint32_t expected = uint32_t(n) * uint32_t(p.hkv);
+        uint32_t spins = 0;
+        while (ld_acquire_u32(p.seg_count + seq) < expected) {
+          __nanosleep(32);
+          if (++spins > (kSpinLimit >> 2)) {
+            atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+            break;
+          }
+        }
+        __threadfence();
+      }
+    }
+    __syncthreads();
+    const int n_parts = *n_parts_s;
+    // rows were written by other SMs during this launch: read them past the L1
+    auto row_ptr = [&](int i, int h) { return p.slots + (int64_t(part_row[i]) * p.hq + h) * ROWF; };
+
+    // ---- G groups of threads take every G-th partial row; thread (head mh, four coordinates
+    // from 4*dq) keeps up to kBatch rows in registers so that all loads of a job are in
+    // flight together, and recomputes the weights of its head itself -------------------------
+    {
+      const int h = h0 + mh;
+      float m_run = -INFINITY, den = 0.f;
+      float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c0 = grp; c0 < n_parts; c0 += G * kBatch) {
+        float2 ml[kBatch];
+        float4 v[kBatch];
+#pragma unroll
+        for (int x = 0; x < kBatch; ++x) {
+          ml[x] = make_float2(-INFINITY, 0.f);
+          v[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c0 + x * G < n_parts && h < p.hq) {
+            const float* row = row_ptr(c0 + x * G, h);
+            ml[x] = __ldcg(reinterpret_cast<const float2*>(row + D));
+            v[x] = __ldcg(reinterpret_cast<const float4*>(row) + dq);
+          }
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int x = 0; x < kBatch; ++x) m_new = fmaxf(m_new, ml[x].x);
+        const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+        den *= alpha;
+        num.x *= alpha; num.y *= alpha; num.z *= alpha; num.w *= alpha;
+#pragma unroll
+        for (int x = 0; x < kBatch; ++x) {
+          const float w = (ml[x].x == -INFINITY) ? 0.f : exp2f(ml[x].x - m_new);
+          den = fmaf(w, ml[x].y, den);
+          num.x = fmaf(w, v[x].x, num.x);
+          num.y = fmaf(w, v[x].y, num.y);
+          num.z = fmaf(w, v[x].z, num.z);
+          num.w = fmaf(w, v[x].w, num.w);
+        }
+        m_run = m_new;
+      }
+      reinterpret_cast<float4*>(num_s + (grp * kMergeHeads + mh) * D)[dq] = num;
+      if (dq == 0) ml_s[grp * kMergeHeads + mh] = make_float2(m_run, den);
+    }
+    __syncthreads();
+    // ---- combine the groups; thread (head hh, coordinate d) from here on --------------------
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+      const int hh = hh0 + ps * HP;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) m_all = fmaxf(m_all, ml_s[gi * kMergeHeads + hh].x);
+      float den = 0.f, num = 0.f;
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        const float2 ml = ml_s[gi * kMergeHeads + hh];
+        const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - m_all);
+        den = fmaf(w, ml.y, den);
+        num = fmaf(w, num_s[(gi * kMergeHeads + hh) * D + d], num);
+      }
+      const float o = (h0 + hh < p.hq && den > 0.f) ? num / den : 0.f;
+      o_s[hh * D + d] = to_f32(from_f32<T>(o));  // the reference rounds the rotated output
+    }
+    __syncthreads();
+    if (!pi_ready) {
+      if (!mbar_wait(pi_bar, 0)) {  // only if the copy were lost
+        if (tid == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+        return;
+      }
+      pi_ready = true;
+    }
+    float acc[PASSES];
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) acc[ps] = 0.f;
+#pragma unroll 4
+    for (int k4 = 0; k4 < D; k4 += 4) {
+      const float b0 = pi_s[(k4 + 0) * D + d], b1 = pi_s[(k4 + 1) * D + d];
+      const float b2 = pi_s[(k4 + 2) * D + d], b3 = pi_s[(k4 + 3) * D + d];
+#pragma unroll
+      for (int ps = 0; ps < PASSES; ++ps) {
+        const float4 a = *reinterpret_cast<const float4*>(o_s + (hh0 + ps * HP) * D + k4);
+        acc[ps] = fmaf(a.x, b0, acc[ps]);
+        acc[ps] = fmaf(a.y, b1, acc[ps]);
+        acc[ps] = fmaf(a.z, b2, acc[ps]);
+        acc[ps] = fmaf(a.w, b3, acc[ps]);
+      }
+    }
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+      const int hh = hh0 + ps * HP;
+      if (h0 + hh < p.hq)
+        static_cast<T*>(p.out)[(int64_t(seq) * p.hq + h0 + hh) * D + d] = from_f32<T>(acc[ps]);
+    }
+    __syncthreads();  // scratch is reused by the next job
+    // the last job of a sequence puts its counters back to zero for the next call
+    if (tid == 0 && atomicAdd(p.merge_count + seq, 1u) == uint32_t(hgroups - 1)) {
+      p.q_count[seq] = 0u;
+      p.seg_count[seq] = 0u;
+      p.merge_count[seq] = 0u;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // 2. streaming kernel
 //
@@ -175,8 +478,10 @@ __device__ __forceinline__ uint32_t lut_addr(uint32_t w, uint32_t lane4) {
   return prmt(w, lane4, 0x5504u | (uint32_t(I) << 4));
 }
 
-template <int D, bool KPRMT>
+// FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out
+template <int D, bool KPRMT, int FUSE>
 __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeArgs p) {
+  using TQ = typename std::conditional<FUSE == 2, __half, __nv_bfloat16>::type;
   constexpr int KS = D / 16;  // k-steps of the QK product = m-tiles of the PV product
   constexpr int KW = D / 32;  // 32-bit words of K codes per lane and row
   constexpr int VB = D / 16;  // bytes of V codes per lane and row
@@ -207,6 +512,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const uint32_t ring_off = p.off_ring + uint32_t(team) * stages * page_bytes;
   const uint32_t q_off = p.off_q + uint32_t(team) * q_bytes;
 
+  const int q_tiles = ((p.hq + 15) / 16) * (D / 8);  // rotated tiles per sequence
+  [[maybe_unused]] RotTileOperands<D> rot_op;
+  [[maybe_unused]] int rot_len = 0;
+  [[maybe_unused]] const int rot_jobs = p.num_seqs * q_tiles;
+  [[maybe_unused]] const int rot_job0 = blockIdx.x * kCW + warp;
+  [[maybe_unused]] const int m_tiles = (p.hq + 15) / 16;
   // ---- set-up: barriers, page prefix (warp 0), look-up table (all warps) ---------------
   if (leader && lane == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -215,33 +526,37 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     }
     mbar_init(qfull_bar, 1);
     mbar_init(qempty_bar, p.hkv);
+    if (FUSE && tid == 0)
+      mbar_init(reinterpret_cast<uint64_t*>(smem + p.off_bar) + teams * (2 * stages + 2), 1);
     mbar_fence_init();
   }
-  // centroids as fp16, staged where the first ring stage will live later
-  {
-    __half* cstage = reinterpret_cast<__half*>(smem + p.off_ring);
-    if (tid < 32) {
-      const int i = tid & 15;
-      float c = 0.f;
-      if (tid < 16) { if (i < p.nck) c = p.cent_k[i]; } else { if (i < p.ncv) c = p.cent_v[i]; }
-      cstage[tid] = __float2half_rn(c);
-    }
+  // The first loads of a CTA miss every cache, so the two that do not depend on each other
+  // go out together: the sequence lengths (warp 0, for the page prefix) and the centroids
+  // (warp 1, as fp16).  The block table can only be read once the prefix is there, and the
+  // first page only after that: the leaders start both right after the barrier below, and
+  // the look-up table is filled while those loads are in flight.
+  const unsigned short* cs = reinterpret_cast<const unsigned short*>(smem + p.off_cent);
+  float cent_val = 0.f;
+  if (warp == 1) {
+    const int i = lane & 15;
+    if (lane < 16) { if (i < p.nck) cent_val = p.cent_k[i]; } else { if (i < p.ncv) cent_val = p.cent_v[i]; }
   }
-  __syncthreads();
+  // ---- phase a, first half: the operands of this warp's query tile are requested now, so
+  // that the rest of the set-up runs in the shadow of these (cold) loads -------------------
+  if constexpr (FUSE != 0) {
+    if (rot_job0 < rot_jobs) {
+      const int seq = rot_job0 / q_tiles, r = rot_job0 - seq * q_tiles;
+      rot_len = p.seq_lens[seq];
+      rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src), p.rotation, p.hq, seq,
+                                r % m_tiles, r / m_tiles, lane);
+    }
+    // first touch of the other buffers: address translation is warm when they are needed
+    if (tid == 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.block_table));
+    if (tid == 65) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_count));
+    if (tid == 66) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rot_w));
+  }
+  if (warp == 1) reinterpret_cast<__half*>(smem + p.off_cent)[lane] = __float2half_rn(cent_val);
   if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
-  {
-    const unsigned short* cs = reinterpret_cast<const unsigned short*>(smem + p.off_ring);
-    for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
-      const int e = i >> 5, l = i & 31;
-      const uint32_t hi = e >> 4, lo = e & 15;
-      // K entry: byte of one token -> (even coordinate, odd coordinate)
-      // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
-      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
-          uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
-      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
-          uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
-    }
-  }
   __syncthreads();
 
   // ---- this team's run of the flat page list ------------------------------------------------
@@ -249,13 +564,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const int64_t workers = int64_t(gridDim.x) * teams;
   const int64_t active = total < workers ? total : workers;
   const int64_t wk = int64_t(blockIdx.x) * teams + team;
-  if (wk >= active) return;
-  const int64_t f0 = total * wk / active, f1 = total * (wk + 1) / active;
-  const int n_run = int(f1 - f0);
-  if (n_run <= 0) return;
+  const int64_t f0 = wk < active ? total * wk / active : 0;
+  const int n_run = wk < active ? int(total * (wk + 1) / active - f0) : 0;
 
   // ---- producer state (used by the leader warp only) ---------------------------------------
   int issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0;
+  int q_owed = -1;  // sequence whose query copy is still to be issued
 
   // descriptors of run pages [base, base + 32): x = physical page, y = valid tokens |
   // flags << 8, z = sequence, w = partial-row slot
@@ -300,7 +614,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     if (issue_idx < n_run && !empty_ok)
       empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
   };
-  auto pump = [&]() {
+  // the query copy waits for its buffer and, in the single-launch form, for the rotated rows
+  auto pump_q = [&]() {
+    if (q_owed < 0) return;
+    if (q_issued > 0 && !mbar_try_wait(qempty_bar, (q_issued - 1) & 1)) return;
+    if constexpr (FUSE != 0) {
+      if (ld_acquire_u32(p.q_count + q_owed) < uint32_t(q_tiles)) return;
+      fence_proxy_async();  // rows written by other CTAs' stores, read by a bulk copy
+    }
+    mbar_expect_tx(qfull_bar, q_bytes);
+    bulk_g2s(smem + q_off, p.q_rot + int64_t(q_owed) * p.hq * D, q_bytes, qfull_bar);
+    ++q_issued;
+    q_owed = -1;
+  };
+  auto pump = [&](bool with_q = true) {
     while (issue_idx < n_run) {
       if (!empty_ok) {
         empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
@@ -308,10 +635,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       }
       const int4 d = desc_ring[issue_idx & (kDescRing - 1)];
       if ((d.y >> 8) & kQNew) {
-        if (q_issued > 0 && !mbar_try_wait(qempty_bar, (q_issued - 1) & 1)) break;
-        mbar_expect_tx(qfull_bar, q_bytes);
-        bulk_g2s(smem + q_off, p.q_rot + int64_t(d.z) * p.hq * D, q_bytes, qfull_bar);
-        ++q_issued;
+        if (q_owed >= 0) {  // the previous query copy has not gone out yet
+          pump_q();
+          if (q_owed >= 0) break;
+        }
+        q_owed = d.z;
       }
       mbar_expect_tx(full_bar + issue_stage, page_bytes);
       bulk_g2s(smem + ring_off + uint32_t(issue_stage) * page_bytes,
@@ -321,12 +649,46 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
       empty_ok = issue_idx < stages;  // the first pass over the ring needs no poll
     }
+    // after the pages: the poll of the query's counter is a round trip to L2
+    if (with_q) pump_q();
   };
 
-  if (leader) {
+  if (leader && n_run > 0) {
     produce_chunk(0);
-    if (lane == 0) pump();
+    if (lane == 0) pump(false);  // the query is asked for once the table is filled
   }
+
+  // ---- look-up table -------------------------------------------------------------------------
+  for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
+    const int e = i >> 5, l = i & 31;
+    const uint32_t hi = e >> 4, lo = e & 15;
+    // K entry: byte of one token -> (even coordinate, odd coordinate)
+    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
+        uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
+        uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
+  }
+
+  // ---- phase a: one rotated query tile per warp of the grid --------------------------------
+  if constexpr (FUSE != 0) {
+    for (int job = rot_job0; job < rot_jobs; job += gridDim.x * kCW) {
+      const int seq = job / q_tiles, r = job - seq * q_tiles;
+      if (job != rot_job0) {
+        rot_len = p.seq_lens[seq];
+        rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src), p.rotation, p.hq, seq,
+                                  r % m_tiles, r / m_tiles, lane);
+      }
+      if (rot_len <= 0) continue;  // nobody reads the query of an empty sequence
+      rotate_q_tile_finish<D, TQ>(rot_op, p.q_rot_w, p.hq, seq, r % m_tiles, r / m_tiles, lane);
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.q_count + seq, 1u);
+    }
+  }
+
+  __syncthreads();  // the table is complete
+  if (n_run > 0) {  // ---- phase b ----------------------------------------------------------
 
   // ---- per-warp constants -------------------------------------------------------------------
   const uint32_t lane4 = uint32_t(lane) * 4;
@@ -342,8 +704,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   if constexpr (KPRMT) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float c = i < p.nck ? p.cent_k[i] : 0.f;
-      const uint32_t h = uint32_t(__half_as_ushort(__float2half_rn(c)));
+      const uint32_t h = cs[i];
       const uint32_t lo8 = (h & 0xffu) << (8 * (i & 3)), hi8 = (h >> 8) << (8 * (i & 3));
       if (i < 4) { tl0 |= lo8; th0 |= hi8; } else { tl1 |= lo8; th1 |= hi8; }
     }
@@ -405,10 +766,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 #pragma unroll
         for (int c = 0; c < 4; ++c) oacc[j][c] = 0.f;
       if (flags & kQNew) {
-        if (!mbar_wait(qfull_bar, qcnt & 1)) {
+        if (leader) {  // the copy may still be owed: keep the producer going
+          uint32_t spins = 0;
+#pragma unroll 1
+          while (!mbar_try_wait(qfull_bar, qcnt & 1)) {
+            if (lane == 0) pump();
+            if (++spins > kSpinLimit) {
+              timed_out = true;
+              break;
+            }
+          }
+          __syncwarp();
+        } else if (!mbar_wait(qfull_bar, qcnt & 1)) {
           timed_out = true;
-          break;
         }
+        if (timed_out) break;
         // lane (g,t), k-step s: coordinates of cache bytes (D/8)t + 2s, +1 of q head head*G+g
         const bool valid = g < group;
         const uint32_t qoff =
@@ -615,6 +987,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         }
         if (g == 0) *reinterpret_cast<float4*>(row + D) = make_float4(m_run[c], l_run[c], 0.f, 0.f);
       }
+      if constexpr (FUSE != 0) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.seg_count + d.z, 1u);
+      }
     }
 
     __syncwarp();
@@ -622,6 +999,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     if (++stage == stages) { stage = 0; fphase ^= 1; }
   }
   if (timed_out && lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+  }  // phase b
+
+  if constexpr (FUSE != 0) fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
 }
 
 // ------------------------------------------------------------------------------------
@@ -646,10 +1026,6 @@ struct MergeArgs {
   float* row_out;
   int num_seqs, hq;
 };
-
-constexpr int kMergeHeads = 8;
-constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams + splits)
-constexpr int kPartChunk = 128;  // rows merged per pass
 
 template <int D, typename T, bool kFromSlots, bool kFinal>
 __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs p) {
@@ -809,8 +1185,10 @@ static int device_sm_count() {
   return cached;
 }
 
+// status word at 0; three counter arrays of kMaxSeqs words (single-launch form) at 256;
+// the rotated query; the partial rows
 struct WorkspaceLayout {
-  size_t q_rot_off, slots_off, total;
+  size_t count_off, q_rot_off, slots_off, total;
 };
 
 static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
@@ -820,7 +1198,8 @@ static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits,
   if (splits <= 0) splits = kMaxSplits;
   const int ctas = workers;
   WorkspaceLayout w;
-  w.q_rot_off = 256;
+  w.count_off = 256;
+  w.q_rot_off = up256(w.count_off + 3 * size_t(kMaxSeqs) * sizeof(uint32_t));
   w.slots_off = up256(w.q_rot_off + size_t(num_seqs) * hq * d * sizeof(__half));
   w.total = up256(w.slots_off +
                   (size_t(num_seqs) * splits + ctas) * hq * (d + kPartPad) * sizeof(float));
@@ -833,7 +1212,7 @@ static int auto_splits() { return 1; }
 
 struct SmemPlan {
   int stages;  // per team
-  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, total;
+  uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent, total;
 };
 
 static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size) {
@@ -844,7 +1223,7 @@ static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size) 
   const uint32_t q_all = teams * up16(uint32_t(hq) * d * 2);
   const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
   const uint32_t desc = teams * kDescRing * 16;
-  const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16;
+  const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16 + 96;
   const uint32_t budget = 227 * 1024 - 512;
   int stages = 0;
   if (budget > fixed) stages = int((budget - fixed) / (teams * (page_bytes + 16)));
@@ -855,13 +1234,14 @@ static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size) 
   s.off_prefix = s.off_q + q_all;
   s.off_desc = s.off_prefix + prefix;
   s.off_bar = s.off_desc + desc;
-  s.total = s.off_bar + teams * (2 * uint32_t(stages) + 2) * 8;
+  s.off_cent = up16(s.off_bar + teams * (2 * uint32_t(stages) + 2) * 8 + 8);  // + merge barrier
+  s.total = s.off_cent + 64;  // 32 fp16 centroids
   return s;
 }
 
-template <int D, bool KPRMT>
+template <int D, bool KPRMT, int FUSE>
 static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
-  auto kern = paged_decode_kernel<D, KPRMT>;
+  auto kern = paged_decode_kernel<D, KPRMT, FUSE>;
   // opt in once per (thread, device, size): the attribute call is not free
   static thread_local int set_dev = -1;
   static thread_local size_t set_bytes = 0;
@@ -879,19 +1259,38 @@ static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStre
   a.stages = sp.stages;
   a.off_ring = sp.off_ring; a.off_q = sp.off_q;
   a.off_prefix = sp.off_prefix; a.off_desc = sp.off_desc; a.off_bar = sp.off_bar;
-  kern<<<ctas, kDecodeThreads, sp.total, stream>>>(a);
+  a.off_cent = sp.off_cent;
+  if constexpr (FUSE == 0) {
+    kern<<<ctas, kDecodeThreads, sp.total, stream>>>(a);
+  } else {
+    // CTAs wait for one another: all of them must be resident
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = sp.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs refused: %s", ctas,
+                  cudaGetErrorString(e));
+  }
   return check_launch("paged decode kernel launch");
 }
 
+template <int FUSE>
 static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, int head_dim,
                          cudaStream_t stream) {
-  static const bool force_lut = getenv("FQ_DECODE_KLUT") != nullptr;  // experiment knob
-  const bool kprmt = a.nck <= 8 && !force_lut;  // key codes fit a register-resident 8-entry table
+  const bool kprmt = a.nck <= 8;  // key codes fit a register-resident 8-entry table
   if (head_dim == 128)
-    return kprmt ? launch_stream_t<128, true>(a, sp, ctas, stream)
-                 : launch_stream_t<128, false>(a, sp, ctas, stream);
-  return kprmt ? launch_stream_t<64, true>(a, sp, ctas, stream)
-               : launch_stream_t<64, false>(a, sp, ctas, stream);
+    return kprmt ? launch_stream_t<128, true, FUSE>(a, sp, ctas, stream)
+                 : launch_stream_t<128, false, FUSE>(a, sp, ctas, stream);
+  return kprmt ? launch_stream_t<64, true, FUSE>(a, sp, ctas, stream)
+               : launch_stream_t<64, false, FUSE>(a, sp, ctas, stream);
 }
 
 template <int D>
@@ -992,7 +1391,7 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                         const float* centroids_v, int ncv, const float* rotation, int num_seqs,
                         int hq, int hkv, int head_dim, int block_size, int64_t num_blocks,
                         float sm_scale, int num_splits, void* workspace, size_t workspace_bytes,
-                        int ctas, cudaStream_t stream) {
+                        int ctas, cudaStream_t stream, void* fused_out = nullptr) {
   FQ_REQUIRE(workspace && aligned(workspace, 256), FQ_ERR_WORKSPACE,
              "paged decode: workspace is null or not 256-byte aligned");
   const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv));
@@ -1002,9 +1401,13 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   FQ_REQUIRE(sp.stages >= 2, FQ_ERR_UNSUPPORTED,
              "paged decode: a page of %d tokens x %d heads does not fit the shared-memory ring",
              block_size, hkv);
+  FQ_REQUIRE(sp.off_q - sp.off_ring >= kMergeScratchBytes, FQ_ERR_UNSUPPORTED,
+             "paged decode: shared-memory ring too small for the merge phase");
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   const __half* q_rot = reinterpret_cast<const __half*>(ws + w.q_rot_off);
-  if (rotation) {
+  if (fused_out) {
+    // rotation, streaming and merge in one launch
+  } else if (rotation) {
     __half* dst = reinterpret_cast<__half*>(ws + w.q_rot_off);
     int rc = head_dim == 128 ? rotate_q<128>(q, dtype, rotation, dst, num_seqs * hq, stream)
                              : rotate_q<64>(q, dtype, rotation, dst, num_seqs * hq, stream);
@@ -1026,7 +1429,16 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.num_splits = num_splits;
   a.slots = reinterpret_cast<float*>(ws + w.slots_off);
   a.status = reinterpret_cast<uint32_t*>(ws);
-  return launch_stream(a, sp, ctas, head_dim, stream);
+  if (!fused_out) return launch_stream<0>(a, sp, ctas, head_dim, stream);
+  a.q_src = q;
+  a.rotation = rotation;
+  a.out = fused_out;
+  a.q_rot_w = reinterpret_cast<__half*>(ws + w.q_rot_off);
+  a.q_count = reinterpret_cast<uint32_t*>(ws + w.count_off);
+  a.seg_count = a.q_count + kMaxSeqs;
+  a.merge_count = a.seg_count + kMaxSeqs;
+  return dtype == FQ_BF16 ? launch_stream<1>(a, sp, ctas, head_dim, stream)
+                          : launch_stream<2>(a, sp, ctas, head_dim, stream);
 }
 
 static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int hkv, int head_dim,
@@ -1076,16 +1488,10 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
   if (num_seqs == 0) return FQ_OK;
   const int ctas = device_sm_count();
   if (num_splits == 0) num_splits = auto_splits();
-  rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
-                    num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
-                    workspace, workspace_bytes, ctas, stream);
-  if (rc != FQ_OK) return rc;
-  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                num_splits, ctas, seq_lens, block_size);
-  m.rotation = rotation;
-  m.out = out;
-  return launch_merge<true, true>(m, head_dim, dtype, stream);
+  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
+                      workspace, workspace_bytes, ctas, stream, out);
 }
 
 static int partials_common(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
@@ -1273,18 +1679,14 @@ extern "C" int fq_split_k_paged_decode_static(
   void* scratch = nullptr;
   rc = static_scratch(&scratch);
   if (rc != FQ_OK) return rc;
-  // the array keeps what the previous call left: the status word must start at zero
-  cudaError_t e = cudaMemsetAsync(scratch, 0, 256, stream);
+  // the array keeps what the previous call left: the status word and the counters the CTAs
+  // signal each other through must start at zero
+  const size_t head_bytes = workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, 0).q_rot_off;
+  cudaError_t e = cudaMemsetAsync(scratch, 0, head_bytes, stream);
   if (e != cudaSuccess)
     return fail(FQ_ERR_CUDA, "clearing the scratch status word: %s", cudaGetErrorString(e));
-  rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
-                    num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits, scratch,
-                    kStaticScratchBytes, ctas, stream);
-  if (rc != FQ_OK) return rc;
-  MergeArgs m = slot_merge_args(scratch, num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                num_splits, ctas, seq_lens, block_size);
-  m.rotation = rotation;
-  m.out = out;
-  return launch_merge<true, true>(m, head_dim, dtype, stream);
+  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
+                      scratch, kStaticScratchBytes, ctas, stream, out);
 }

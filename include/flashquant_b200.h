@@ -149,8 +149,16 @@ int fq_tq4_compress_append_qjl(const void* key, const void* value, fq_dtype dtyp
  *                  boundary between partial rows.  The pages of the whole batch are spread
  *                  evenly over the SMs whatever this number is; 0 means 1
  *   workspace      caller-owned, 256-byte aligned, at least
- *                  fq_paged_decode_workspace_bytes(...) bytes; its first word is a status
- *                  word that must be zero before the first call (FQ_DEV_* bits are OR-ed in)
+ *                  fq_paged_decode_workspace_bytes(...) bytes.  Its first 32 KiB must be zero
+ *                  before the first call: word 0 is a status word (FQ_DEV_* bits are OR-ed
+ *                  in), the rest holds per-sequence counters that the CTAs of the single
+ *                  launch signal each other through and that every successful call leaves at
+ *                  zero again.  After a call that set a status bit, zero those 32 KiB before
+ *                  the workspace is used again.  Calls that overlap on the GPU need separate
+ *                  workspaces.
+ * The call is one cooperative launch with one CTA per SM: it needs the whole GPU to itself
+ * while it runs (kernels of other streams delay it, they cannot deadlock it: every wait in
+ * the kernel is bounded and ends in FQ_DEV_WAIT_TIMEOUT).
  * head_dim 128 (or 64), block_size a multiple of 16, num_kv_heads in {1,2,4,8,16},
  * num_q_heads/num_kv_heads <= 8, num_seqs <= 2048.
  */
@@ -188,9 +196,9 @@ int fq_split_k_paged_decode_static(const void* q, fq_dtype dtype, const uint8_t*
                                    int num_splits, fq_stream_t stream);
 
 /*
- * The two halves of the call above, for a sequence whose tokens are spread over several
- * GPUs: each GPU produces one partial row per (sequence, query head) over the pages it
- * holds, the rows are exchanged (one all-gather) and every GPU merges all of them.
+ * The two halves of fq_split_k_paged_decode, for a sequence whose tokens are spread over
+ * several GPUs: each GPU produces one partial row per (sequence, query head) over the pages
+ * it holds, the rows are exchanged (one all-gather) and every GPU merges all of them.
  *
  * fq_paged_decode_partials: `partials` (16-byte aligned) receives (num_seqs, num_q_heads,
  * head_dim+4) fp32 rows: head_dim un-normalised accumulator values, then m (base-2
