@@ -39,8 +39,12 @@
 
 namespace fq {
 
-constexpr int kCW = 16;                  // warps per CTA (16 keeps 128 registers per thread)
-constexpr int kDecodeThreads = kCW * 32;
+constexpr int kCW = 16;                  // compute warps per CTA
+constexpr int kComputeThreads = kCW * 32;
+// One more group of four warps holds the producer warp.  The CTA starts with 96 registers per
+// thread (20 warps); the producer group then drops to 24, and the 128 x 72 registers it gives back
+// let the 512 compute threads rise by 16 to 112 (a CTA cannot take more than it released).
+constexpr int kDecodeThreads = kComputeThreads + 128;
 constexpr int kLutBytes = 256 * 256;     // 256 entries x (32 lanes x 4 B for K + the same for V)
 constexpr int kMaxStages = 16;           // per team; the descriptor ring relies on <= 16
 constexpr int kMaxSeqs = 2048;                  // page-count prefix lives in shared memory
@@ -53,7 +57,7 @@ constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams +
 constexpr int kPartChunk = 128;  // rows merged per pass
 // shared memory of a merge job of the single-launch form besides Pi: rounded rows, row list
 constexpr uint32_t kMergeScratchBytes =
-    (kMergeHeads * 128 + kMergeHeads * kDecodeThreads / 2 + 64 + kMaxParts + 4) * 4;
+    (kMergeHeads * 128 + kMergeHeads * kComputeThreads / 2 + 64 + kMaxParts + 4) * 4;
 
 enum : int { kSegStart = 1, kSegEnd = 2, kQNew = 4 };
 
@@ -107,6 +111,11 @@ __device__ __forceinline__ void build_page_prefix(const int32_t* __restrict__ se
     carry = __shfl_sync(0xffffffffu, v, 31);
   }
   __syncwarp();
+}
+
+// Barrier of the 16 compute warps (the producer warp group does not take part).
+__device__ __forceinline__ void compute_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
 }
 
 // CTA that owns flat page f when `total` pages are cut into `active` equal runs
@@ -278,15 +287,15 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
                                             const int* prefix, int64_t total, int64_t active,
                                             int teams, int stages) {
   constexpr int ROWF = D + kPartPad;
-  constexpr int HP = kDecodeThreads / D;  // heads handled at a time
+  constexpr int HP = kComputeThreads / D;  // heads handled at a time
   constexpr int PASSES = kMergeHeads / HP;
   constexpr int TPG = kMergeHeads * D / 4;  // threads that cover 8 rows, four values each
-  constexpr int G = kDecodeThreads / TPG;   // groups of such threads
+  constexpr int G = kComputeThreads / TPG;   // groups of such threads
   constexpr int kBatch = 10;                // rows a thread keeps in flight
   const int tid = threadIdx.x;
   const int hgroups = (p.hq + kMergeHeads - 1) / kMergeHeads;
   const int jobs = p.num_seqs * hgroups;
-  __syncthreads();  // every warp of the CTA has left the table and the rings
+  compute_sync();  // every warp of the CTA has left the table and the rings
   if (int(blockIdx.x) >= jobs) return;
 
   float* pi_s = reinterpret_cast<float*>(smem);  // [k][j]
@@ -349,7 +358,7 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
         __threadfence();
       }
     }
-    __syncthreads();
+    compute_sync();
     const int n_parts = *n_parts_s;
     // rows were written by other SMs during this launch: read them past the L1
     auto row_ptr = [&](int i, int h) { return p.slots + (int64_t(part_row[i]) * p.hq + h) * ROWF; };
@@ -394,7 +403,7 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       reinterpret_cast<float4*>(num_s + (grp * kMergeHeads + mh) * D)[dq] = num;
       if (dq == 0) ml_s[grp * kMergeHeads + mh] = make_float2(m_run, den);
     }
-    __syncthreads();
+    compute_sync();
     // ---- combine the groups; thread (head hh, coordinate d) from here on --------------------
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
@@ -413,7 +422,7 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       const float o = (h0 + hh < p.hq && den > 0.f) ? num / den : 0.f;
       o_s[hh * D + d] = to_f32(from_f32<T>(o));  // the reference rounds the rotated output
     }
-    __syncthreads();
+    compute_sync();
     if (!pi_ready) {
       if (!mbar_wait(pi_bar, 0)) {  // only if the copy were lost
         if (tid == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
@@ -443,7 +452,7 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       if (h0 + hh < p.hq)
         static_cast<T*>(p.out)[(int64_t(seq) * p.hq + h0 + hh) * D + d] = from_f32<T>(acc[ps]);
     }
-    __syncthreads();  // scratch is reused by the next job
+    compute_sync();  // scratch is reused by the next job
     // the last job of a sequence puts its counters back to zero for the next call
     if (tid == 0 && atomicAdd(p.merge_count + seq, 1u) == uint32_t(hgroups - 1)) {
       p.q_count[seq] = 0u;
@@ -519,7 +528,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   [[maybe_unused]] const int rot_job0 = blockIdx.x * kCW + warp;
   [[maybe_unused]] const int m_tiles = (p.hq + 15) / 16;
   // ---- set-up: barriers, page prefix (warp 0), look-up table (all warps) ---------------
-  if (leader && lane == 0) {
+  if (leader && lane == 0 && warp < kCW) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + s, 1);
       mbar_init(empty_bar + s, p.hkv);
@@ -544,7 +553,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   // ---- phase a, first half: the operands of this warp's query tile are requested now, so
   // that the rest of the set-up runs in the shadow of these (cold) loads -------------------
   if constexpr (FUSE != 0) {
-    if (rot_job0 < rot_jobs) {
+    if (warp < kCW && rot_job0 < rot_jobs) {
       const int seq = rot_job0 / q_tiles, r = rot_job0 - seq * q_tiles;
       rot_len = p.seq_lens[seq];
       rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src), p.rotation, p.hq, seq,
@@ -559,107 +568,146 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
   __syncthreads();
 
-  // ---- this team's run of the flat page list ------------------------------------------------
+  // ---- the flat page list and its cut into runs ---------------------------------------------
   const int64_t total = prefix[p.num_seqs];
   const int64_t workers = int64_t(gridDim.x) * teams;
   const int64_t active = total < workers ? total : workers;
-  const int64_t wk = int64_t(blockIdx.x) * teams + team;
-  const int64_t f0 = wk < active ? total * wk / active : 0;
-  const int n_run = wk < active ? int(total * (wk + 1) / active - f0) : 0;
 
-  // ---- producer state (used by the leader warp only) ---------------------------------------
-  int issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0;
-  int q_owed = -1;  // sequence whose query copy is still to be issued
-
-  // descriptors of run pages [base, base + 32): x = physical page, y = valid tokens |
-  // flags << 8, z = sequence, w = partial-row slot
-  auto produce_chunk = [&](int base) {
-    const int i = base + lane;
-    if (i < n_run) {
-      const int64_t f = f0 + i;
-      int lo = 0, hi = p.num_seqs - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
-      }
-      const int seq = lo;
-      const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
-      const int pg = int(f - p0);
-      const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
-      const int s = pg / pps;
-      int split_end = (s + 1) * pps;
-      if (split_end > n_pages) split_end = n_pages;
-      const bool seg_first = (pg == s * pps) || (i == 0);
-      const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
-      const bool q_new = (i == 0) || (pg == 0);
-      int64_t phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
-      if (phys < 0 || phys >= p.num_blocks) {
-        atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
-        phys = 0;
-      }
-      int n_valid = p.seq_lens[seq] - pg * p.block_size;
-      if (n_valid > p.block_size) n_valid = p.block_size;
-      const int flags = (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
-      desc_ring[i & (kDescRing - 1)] =
-          make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
+  // ------------------------------------------------------------------------------------------
+  // Producer warp: lane l feeds team l.  It owns everything that is not arithmetic on codes:
+  // the page descriptors (32 at a time per team, all lanes together), the bulk copies of the
+  // pages into the team's ring as stages come free, and the copy of the rotated query when a
+  // new sequence starts.  It keeps 24 registers and hands the rest of its share to the
+  // compute warps.
+  // ------------------------------------------------------------------------------------------
+  if (warp >= kCW) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+    if (warp > kCW) return;
+    const bool has_team = lane < teams;
+    const int64_t my_wk = int64_t(blockIdx.x) * teams + lane;
+    int64_t my_f0 = 0;
+    int my_run = 0;
+    if (has_team && my_wk < active) {
+      my_f0 = total * my_wk / active;
+      my_run = int(total * (my_wk + 1) / active - my_f0);
     }
-    __syncwarp();
-  };
-
-  // lane 0 of the leader: issue pages whose stage is free; never blocks.  The answer of an
-  // mbarrier poll takes a few hundred cycles to come back, so the poll for the next stage
-  // is sent early (`pump_poll`, in the middle of a page) and only read here.
-  bool empty_ok = true;  // stage of page `issue_idx` known to be free
-  auto pump_poll = [&]() {
-    if (issue_idx < n_run && !empty_ok)
-      empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
-  };
-  // the query copy waits for its buffer and, in the single-launch form, for the rotated rows
-  auto pump_q = [&]() {
-    if (q_owed < 0) return;
-    if (q_issued > 0 && !mbar_try_wait(qempty_bar, (q_issued - 1) & 1)) return;
-    if constexpr (FUSE != 0) {
-      if (ld_acquire_u32(p.q_count + q_owed) < uint32_t(q_tiles)) return;
-      fence_proxy_async();  // rows written by other CTAs' stores, read by a bulk copy
-    }
-    mbar_expect_tx(qfull_bar, q_bytes);
-    bulk_g2s(smem + q_off, p.q_rot + int64_t(q_owed) * p.hq * D, q_bytes, qfull_bar);
-    ++q_issued;
-    q_owed = -1;
-  };
-  auto pump = [&](bool with_q = true) {
-    while (issue_idx < n_run) {
-      if (!empty_ok) {
-        empty_ok = mbar_try_wait(empty_bar + issue_stage, issue_phase);
-        if (!empty_ok) break;
-      }
-      const int4 d = desc_ring[issue_idx & (kDescRing - 1)];
-      if ((d.y >> 8) & kQNew) {
-        if (q_owed >= 0) {  // the previous query copy has not gone out yet
-          pump_q();
-          if (q_owed >= 0) break;
+    uint64_t* my_full = reinterpret_cast<uint64_t*>(smem + p.off_bar) + lane * (2 * stages + 2);
+    uint64_t* my_empty = my_full + stages;
+    uint64_t* my_qfull = my_empty + stages;
+    uint64_t* my_qempty = my_qfull + 1;
+    const int4* my_desc = reinterpret_cast<const int4*>(smem + p.off_desc) + lane * kDescRing;
+    const uint32_t my_ring = p.off_ring + uint32_t(lane) * stages * page_bytes;
+    const uint32_t my_q = p.off_q + uint32_t(lane) * q_bytes;
+    int produced = 0, issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0, q_owed = -1;
+    uint32_t idle = 0;
+#pragma unroll 1
+    while (true) {
+      // ---- descriptors of run pages [base, base + 32) of team T: x = physical page, y = valid
+      // tokens | flags << 8, z = sequence, w = partial-row slot.  A chunk is written when fewer
+      // than 16 described pages are left to issue; the ring slots it overwrites held pages
+      // more than 16 behind the issue front, which every warp of the team has left (a warp is
+      // never more than `stages` <= 16 pages behind it).
+#pragma unroll 1
+      for (int T = 0; T < teams; ++T) {
+        const int base = __shfl_sync(0xffffffffu, produced, T);
+        const int iss = __shfl_sync(0xffffffffu, issue_idx, T);
+        const int n_run = __shfl_sync(0xffffffffu, my_run, T);
+        if (base >= n_run || base - iss >= 16) continue;
+        const int64_t f0 = __shfl_sync(0xffffffffu, my_f0, T);
+        const int64_t wk = int64_t(blockIdx.x) * teams + T;
+        int4* ring = reinterpret_cast<int4*>(smem + p.off_desc) + T * kDescRing;
+        const int i = base + lane;
+        if (i < n_run) {
+          const int64_t f = f0 + i;
+          int lo = 0, hi = p.num_seqs - 1;
+          while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
+          }
+          const int seq = lo;
+          const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
+          const int pg = int(f - p0);
+          const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
+          const int s = pg / pps;
+          int split_end = (s + 1) * pps;
+          if (split_end > n_pages) split_end = n_pages;
+          const bool seg_first = (pg == s * pps) || (i == 0);
+          const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
+          const bool q_new = (i == 0) || (pg == 0);
+          int64_t phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
+          if (phys < 0 || phys >= p.num_blocks) {
+            atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
+            phys = 0;
+          }
+          int n_valid = p.seq_lens[seq] - pg * p.block_size;
+          if (n_valid > p.block_size) n_valid = p.block_size;
+          const int flags =
+              (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
+          ring[i & (kDescRing - 1)] =
+              make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
         }
-        q_owed = d.z;
+        __syncwarp();
+        if (lane == T) produced += 32;
       }
-      mbar_expect_tx(full_bar + issue_stage, page_bytes);
-      bulk_g2s(smem + ring_off + uint32_t(issue_stage) * page_bytes,
-               p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
-               full_bar + issue_stage);
-      ++issue_idx;
-      if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
-      empty_ok = issue_idx < stages;  // the first pass over the ring needs no poll
-    }
-    // after the pages: the poll of the query's counter is a round trip to L2
-    if (with_q) pump_q();
-  };
 
-  if (leader && n_run > 0) {
-    produce_chunk(0);
-    if (lane == 0) pump(false);  // the query is asked for once the table is filled
+      // ---- this lane's team: issue every described page whose stage is free ---------------------
+      bool progress = false;
+      if (my_run > 0) {
+        const int limit = produced < my_run ? produced : my_run;
+        while (issue_idx < limit) {
+          if (issue_idx >= stages && !mbar_test_wait(my_empty + issue_stage, issue_phase)) break;
+          const int4 d = my_desc[issue_idx & (kDescRing - 1)];
+          if ((d.y >> 8) & kQNew) {
+            if (q_owed >= 0) break;  // the previous query copy has not gone out yet
+            q_owed = d.z;
+          }
+          mbar_expect_tx(my_full + issue_stage, page_bytes);
+          bulk_g2s(smem + my_ring + uint32_t(issue_stage) * page_bytes,
+                   p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
+                   my_full + issue_stage);
+          ++issue_idx;
+          if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
+          progress = true;
+        }
+        // the query copy waits for its buffer and, in the single-launch form, for the rotated
+        // rows (written by other CTAs' stores, read here by a bulk copy)
+        if (q_owed >= 0 && (q_issued == 0 || mbar_test_wait(my_qempty, (q_issued - 1) & 1))) {
+          bool rows_there = true;
+          if constexpr (FUSE != 0) {
+            rows_there = ld_acquire_u32(p.q_count + q_owed) >= uint32_t(q_tiles);
+            if (rows_there) fence_proxy_async();
+          }
+          if (rows_there) {
+            mbar_expect_tx(my_qfull, q_bytes);
+            bulk_g2s(smem + my_q, p.q_rot + int64_t(q_owed) * p.hq * D, q_bytes, my_qfull);
+            ++q_issued;
+            q_owed = -1;
+            progress = true;
+          }
+        }
+      }
+      const bool done = issue_idx >= my_run && q_owed < 0;
+      if (__all_sync(0xffffffffu, done)) break;
+      if (__any_sync(0xffffffffu, progress)) {
+        idle = 0;
+      } else {
+        __nanosleep(32);
+        if (++idle > kSpinLimit) {
+          if (lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+          break;
+        }
+      }
+    }
+    return;
   }
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+
+  // ---- compute warps: this team's run ---------------------------------------------------------
+  const int64_t wk = int64_t(blockIdx.x) * teams + team;
+  const int n_run = wk < active ? int(total * (wk + 1) / active - total * wk / active) : 0;
 
   // ---- look-up table -------------------------------------------------------------------------
-  for (int i = tid; i < 256 * 32; i += kDecodeThreads) {
+  for (int i = tid; i < 256 * 32; i += kComputeThreads) {
     const int e = i >> 5, l = i & 31;
     const uint32_t hi = e >> 4, lo = e & 15;
     // K entry: byte of one token -> (even coordinate, odd coordinate)
@@ -687,7 +735,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     }
   }
 
-  __syncthreads();  // the table is complete
+  compute_sync();  // the table is complete
   if (n_run > 0) {  // ---- phase b ----------------------------------------------------------
 
   // ---- per-warp constants -------------------------------------------------------------------
@@ -725,35 +773,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   bool timed_out = false, page_ready = false;
 #pragma unroll 1
   for (int it = 0; it < n_run; ++it) {
-    // ---- wait for the page (the leader keeps the copies going while it waits) -----------
-    if (leader) {
-      // chunk k (pages 32k..32k+31) is written while the team is at page 32k-16: the ring
-      // slots it overwrites held pages < 32k-32, which every warp has left (a warp is never
-      // more than `stages` <= 16 pages behind), and the pump never looks further than 16
-      // pages ahead
-      if ((it & 31) == 16) produce_chunk(it + 16);
-      if (lane == 0) pump();
-      if (!page_ready) {
-        uint32_t spins = 0;
-#pragma unroll 1
-        while (!mbar_try_wait(full_bar + stage, fphase)) {
-          if (lane == 0) pump();
-          if (++spins > kSpinLimit) {
-            timed_out = true;
-            break;
-          }
-        }
-      }
-      __syncwarp();
-    } else if (!page_ready && !mbar_wait(full_bar + stage, fphase)) {
+    // ---- wait for the page ----------------------------------------------------------------
+    if (!page_ready && !mbar_wait(full_bar + stage, fphase)) {
       timed_out = true;
+      break;
     }
-    if (timed_out) break;
-    // the poll for the next page goes out now and is read at the top of the next iteration
+    // a look at the next page's barrier goes out now and is read at the top of the next
+    // iteration (it never suspends the warp: the page may well still be on its way)
     {
       int ns = stage + 1, nph = fphase;
       if (ns == stages) { ns = 0; nph ^= 1; }
-      page_ready = (it + 1 < n_run) && mbar_try_wait(full_bar + ns, nph);
+      page_ready = (it + 1 < n_run) && mbar_test_wait(full_bar + ns, nph);
     }
     const int4 d = desc_ring[it & (kDescRing - 1)];
     const int n_valid = d.y & 0xff, flags = d.y >> 8;
@@ -766,21 +796,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 #pragma unroll
         for (int c = 0; c < 4; ++c) oacc[j][c] = 0.f;
       if (flags & kQNew) {
-        if (leader) {  // the copy may still be owed: keep the producer going
-          uint32_t spins = 0;
-#pragma unroll 1
-          while (!mbar_try_wait(qfull_bar, qcnt & 1)) {
-            if (lane == 0) pump();
-            if (++spins > kSpinLimit) {
-              timed_out = true;
-              break;
-            }
-          }
-          __syncwarp();
-        } else if (!mbar_wait(qfull_bar, qcnt & 1)) {
+        if (!mbar_wait(qfull_bar, qcnt & 1)) {
           timed_out = true;
+          break;
         }
-        if (timed_out) break;
         // lane (g,t), k-step s: coordinates of cache bytes (D/8)t + 2s, +1 of q head head*G+g
         const bool valid = g < group;
         const uint32_t qoff =
@@ -864,8 +883,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         mma_f16(sacc[0], a[0][0], a[0][1], a[0][2], a[0][3], qf[2 * w][0], qf[2 * w][1]);
         mma_f16(sacc[1], a[1][0], a[1][1], a[1][2], a[1][3], qf[2 * w + 1][0], qf[2 * w + 1][1]);
       }
-
-      if (leader && lane == 0) pump_poll();
 
       // ---------- online softmax in the accumulator layout ---------------------------------
       const bool ok_lo = tok0 + g < n_valid, ok_hi = tok0 + g + 8 < n_valid;
