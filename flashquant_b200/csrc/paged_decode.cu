@@ -50,7 +50,8 @@ constexpr int kMaxStages = 16;           // per team; the descriptor ring relies
 constexpr int kMaxSeqs = 2048;                  // page-count prefix lives in shared memory
 constexpr int kMaxSplits = 64;
 constexpr int kPartPad = 4;                     // partial row = D + 4 floats (acc, m, l, 0, 0)
-constexpr float kPScaleLog2 = 14.f;             // fp16 weights are scaled by 2^14
+constexpr float kPScaleLog2 = 8.f;              // fp16 weights are scaled by 2^8 ...
+constexpr float kMaxSlack = 6.f;                // ... and may exceed 1 by 2^6 before m is raised
 
 constexpr int kMergeHeads = 8;                  // query heads per merge job
 constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams + splits)
@@ -289,6 +290,8 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
   constexpr int ROWF = D + kPartPad;
   constexpr int HP = kComputeThreads / D;  // heads handled at a time
   constexpr int PASSES = kMergeHeads / HP;
+  constexpr int RP = kComputeThreads / 2 / D;  // heads covered at a time by the final rotation
+  constexpr int RH = kMergeHeads / RP;         // heads per thread there
   constexpr int TPG = kMergeHeads * D / 4;  // threads that cover 8 rows, four values each
   constexpr int G = kComputeThreads / TPG;   // groups of such threads
   constexpr int kBatch = 10;                // rows a thread keeps in flight
@@ -430,27 +433,31 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       }
       pi_ready = true;
     }
-    float acc[PASSES];
+    // out = o Pi: half of the threads, each with RH heads per value of Pi it reads (reading
+    // Pi from shared memory is what bounds this step)
+    if (tid < kComputeThreads / 2) {
+      float acc[RH];
 #pragma unroll
-    for (int ps = 0; ps < PASSES; ++ps) acc[ps] = 0.f;
-#pragma unroll 4
-    for (int k4 = 0; k4 < D; k4 += 4) {
-      const float b0 = pi_s[(k4 + 0) * D + d], b1 = pi_s[(k4 + 1) * D + d];
-      const float b2 = pi_s[(k4 + 2) * D + d], b3 = pi_s[(k4 + 3) * D + d];
+      for (int r = 0; r < RH; ++r) acc[r] = 0.f;
+#pragma unroll 2
+      for (int k4 = 0; k4 < D; k4 += 4) {
+        const float b0 = pi_s[(k4 + 0) * D + d], b1 = pi_s[(k4 + 1) * D + d];
+        const float b2 = pi_s[(k4 + 2) * D + d], b3 = pi_s[(k4 + 3) * D + d];
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
-        const float4 a = *reinterpret_cast<const float4*>(o_s + (hh0 + ps * HP) * D + k4);
-        acc[ps] = fmaf(a.x, b0, acc[ps]);
-        acc[ps] = fmaf(a.y, b1, acc[ps]);
-        acc[ps] = fmaf(a.z, b2, acc[ps]);
-        acc[ps] = fmaf(a.w, b3, acc[ps]);
+        for (int r = 0; r < RH; ++r) {
+          const float4 a = *reinterpret_cast<const float4*>(o_s + (hh0 + r * RP) * D + k4);
+          acc[r] = fmaf(a.x, b0, acc[r]);
+          acc[r] = fmaf(a.y, b1, acc[r]);
+          acc[r] = fmaf(a.z, b2, acc[r]);
+          acc[r] = fmaf(a.w, b3, acc[r]);
+        }
       }
-    }
 #pragma unroll
-    for (int ps = 0; ps < PASSES; ++ps) {
-      const int hh = hh0 + ps * HP;
-      if (h0 + hh < p.hq)
-        static_cast<T*>(p.out)[(int64_t(seq) * p.hq + h0 + hh) * D + d] = from_f32<T>(acc[ps]);
+      for (int r = 0; r < RH; ++r) {
+        const int hh = hh0 + r * RP;
+        if (h0 + hh < p.hq)
+          static_cast<T*>(p.out)[(int64_t(seq) * p.hq + h0 + hh) * D + d] = from_f32<T>(acc[r]);
+      }
     }
     compute_sync();  // scratch is reused by the next job
     // the last job of a sequence puts its counters back to zero for the next call
@@ -474,6 +481,9 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
 // time, one chunk ahead.  Warps of a team never synchronise with each other except through
 // the stage barriers, and every warp writes its own partial rows.
 // ------------------------------------------------------------------------------------
+#ifndef FQ_KMIX
+#define FQ_KMIX 1
+#endif
 constexpr uint32_t kLutStride = 256;  // bytes per table entry: K copy per lane, then V copy
 constexpr int kDescRing = 64;
 
@@ -599,6 +609,39 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     const uint32_t my_ring = p.off_ring + uint32_t(lane) * stages * page_bytes;
     const uint32_t my_q = p.off_q + uint32_t(lane) * q_bytes;
     int produced = 0, issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0, q_owed = -1;
+    // descriptor of run page i of team T
+    auto describe = [&](int T, int i, int n_run, int64_t f0) {
+      const int64_t wk = int64_t(blockIdx.x) * teams + T;
+      int4* ring = reinterpret_cast<int4*>(smem + p.off_desc) + T * kDescRing;
+      const int64_t f = f0 + i;
+      int lo = 0, hi = p.num_seqs - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
+      }
+      const int seq = lo;
+      const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
+      const int pg = int(f - p0);
+      const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
+      const int s = pg / pps;
+      int split_end = (s + 1) * pps;
+      if (split_end > n_pages) split_end = n_pages;
+      const bool seg_first = (pg == s * pps) || (i == 0);
+      const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
+      const bool q_new = (i == 0) || (pg == 0);
+      int64_t phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
+      if (phys < 0 || phys >= p.num_blocks) {
+        atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
+        phys = 0;
+      }
+      int n_valid = p.seq_lens[seq] - pg * p.block_size;
+      if (n_valid > p.block_size) n_valid = p.block_size;
+      const int flags =
+          (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
+      ring[i & (kDescRing - 1)] =
+          make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
+    };
+    bool first_round = true;
     uint32_t idle = 0;
 #pragma unroll 1
     while (true) {
@@ -607,47 +650,28 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       // than 16 described pages are left to issue; the ring slots it overwrites held pages
       // more than 16 behind the issue front, which every warp of the team has left (a warp is
       // never more than `stages` <= 16 pages behind it).
-#pragma unroll 1
-      for (int T = 0; T < teams; ++T) {
-        const int base = __shfl_sync(0xffffffffu, produced, T);
-        const int iss = __shfl_sync(0xffffffffu, issue_idx, T);
+      if (first_round) {
+        // the very first descriptors of all teams at once (32 / teams pages each), so that
+        // every team's first block-table read is in flight at the same time
+        first_round = false;
+        const int per = 32 / teams, T = lane / per, i = lane - T * per;
         const int n_run = __shfl_sync(0xffffffffu, my_run, T);
-        if (base >= n_run || base - iss >= 16) continue;
         const int64_t f0 = __shfl_sync(0xffffffffu, my_f0, T);
-        const int64_t wk = int64_t(blockIdx.x) * teams + T;
-        int4* ring = reinterpret_cast<int4*>(smem + p.off_desc) + T * kDescRing;
-        const int i = base + lane;
-        if (i < n_run) {
-          const int64_t f = f0 + i;
-          int lo = 0, hi = p.num_seqs - 1;
-          while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
-          }
-          const int seq = lo;
-          const int p0 = prefix[seq], n_pages = prefix[seq + 1] - p0;
-          const int pg = int(f - p0);
-          const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
-          const int s = pg / pps;
-          int split_end = (s + 1) * pps;
-          if (split_end > n_pages) split_end = n_pages;
-          const bool seg_first = (pg == s * pps) || (i == 0);
-          const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
-          const bool q_new = (i == 0) || (pg == 0);
-          int64_t phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
-          if (phys < 0 || phys >= p.num_blocks) {
-            atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
-            phys = 0;
-          }
-          int n_valid = p.seq_lens[seq] - pg * p.block_size;
-          if (n_valid > p.block_size) n_valid = p.block_size;
-          const int flags =
-              (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
-          ring[i & (kDescRing - 1)] =
-              make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
-        }
+        if (i < n_run) describe(T, i, n_run, f0);
         __syncwarp();
-        if (lane == T) produced += 32;
+        if (has_team) produced = per;
+      } else {
+#pragma unroll 1
+        for (int T = 0; T < teams; ++T) {
+          const int base = __shfl_sync(0xffffffffu, produced, T);
+          const int iss = __shfl_sync(0xffffffffu, issue_idx, T);
+          const int n_run = __shfl_sync(0xffffffffu, my_run, T);
+          if (base >= n_run || base - iss >= 16) continue;
+          const int64_t f0 = __shfl_sync(0xffffffffu, my_f0, T);
+          if (base + lane < n_run) describe(T, base + lane, n_run, f0);
+          __syncwarp();
+          if (lane == T) produced += 32;
+        }
       }
 
       // ---- this lane's team: issue every described page whose stage is free ---------------------
@@ -706,18 +730,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const int64_t wk = int64_t(blockIdx.x) * teams + team;
   const int n_run = wk < active ? int(total * (wk + 1) / active - total * wk / active) : 0;
 
-  // ---- look-up table -------------------------------------------------------------------------
-  for (int i = tid; i < 256 * 32; i += kComputeThreads) {
-    const int e = i >> 5, l = i & 31;
-    const uint32_t hi = e >> 4, lo = e & 15;
-    // K entry: byte of one token -> (even coordinate, odd coordinate)
-    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
-        uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
-        uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
-  }
-
   // ---- phase a: one rotated query tile per warp of the grid --------------------------------
   if constexpr (FUSE != 0) {
     for (int job = rot_job0; job < rot_jobs; job += gridDim.x * kCW) {
@@ -733,6 +745,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       __syncwarp();
       if (lane == 0) atomicAdd(p.q_count + seq, 1u);
     }
+  }
+
+  // ---- look-up table -------------------------------------------------------------------------
+  for (int i = tid; i < 256 * 32; i += kComputeThreads) {
+    const int e = i >> 5, l = i & 31;
+    const uint32_t hi = e >> 4, lo = e & 15;
+    // K entry: byte of one token -> (even coordinate, odd coordinate)
+    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
+        KPRMT ? uint32_t(cs[lo]) | (uint32_t(cs[hi]) << 16)
+              : uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
+    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
+        uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
   }
 
   compute_sync();  // the table is complete
@@ -859,7 +884,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       for (int w = 0; w < KW; ++w) {
         // word w of the lane's chunk = cache bytes 4w..4w+3 = k-steps 2w (bytes 0,1), 2w+1
         uint32_t a[2][4];
-        if constexpr (KPRMT) {
+        if (KPRMT && !(FQ_KMIX && (w & 1))) {
 #pragma unroll
           for (int hw = 0; hw < 2; ++hw) {
             const uint32_t sa = hw ? (ka[w] >> 16) : ka[w], sb = hw ? (kb[w] >> 16) : kb[w];
@@ -899,13 +924,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         s_hi[c] = (sacc[0][2 + c] + sacc[1][2 + c]) * ks_hi;
         mx[c] = fmaxf(ok_lo ? s_lo[c] + lv_lo : -INFINITY, ok_hi ? s_hi[c] + lv_hi : -INFINITY);
       }
-#pragma unroll
-      for (int o = 4; o < 32; o <<= 1) {
-        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-      }
-      const bool grew = (mx[0] > m_run[0]) || (mx[1] > m_run[1]);
+      // The reference exponent m only has to stay within kMaxSlack bits of the true running
+      // maximum (the weights then stay below 2^(kMaxSlack + kPScaleLog2) <= 2^14 in fp16), so
+      // the reduction over the 16 tokens and the rescaling run only when some lane's scores
+      // outgrow it by more than that - rarely, once the first tokens of a segment are in
+      const bool grew = (mx[0] > m_run[0] + kMaxSlack) || (mx[1] > m_run[1] + kMaxSlack);
       if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+        }
         const float n0 = fmaxf(m_run[0], mx[0]), n1 = fmaxf(m_run[1], mx[1]);
         const float a0 = (m_run[0] == -INFINITY) ? 0.f : fast_exp2(m_run[0] - n0);
         const float a1 = (m_run[1] == -INFINITY) ? 0.f : fast_exp2(m_run[1] - n1);
@@ -920,14 +949,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         m_run[1] = n1;
       }
       float w_lo[2], w_hi[2];
+      // the weight that meets the value codes carries the value norm and the fp16 scale;
+      // m >= s + max(lg2 n_v, -40) - kMaxSlack, so p * n_v <= 2^kMaxSlack and p <= 2^46
+      constexpr float kPScale = float(1 << int(kPScaleLog2));
+      const float vs_lo = nv_lo * kPScale, vs_hi = nv_hi * kPScale;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const float mref = (m_run[c] == -INFINITY) ? 0.f : m_run[c];
-        // lg2(0) = -inf makes the weight of a zero-norm value exactly 0
-        w_lo[c] = ok_lo ? fast_exp2(s_lo[c] + (lg_lo - mref + kPScaleLog2)) : 0.f;
-        w_hi[c] = ok_hi ? fast_exp2(s_hi[c] + (lg_hi - mref + kPScaleLog2)) : 0.f;
         const float p_lo = ok_lo ? fast_exp2(s_lo[c] - mref) : 0.f;
         const float p_hi = ok_hi ? fast_exp2(s_hi[c] - mref) : 0.f;
+        w_lo[c] = p_lo * vs_lo;
+        w_hi[c] = p_hi * vs_hi;
         l_run[c] += p_lo + p_hi;
       }
       // weights as the B operand of the PV product: transpose (token, head) -> (head, token)
@@ -990,7 +1022,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
       }
-      const float unscale = 1.f / 16384.f;  // 2^-kPScaleLog2
+      const float unscale = 1.f / float(1 << int(kPScaleLog2));
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int col = 2 * t + c;
