@@ -5,6 +5,7 @@ raises if ``libflashquant_b200.so`` has not been built (``python -m flashquant_b
 """
 
 from .kernels import (  # noqa: F401
+    HostDecodeStep,
     fused_tq_attention,
     paged_decode_partials,
     split_k_merge,

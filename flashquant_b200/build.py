@@ -27,8 +27,8 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE]
 
-KERNEL_SOURCES = ["capi.cu", "compress.cu", "decompress.cu", "paged_decode.cu", "prefill.cu", "rotate.cu",
-                  "no_alloc.cu"]
+KERNEL_SOURCES = ["capi.cu", "compress.cu", "decompress.cu", "paged_decode.cu", "prefill.cu",
+                  "rotate.cu", "host_step.cu"]
 
 
 def _sources():

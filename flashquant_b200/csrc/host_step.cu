@@ -1,0 +1,135 @@
+// One decode step with HOST buffers in and out: what an attention backend does per layer and
+// step when its inputs live on the host side of the boundary.
+//
+// Mirrors FlashQuantAttentionImpl._fused_decode_path (src/flashquant/vllm/impl.py:362-395):
+// compress the step's new K/V token of every sequence into the paged cache, then run the
+// fused paged decode.  Around those two launches this entry point does the copies itself -
+// six host-to-device copies into a caller-owned device staging area, one device-to-host copy
+// of the result - and waits for the stream, so that one C call is the whole step and no
+// interpreter time sits between the pieces.  (Letting the kernels read page-locked host
+// arrays in place was measured and is slower: the sequence lengths and the block table sit
+// at the head of the decode kernel's dependency chain, and every CTA would fetch them over
+// the bus.)
+#include "fq_common.cuh"
+
+namespace fq {
+
+struct StepLayout {
+  size_t q, k, v, slots, bt, sl, out, total;
+};
+
+static size_t up256_(size_t v) { return (v + 255) / 256 * 256; }
+
+static StepLayout step_layout(int num_seqs, int hq, int hkv, int d, int64_t bt_stride,
+                              int slot_is_int64) {
+  StepLayout L{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = up256_(off + bytes);
+    return at;
+  };
+  L.q = take(size_t(num_seqs) * hq * d * 2);
+  L.k = take(size_t(num_seqs) * hkv * d * 2);
+  L.v = take(size_t(num_seqs) * hkv * d * 2);
+  L.slots = take(size_t(num_seqs) * (slot_is_int64 ? 8 : 4));
+  L.bt = take(size_t(num_seqs) * size_t(bt_stride) * 4);
+  L.sl = take(size_t(num_seqs) * 4);
+  L.out = take(size_t(num_seqs) * hq * d * 2);
+  L.total = off;
+  return L;
+}
+
+}  // namespace fq
+
+using namespace fq;
+
+extern "C" size_t fq_decode_step_host_staging_bytes(int num_seqs, int num_q_heads,
+                                                    int num_kv_heads, int head_dim,
+                                                    int64_t block_table_stride,
+                                                    int slot_is_int64) {
+  if (num_seqs < 0 || num_q_heads < 0 || num_kv_heads < 0 || head_dim < 0 || block_table_stride < 0)
+    return 0;
+  return step_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, block_table_stride,
+                     slot_is_int64)
+      .total;
+}
+
+extern "C" int fq_decode_step_host(
+    const void* q_host, const void* key_host, const void* value_host, fq_dtype dtype,
+    const void* slot_mapping_host, int slot_is_int64, const int32_t* block_table_host,
+    int64_t block_table_stride, const int32_t* seq_lens_host, uint8_t* kv_cache,
+    uint8_t* kq_cache, const float* rotation, const float* boundaries_k, int n_boundaries_k,
+    const float* centroids_k, int n_centroids_k, const float* boundaries_v, int n_boundaries_v,
+    const float* centroids_v, int n_centroids_v, const float* qjl, int num_seqs,
+    int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+    float sm_scale, int num_splits, void* out_host, void* staging, size_t staging_bytes,
+    void* workspace, size_t workspace_bytes, fq_stream_t stream_) {
+  FQ_REQUIRE(q_host && key_host && value_host && slot_mapping_host && block_table_host &&
+                 seq_lens_host && out_host,
+             FQ_ERR_INVALID_ARGUMENT, "decode step: null host pointer");
+  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
+             "decode step: q, key and value must be fp16 or bf16");
+  FQ_REQUIRE(num_seqs >= 0 && num_q_heads >= 1 && num_kv_heads >= 1 && head_dim >= 1 &&
+                 block_table_stride >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "decode step: negative size");
+  FQ_REQUIRE(staging && aligned(staging, 256), FQ_ERR_WORKSPACE,
+             "decode step: staging is null or not 256-byte aligned");
+  const StepLayout L = step_layout(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                   block_table_stride, slot_is_int64);
+  FQ_REQUIRE(staging_bytes >= L.total, FQ_ERR_WORKSPACE,
+             "decode step: staging has %zu bytes, %zu needed", staging_bytes, L.total);
+  if (num_seqs == 0) return FQ_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  unsigned char* st = static_cast<unsigned char*>(staging);
+  const size_t n = size_t(num_seqs);
+  struct Copy {
+    size_t off;
+    const void* src;
+    size_t bytes;
+  };
+  const Copy copies[6] = {
+      {L.sl, seq_lens_host, n * 4},
+      {L.bt, block_table_host, n * size_t(block_table_stride) * 4},
+      {L.k, key_host, n * num_kv_heads * head_dim * 2},
+      {L.v, value_host, n * num_kv_heads * head_dim * 2},
+      {L.slots, slot_mapping_host, n * (slot_is_int64 ? 8 : 4)},
+      {L.q, q_host, n * num_q_heads * head_dim * 2},
+  };
+  for (const Copy& c : copies) {
+    cudaError_t e = cudaMemcpyAsync(st + c.off, c.src, c.bytes, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "decode step: host-to-device copy: %s", cudaGetErrorString(e));
+  }
+  const void *q_d = st + L.q, *k_d = st + L.k, *v_d = st + L.v, *slots_d = st + L.slots;
+  const void *bt_d = st + L.bt, *sl_d = st + L.sl;
+  void* out_d = st + L.out;
+  int rc;
+  const int64_t num_slots = num_blocks * block_size;
+  if (kq_cache) {
+    rc = fq_tq4_compress_append_qjl(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
+                                    int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
+                                    n_boundaries_k, centroids_k, boundaries_v, n_boundaries_v, qjl,
+                                    kv_cache, kq_cache, num_slots, slots_d, slot_is_int64,
+                                    stream_);
+  } else {
+    rc = fq_tq4_compress_append(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
+                                int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
+                                n_boundaries_k, boundaries_v, n_boundaries_v, kv_cache, num_slots,
+                                slots_d, slot_is_int64, stream_);
+  }
+  if (rc != FQ_OK) return rc;
+  rc = fq_split_k_paged_decode(q_d, dtype, kv_cache, static_cast<const int32_t*>(bt_d),
+                               block_table_stride, static_cast<const int32_t*>(sl_d), centroids_k,
+                               n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs,
+                               num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
+                               sm_scale, out_d, num_splits, workspace, workspace_bytes,
+                               stream_);
+  if (rc != FQ_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(out_host, out_d, n * num_q_heads * head_dim * 2,
+                                  cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "decode step: result copy or synchronise: %s", cudaGetErrorString(e));
+  return FQ_OK;
+}

@@ -295,6 +295,75 @@ def split_k_paged_decode(
     return out
 
 
+class HostDecodeStep:
+    """One decode step with host tensors in and out (``fq_decode_step_host``).
+
+    The host-side form of ``FlashQuantAttentionImpl._fused_decode_path``
+    (src/flashquant/vllm/impl.py:362-395): the step's new K/V token of every sequence is
+    compressed into the paged cache, then the fused paged decode runs.  The object binds what
+    does not change between steps (cache, constants, shapes, device scratch); ``__call__``
+    takes the step's host tensors - pinned memory keeps the copies asynchronous - and returns
+    after the result has landed in ``out_host``.
+    """
+
+    def __init__(self, kv_cache, kq_cache, rotation, boundaries_k, centroids_k, boundaries_v,
+                 centroids_v, qjl_matrix, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                 block_size, block_table_stride, dtype=torch.bfloat16, sm_scale=None,
+                 num_splits=0, slot_dtype=torch.int64):
+        N.require_cuda(kv_cache)
+        dev = kv_cache.device
+        self.lib = N.load()
+        self.dev = dev
+        self.kv_cache, self.kq_cache = kv_cache, kq_cache
+        if kq_cache is not None and qjl_matrix is None:
+            raise ValueError("a QJL side plane needs the QJL matrix")
+        self.consts = [_f32(t, dev) if t is not None else None for t in
+                       (rotation, boundaries_k, centroids_k, boundaries_v, centroids_v, qjl_matrix)]
+        self.shape = (num_seqs, num_q_heads, num_kv_heads, head_dim, block_size)
+        self.bt_stride = int(block_table_stride)
+        self.dtype = dtype
+        self.slot_is_int64 = 1 if slot_dtype == torch.int64 else 0
+        self.slot_dtype = slot_dtype
+        self.sm_scale = float(sm_scale if sm_scale is not None else 1.0 / math.sqrt(head_dim))
+        self.num_splits = int(num_splits)
+        need = self.lib.fq_decode_step_host_staging_bytes(
+            num_seqs, num_q_heads, num_kv_heads, head_dim, self.bt_stride, self.slot_is_int64)
+        self.staging = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        self.workspace = decode_workspace(dev, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                          num_splits)
+
+    def __call__(self, q_host, key_host, value_host, slot_mapping_host, block_table_host,
+                 seq_lens_host, out_host, kv_cache=None, kq_cache=None):
+        """``kv_cache`` / ``kq_cache`` override the bound cache for this step (same shapes)."""
+        num_seqs, hq, hkv, d, bs = self.shape
+        kv_cache = self.kv_cache if kv_cache is None else kv_cache
+        kq_cache = self.kq_cache if kq_cache is None else kq_cache
+        for t, shape, dt in ((q_host, (num_seqs, hq, d), self.dtype),
+                             (out_host, (num_seqs, hq, d), self.dtype),
+                             (key_host, (num_seqs, hkv, d), self.dtype),
+                             (value_host, (num_seqs, hkv, d), self.dtype),
+                             (slot_mapping_host, (num_seqs,), self.slot_dtype),
+                             (block_table_host, (num_seqs, self.bt_stride), torch.int32),
+                             (seq_lens_host, (num_seqs,), torch.int32)):
+            if t.device.type != "cpu" or tuple(t.shape) != shape or t.dtype != dt or \
+                    not t.is_contiguous():
+                raise ValueError(f"host tensor of shape {tuple(t.shape)} / {t.dtype}: expected "
+                                 f"contiguous CPU {shape} / {dt}")
+        rot, bk, ck, bv, cv, qjl = self.consts
+        N.check(self.lib.fq_decode_step_host(
+            q_host.data_ptr(), key_host.data_ptr(), value_host.data_ptr(),
+            N.dtype_code(self.dtype), slot_mapping_host.data_ptr(), self.slot_is_int64,
+            block_table_host.data_ptr(), self.bt_stride, seq_lens_host.data_ptr(),
+            N.ptr(kv_cache), N.ptr(kq_cache) if kq_cache is not None else None,
+            N.ptr(rot), N.ptr(bk), bk.numel(), N.ptr(ck), ck.numel(), N.ptr(bv), bv.numel(),
+            N.ptr(cv), cv.numel(), N.ptr(qjl) if qjl is not None else None, num_seqs, hq, hkv, d,
+            bs, kv_cache.shape[0], self.sm_scale, self.num_splits, out_host.data_ptr(),
+            N.ptr(self.staging),
+            self.staging.numel(), N.ptr(self.workspace), self.workspace.numel(),
+            N.stream_ptr(self.dev)))
+        return out_host
+
+
 def paged_decode_partials(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
                           num_kv_heads, head_dim, block_size, num_splits=0, sm_scale=None,
                           partials=None, workspace=None) -> torch.Tensor:

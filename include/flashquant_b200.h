@@ -276,6 +276,41 @@ int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed
                           int is_causal, void* out, void* workspace, size_t workspace_bytes,
                           fq_stream_t stream);
 
+/*
+ * One decode step with HOST buffers: the host-side form of
+ * FlashQuantAttentionImpl._fused_decode_path (src/flashquant/vllm/impl.py:362-395), which
+ * compresses the step's new K/V token of every sequence into the paged cache and then runs
+ * the fused paged decode.  Here the inputs of the step are host arrays (pinned memory makes
+ * the copies asynchronous): they are copied into `staging` on the device, the two kernels
+ * run, the result is copied to out_host and the stream is synchronised before returning.
+ *   q_host, out_host        (num_seqs, num_q_heads, head_dim) of `dtype` (FQ_F16 / FQ_BF16)
+ *   key_host, value_host    (num_seqs, num_kv_heads, head_dim): one new token per sequence
+ *   slot_mapping_host       num_seqs cache rows for the new tokens (int64 or int32)
+ *   block_table_host        (num_seqs, block_table_stride) int32;  seq_lens_host (num_seqs)
+ *                           int32, lengths that already count the new token
+ *   kv_cache, kq_cache      device-resident packed cache and QJL side plane; kq_cache NULL
+ *                           selects the one-stage quantiser for K (fq_tq4_compress_append),
+ *                           otherwise fq_tq4_compress_append_qjl is used and qjl is required
+ *   rotation ... qjl        device-resident constants, as for the calls this one is made of
+ *   staging                 device scratch, 256-byte aligned, at least
+ *                           fq_decode_step_host_staging_bytes(...) bytes
+ *   workspace               as for fq_split_k_paged_decode
+ */
+size_t fq_decode_step_host_staging_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
+                                         int head_dim, int64_t block_table_stride,
+                                         int slot_is_int64);
+int fq_decode_step_host(const void* q_host, const void* key_host, const void* value_host,
+                        fq_dtype dtype, const void* slot_mapping_host, int slot_is_int64,
+                        const int32_t* block_table_host, int64_t block_table_stride,
+                        const int32_t* seq_lens_host, uint8_t* kv_cache, uint8_t* kq_cache,
+                        const float* rotation, const float* boundaries_k, int n_boundaries_k,
+                        const float* centroids_k, int n_centroids_k, const float* boundaries_v,
+                        int n_boundaries_v, const float* centroids_v, int n_centroids_v,
+                        const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads,
+                        int head_dim, int block_size, int64_t num_blocks, float sm_scale,
+                        int num_splits, void* out_host, void* staging, size_t staging_bytes,
+                        void* workspace, size_t workspace_bytes, fq_stream_t stream);
+
 /* Copies the device status word of a decode workspace to *status (synchronises stream). */
 int fq_workspace_status(const void* workspace, uint32_t* status, fq_stream_t stream);
 

@@ -235,3 +235,50 @@ def test_long_sequence_spread_over_every_team(consts):
     ref = run_oracle(w, cache, consts)
     for splits in (0, 5):
         attention_close(run_gpu(w, cache, consts, num_splits=splits), ref)
+
+
+@pytest.mark.parametrize("with_qjl,pinned", [(False, True), (True, True), (True, False)])
+def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
+    """fq_decode_step_host = copies + compress-on-append + decode: same bytes as the pieces,
+    with page-locked and with pageable host arrays."""
+    d, hkv, hq, bs = 128, 8, 32, 16
+    w = W.decode_workload(num_q_heads=hq, num_kv_heads=hkv, head_dim=d, block_size=bs, cfg=1,
+                          seq_lens=[33, 1, 700, 16, 257])
+    grown = fill_cache_cpu(w, consts).to(DEV)
+    rot, S = consts["rotation_128_0"], consts["qjl_128_0"]
+    bk, ck = consts["boundaries_128_3"], consts["centroids_128_3"]
+    bv, cv = consts["boundaries_128_4"], consts["centroids_128_4"]
+    # the step appends one more token to every sequence, in the row after its last one (every
+    # sequence owns as many pages as the longest, so the row exists)
+    new_k, new_v = W.make_kv(w.num_seqs, hkv, d, 9, torch.bfloat16)
+    bt = w.block_table
+    pos = w.seq_lens.long()
+    new_slots = bt[torch.arange(w.num_seqs), pos // bs].long() * bs + pos % bs
+    lens = w.seq_lens + 1
+    plane = torch.zeros(grown.shape[0], bs, hkv * (d // 8 + 4), dtype=torch.uint8, device=DEV)
+
+    # the pieces, on device tensors
+    ref_cache, ref_plane = grown.clone(), plane.clone()
+    if with_qjl:
+        K.tq4_compress_append_qjl(new_k.to(DEV), new_v.to(DEV), ref_cache, ref_plane,
+                                  new_slots.to(DEV), rot, bk, ck, bv, S)
+    else:
+        K.tq4_compress_append(new_k.to(DEV), new_v.to(DEV), ref_cache, new_slots.to(DEV), rot, bk, bv)
+    ref = K.split_k_paged_decode(w.q.to(DEV), ref_cache, bt.to(DEV), lens.to(DEV), ck, cv, rot,
+                                 hkv, d, bs, num_splits=2)
+
+    # the one call, on host tensors
+    step = K.HostDecodeStep(grown, plane if with_qjl else None, rot, bk, ck, bv, cv,
+                            S if with_qjl else None, w.num_seqs, hq, hkv, d, bs, bt.shape[1],
+                            num_splits=2)
+    host = (lambda t: t.contiguous().pin_memory()) if pinned else (lambda t: t.contiguous().clone())
+    hout = host(torch.zeros_like(w.q))
+    step(host(w.q), host(new_k), host(new_v), host(new_slots), host(bt), host(lens), hout)
+    assert torch.equal(grown, ref_cache)
+    if with_qjl:
+        assert torch.equal(plane, ref_plane)
+    assert torch.equal(hout.view(torch.int16), ref.cpu().view(torch.int16))
+    assert K.workspace_status(step.workspace) == 0
+    # and against the oracle end to end
+    attention_close(hout, O.split_k_paged_decode(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot, hkv,
+                                                 d, bs, None))
