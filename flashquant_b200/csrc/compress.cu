@@ -1,21 +1,27 @@
 // TQ4 compress / compress-on-append / two-stage (QJL) quantiser for sm_100a.
 //
-// One persistent CTA per SM keeps the rotation (and, for the two-stage quantiser, Pi and
-// S^T as well) resident in shared memory as fp32 and walks over tiles of vectors.  The
-// rotation is an fp32 FMA contraction in the reference's operation order (normalise, then
-// rotate), because the 4-bit codes must match a CPU sgemm to within the spacing of fp32:
-// a coordinate closer than ~1e-7 to a Lloyd-Max boundary may land on either side.
+// The contractions (y = x_hat Pi^T, x_tilde = y_tilde Pi, r S^T) run on the tensor pipe with
+// fp32-level accuracy: every operand is split into two fp16 terms, hi = fp16(v) and
+// lo' = fp16((v - hi) * 2048), and a product is accumulated as hi*hi into one fp32 accumulator
+// and hi*lo' + lo'*hi into a second one that is scaled by 2^-11 at the end (the lo*lo term,
+// 2^-22 of the product, is dropped).  That keeps the codes within the reference's own sgemm
+// rounding of a Lloyd-Max boundary (a coordinate closer than ~1e-7 to a boundary may land on
+// either side with any summation order) at a third of the multiply-add issue slots of an fp32
+// FMA contraction, which was the bound of this kernel before.
 //
-// Work split inside a CTA of 8 warps: a warp owns TV/8 vectors of the tile end to end
-// (load, norm, three contractions, pack, store), a lane owns D/32 consecutive output
-// coordinates of each of them.  Nothing but the matrices is shared between warps, so the
-// tile loop needs no block-wide barrier.
+// A CTA of 16 warps keeps the matrices resident in shared memory as fp16 hi / lo' planes (the
+// same bytes as fp32) and walks over tiles of 16 vectors: K of the tile, then V.  Warp w
+// loads and normalises vector w of the tile and owns column tile w of every product
+// (fragments by ldmatrix: three loads and three MMAs per 16 values of k); the left operand
+// (x_hat, then the centroid vector, then the residual) is exchanged through shared memory as
+// hi / lo' planes, so a K tile of the two-stage quantiser costs six block-wide barriers.  The operation order is the
+// reference's (normalise, then rotate); the tie rule is bucketize(right=False).
 #include "fq_common.cuh"
 
 namespace fq {
 
-constexpr int kCompressThreads = 256;
-constexpr int kCompressWarps = 8;
+constexpr int kCompressThreads = 512;
+constexpr int kCompressWarps = 16;
 
 struct CompressArgs {
   const void* src[2];  // [0]: K (or the only source), [1]: V
@@ -44,50 +50,31 @@ struct CompressArgs {
   int64_t num_slots;
 };
 
-template <int D, int TV, bool QJL>
+constexpr int kTileRows = 16;         // vectors per tile = rows of one MMA
+constexpr float kLoScale = 2048.f;    // lo' = (v - hi) * 2^11
+constexpr float kLoUnscale = 1.f / 2048.f;
+
+// Shared-memory plan.  Matrices and left operands are fp16 planes with rows padded by 8
+// halves: fragment loads (4 bytes at row g / column pair t, or row n = g) then hit 32 banks.
+template <int D, bool QJL>
 struct CompressSmem {
-  static constexpr int kLda = D + 4;
-  static constexpr size_t kMatBytes = size_t(D) * D * sizeof(float);
-  static constexpr size_t kBytes =
-      kMatBytes * (QJL ? 3 : 1) + size_t(TV) * kLda * sizeof(float) + 2 * 16 * sizeof(float) +
-      16 * sizeof(float);
+  static constexpr int kLd = D + 8;                        // halves per row
+  static constexpr size_t kPlane = size_t(D) * kLd * 2;    // one matrix plane, bytes
+  static constexpr size_t kAPlane = size_t(kTileRows) * kLd * 2;
+  static constexpr int kMats = QJL ? 3 : 1;
+  static constexpr size_t kOffA = kPlane * 2 * kMats;      // hi and lo' plane per matrix
+  static constexpr size_t kOffX = kOffA + 2 * kAPlane;      // the tile's vectors as fp32
+  static constexpr size_t kOffMeta = kOffX + (QJL ? size_t(kTileRows) * (D + 8) * 4 : 0);
+  // meta: nrm[16] f32, gpart[16][16] f32, bnd[2][16] f32, cent[16] f32, slot[16] i64, head[16] i32
+  static constexpr size_t kBytes = kOffMeta + (16 + 256 + 32 + 16) * 4 + 16 * 8 + 16 * 4;
 };
 
-// acc[v][j] += sum_k A[v][k] * B[k][lane*JT + j]
-template <int D, int VPW, int JT>
-__device__ __forceinline__ void tile_matmul(const float* __restrict__ a_rows, int lda,
-                                            const float* __restrict__ b, int lane,
-                                            float (&acc)[VPW][JT]) {
-#pragma unroll
-  for (int v = 0; v < VPW; ++v)
-#pragma unroll
-    for (int j = 0; j < JT; ++j) acc[v][j] = 0.f;
-#pragma unroll 2
-  for (int k4 = 0; k4 < D; k4 += 4) {
-    float bb[4][JT];
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      const float* bp = b + (k4 + kk) * D + lane * JT;
-      if constexpr (JT == 4) {
-        float4 t = *reinterpret_cast<const float4*>(bp);
-        bb[kk][0] = t.x; bb[kk][1] = t.y; bb[kk][2] = t.z; bb[kk][3] = t.w;
-      } else {
-        float2 t = *reinterpret_cast<const float2*>(bp);
-        bb[kk][0] = t.x; bb[kk][1] = t.y;
-      }
-    }
-#pragma unroll
-    for (int v = 0; v < VPW; ++v) {
-      float4 a = *reinterpret_cast<const float4*>(a_rows + v * lda + k4);
-#pragma unroll
-      for (int j = 0; j < JT; ++j) {
-        acc[v][j] = fmaf(a.x, bb[0][j], acc[v][j]);
-        acc[v][j] = fmaf(a.y, bb[1][j], acc[v][j]);
-        acc[v][j] = fmaf(a.z, bb[2][j], acc[v][j]);
-        acc[v][j] = fmaf(a.w, bb[3][j], acc[v][j]);
-      }
-    }
-  }
+__device__ __forceinline__ void split_hi_lo(float v, __half& hi, __half& lo) {
+  hi = __float2half_rn(v);
+  lo = __float2half_rn((v - __half2float(hi)) * kLoScale);
+}
+__device__ __forceinline__ uint32_t pack_h2(__half a, __half b) {
+  return uint32_t(__half_as_ushort(a)) | (uint32_t(__half_as_ushort(b)) << 16);
 }
 
 // index = #{b : b < y} over an ascending table padded with +inf to 15 entries
@@ -99,41 +86,116 @@ __device__ __forceinline__ int bucketize15(float y, const float* __restrict__ sb
   return idx;
 }
 
-template <int D, int TV, int DT, bool QJL>
-__global__ void __launch_bounds__(kCompressThreads, 1) compress_kernel(CompressArgs p) {
+// Stage one D x D matrix as hi / lo' planes: plane[n][k] = get(n, k).  Thread i walks the
+// matrix in the order that makes `get` read global memory contiguously (`k_fast`: k runs
+// fastest, else n).
+template <int D, typename Get>
+__device__ __forceinline__ void stage_matrix(__half* hi, __half* lo, int ld, bool k_fast, Get get,
+                                             int tid) {
+  constexpr int kPer = D * D / kCompressThreads;  // elements per thread
+  constexpr int kBatch = kPer < 16 ? kPer : 16;   // loads in flight per thread
+  static_assert(kPer % kBatch == 0, "matrix size must be a multiple of the batch");
+#pragma unroll 1
+  for (int b = 0; b < kPer; b += kBatch) {
+    float v[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = tid + (b + u) * kCompressThreads;
+      v[u] = get(k_fast ? i / D : i % D, k_fast ? i % D : i / D);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = tid + (b + u) * kCompressThreads;
+      const int n = k_fast ? i / D : i % D, k = k_fast ? i % D : i / D;
+      __half h, l;
+      split_hi_lo(v[u], h, l);
+      hi[n * ld + k] = h;
+      lo[n * ld + k] = l;
+    }
+  }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row_ptr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(row_ptr)));
+}
+
+// acc[c] = sum_k A[row][k] * B[n][k] for column tile `nt` (C-fragment layout: c0,c1 = row g,
+// columns 8*nt + 2t, +1; c2,c3 = row g+8), A and B as hi / lo' planes.  Three ldmatrix and
+// three MMAs per 16 values of k.
+template <int D>
+__device__ __forceinline__ void plane_mma(const __half* __restrict__ ah,
+                                          const __half* __restrict__ al,
+                                          const __half* __restrict__ bh,
+                                          const __half* __restrict__ bl, int ld, int nt, int lane,
+                                          float (&acc)[4]) {
+  const int j = lane >> 3, r = lane & 7;  // ldmatrix: lanes 8j..8j+7 give the rows of matrix j
+  // A: matrix j = rows 8*(j&1).., k-segment j>>1;  B: matrix j = plane j>>1 (hi, lo'), k-segment j&1
+  const __half* pa_h = ah + ((j & 1) * 8 + r) * ld + 8 * (j >> 1);
+  const __half* pa_l = al + ((j & 1) * 8 + r) * ld + 8 * (j >> 1);
+  const __half* pb = ((j >> 1) ? bl : bh) + (8 * nt + r) * ld + 8 * (j & 1);
+  float hi[4] = {0.f, 0.f, 0.f, 0.f}, co[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t xh[4], xl[4], b[4];  // b: b0 hi, b1 hi, b0 lo', b1 lo'
+    ldmatrix_x4(xh, pa_h + 16 * ks);
+    ldmatrix_x4(b, pb + 16 * ks);
+    ldmatrix_x4(xl, pa_l + 16 * ks);
+    mma_f16(hi, xh[0], xh[1], xh[2], xh[3], b[0], b[1]);
+    mma_f16(co, xh[0], xh[1], xh[2], xh[3], b[2], b[3]);
+    mma_f16(co, xl[0], xl[1], xl[2], xl[3], b[0], b[1]);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) acc[c] = fmaf(co[c], kLoUnscale, hi[c]);
+}
+
+template <int D, int DT, bool QJL>
+__global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel(CompressArgs p) {
   using T = typename Elem<DT>::type;
-  using S = CompressSmem<D, TV, QJL>;
-  constexpr int VPW = TV / kCompressWarps;
-  constexpr int JT = D / 32;
-  constexpr int LDA = S::kLda;
-  static_assert(JT == 4 || JT == 2, "head_dim must be 64 or 128");
+  using S = CompressSmem<D, QJL>;
+  constexpr int LD = S::kLd;
+  constexpr int JT = D / 32;   // elements per lane when a warp walks one vector
+  constexpr int NT = D / 8;    // column tiles of a product: warps 0 .. NT-1 take one each
+  static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* b_rot = reinterpret_cast<float*>(smem_raw);           // [k][j] = Pi[j][k]
-  float* b_pi = b_rot + (QJL ? D * D : 0);                     // [k][j] = Pi[k][j]
-  float* b_qjl = b_pi + (QJL ? D * D : 0);                     // [k][j] = S[j][k]
-  float* a_tile = b_rot + D * D * (QJL ? 3 : 1);               // [v][k], row stride LDA
-  float* s_bnd = a_tile + TV * LDA;                            // [2][16]
-  float* s_cent = s_bnd + 32;                                  // [16]
+  __half* m_hi[3];
+  __half* m_lo[3];
+#pragma unroll
+  for (int m = 0; m < 3; ++m) {
+    m_hi[m] = reinterpret_cast<__half*>(smem_raw + S::kPlane * 2 * (m < S::kMats ? m : 0));
+    m_lo[m] = m_hi[m] + D * LD;
+  }
+  __half* a_hi = reinterpret_cast<__half*>(smem_raw + S::kOffA);
+  __half* a_lo = a_hi + kTileRows * LD;
+  [[maybe_unused]] float* s_x = reinterpret_cast<float*>(smem_raw + S::kOffX);  // [16][D+8]
+  float* s_nrm = reinterpret_cast<float*>(smem_raw + S::kOffMeta);
+  float* s_gpart = s_nrm + 16;   // [16 warps][16 rows]
+  float* s_bnd = s_gpart + 256;  // [2][16]
+  float* s_cent = s_bnd + 32;    // [16]
+  int64_t* s_slot = reinterpret_cast<int64_t*>(s_cent + 16);
+  int* s_head = reinterpret_cast<int*>(s_slot + 16);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const bool col_warp = warp < NT;  // takes part in the products
 
-  // ---- resident matrices -----------------------------------------------------------
-  for (int i = tid; i < D * D; i += kCompressThreads) {
-    const int k = i / D, j = i % D;
-    float v;
-    if (p.rot_split) {
-      const float* m = (j & 1) ? p.mat_b : p.mat_a;
-      v = m[k * (D / 2) + (j >> 1)];
-    } else {
-      v = p.mat_a[j * D + k];
-    }
-    b_rot[i] = v;
-    if constexpr (QJL) {
-      b_pi[i] = p.mat_a[i];
-      b_qjl[i] = p.qjl[j * D + k];
-    }
+  // ---- resident matrices -----------------------------------------------------------------
+  // [0]: Pi as it is  (y = x_hat Pi^T:      B[k][n] = Pi[n][k])
+  // [1]: Pi transposed (x_tilde = y_tilde Pi: B[k][n] = Pi[k][n])
+  // [2]: S as it is   (r S^T:               B[k][n] = S[n][k])
+  if (p.rot_split) {
+    stage_matrix<D>(m_hi[0], m_lo[0], LD, false, [&](int n, int k) {
+      return ((n & 1) ? p.mat_b : p.mat_a)[k * (D / 2) + (n >> 1)];
+    }, tid);
+  } else {
+    stage_matrix<D>(m_hi[0], m_lo[0], LD, true, [&](int n, int k) { return p.mat_a[n * D + k]; }, tid);
+  }
+  if constexpr (QJL) {
+    stage_matrix<D>(m_hi[1], m_lo[1], LD, false, [&](int n, int k) { return p.mat_a[k * D + n]; }, tid);
+    stage_matrix<D>(m_hi[2], m_lo[2], LD, true, [&](int n, int k) { return p.qjl[n * D + k]; }, tid);
   }
   if (tid < 32) {
     const int s = tid >> 4, i = tid & 15;
@@ -144,142 +206,197 @@ __global__ void __launch_bounds__(kCompressThreads, 1) compress_kernel(CompressA
   __syncthreads();
 
   const int64_t n_vec = p.n_tokens * p.heads;
-  const int64_t n_tiles = (n_vec + TV - 1) / TV;
-  float* a_rows = a_tile + warp * VPW * LDA;
+  const int64_t n_tiles = (n_vec + kTileRows - 1) / kTileRows;
 
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    for (int s = 0; s < p.n_src; ++s) {
-      const T* src = reinterpret_cast<const T*>(p.src[s]);
-      const float* sb = s_bnd + 16 * s;
-      const int64_t v0 = tile * TV + warp * VPW;
-
-      // ---- load, norm, normalise ----------------------------------------------------
-      float nrm[VPW];
-      int64_t row[VPW];
-      int head[VPW];
-      const T* xptr[VPW];
+  // The vector of the next work item (tile, source) is requested before the current one is
+  // worked on, so that its latency hides behind the contractions.  Warp w holds row w.
+  struct Row {
+    float x[JT];
+    int64_t slot;
+    int head;
+  };
+  // (the host side keeps n_vec below 2^31: 32-bit index arithmetic, no 64-bit divisions)
+  const uint32_t heads = uint32_t(p.heads);
+  auto fetch = [&](uint32_t tile, int s, Row& f) {
+    const T* src = reinterpret_cast<const T*>(p.src[s]);
+    const uint32_t vec = tile * kTileRows + warp;
+    f.slot = -1;
+    f.head = 0;
 #pragma unroll
-      for (int v = 0; v < VPW; ++v) {
-        const int64_t vec = v0 + v;
-        float x[JT];
-        row[v] = -1;
-        head[v] = 0;
-        xptr[v] = nullptr;
-        if (vec < n_vec) {
-          const int64_t tok = vec / p.heads;
-          head[v] = int(vec - tok * p.heads);
-          xptr[v] = src + tok * p.token_stride + int64_t(head[v]) * D + lane * JT;
-          if constexpr (JT == 4) load4(xptr[v], x); else load2(xptr[v], x);
-          int64_t r = tok;
-          if (p.slots) {
-            r = p.slot64 ? reinterpret_cast<const int64_t*>(p.slots)[tok]
-                         : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok]);
-            if (r >= p.num_slots) r = -1;
-          }
-          row[v] = r;
-        } else {
-#pragma unroll
-          for (int j = 0; j < JT; ++j) x[j] = 0.f;
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < JT; ++j) ss = fmaf(x[j], x[j], ss);
-        ss = warp_sum(ss);
-        nrm[v] = sqrtf(ss);
-        const float denom = nrm[v] + 1e-10f;
-        float* ar = a_rows + v * LDA + lane * JT;
-#pragma unroll
-        for (int j = 0; j < JT; ++j) ar[j] = x[j] / denom;
+    for (int j = 0; j < JT; ++j) f.x[j] = 0.f;
+    if (vec < uint32_t(n_vec)) {
+      const uint32_t tok32 = vec / heads;
+      const int64_t tok = tok32;
+      f.head = int(vec - tok32 * heads);
+      const T* xp = src + tok * p.token_stride + int64_t(f.head) * D + lane * JT;
+      if constexpr (JT == 4) load4(xp, f.x); else load2(xp, f.x);
+      int64_t slot = tok;
+      if (p.slots) {
+        slot = p.slot64 ? reinterpret_cast<const int64_t*>(p.slots)[tok]
+                        : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok]);
+        if (slot >= p.num_slots) slot = -1;
       }
-      __syncwarp();
+      f.slot = slot;
+    }
+  };
+  Row cur, nxt;
+  uint32_t tile = blockIdx.x;
+  int s = 0;
+  if (tile < uint32_t(n_tiles)) fetch(tile, 0, cur);
 
-      // ---- y = x_hat Pi^T, codes --------------------------------------------------
-      float acc[VPW][JT];
-      tile_matmul<D, VPW, JT>(a_rows, LDA, b_rot, lane, acc);
-      int idx[VPW][JT];
+  while (tile < uint32_t(n_tiles)) {
+    const float* sb = s_bnd + 16 * s;
+    // the next work item: the other source of this tile, or the first source of the next tile
+    int s_next = s + 1;
+    uint32_t tile_next = tile;
+    if (s_next == p.n_src) {
+      s_next = 0;
+      tile_next = tile + gridDim.x;
+    }
+    if (tile_next < uint32_t(n_tiles)) fetch(tile_next, s_next, nxt);
+
+    // ---- norm, normalise, hi / lo' planes of x_hat -------------------------------------------
+    {
+      float ss = 0.f;
 #pragma unroll
-      for (int v = 0; v < VPW; ++v) {
+      for (int j = 0; j < JT; ++j) ss = fmaf(cur.x[j], cur.x[j], ss);
+      ss = warp_sum(ss);
+      const float nrm = sqrtf(ss);
+      // one reciprocal per vector instead of a division per coordinate: x_hat may differ from
+      // x / (n + 1e-10) in the last bit, far inside the rounding of the contraction
+      const float inv = 1.f / (nrm + 1e-10f);
+      __half h[JT], l[JT];
 #pragma unroll
-        for (int j = 0; j < JT; ++j) idx[v][j] = bucketize15(acc[v][j], sb);
-        if (row[v] >= 0) {
-          uint8_t* dst = p.code[s] + row[v] * p.code_row_stride +
-                         int64_t(head[v]) * p.code_head_stride + lane * (JT / 2);
-          if constexpr (JT == 4) {
-            const uint32_t two = uint32_t((idx[v][0] << 4) | idx[v][1]) |
-                                 (uint32_t((idx[v][2] << 4) | idx[v][3]) << 8);
-            *reinterpret_cast<uint16_t*>(dst) = uint16_t(two);
-          } else {
-            *dst = uint8_t((idx[v][0] << 4) | idx[v][1]);
-          }
-          if (lane == 0)
-            *reinterpret_cast<float*>(p.norm[s] + row[v] * p.norm_row_stride + head[v] * 4) =
-                nrm[v];
-        }
+      for (int j = 0; j < JT; ++j) split_hi_lo(cur.x[j] * inv, h[j], l[j]);
+      if constexpr (JT == 4) {
+        *reinterpret_cast<uint2*>(a_hi + warp * LD + lane * 4) =
+            make_uint2(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]));
+        *reinterpret_cast<uint2*>(a_lo + warp * LD + lane * 4) =
+            make_uint2(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]));
+      } else {
+        *reinterpret_cast<uint32_t*>(a_hi + warp * LD + lane * 2) = pack_h2(h[0], h[1]);
+        *reinterpret_cast<uint32_t*>(a_lo + warp * LD + lane * 2) = pack_h2(l[0], l[1]);
       }
-
       if constexpr (QJL) {
         if (s == 0) {
-          // ---- x_tilde = (c[code] Pi) n ; r = x - x_tilde ; gamma = |r| ----------------
-          __syncwarp();
+          float* xr = s_x + warp * (D + 8) + lane * JT;
 #pragma unroll
-          for (int v = 0; v < VPW; ++v) {
-            float* ar = a_rows + v * LDA + lane * JT;
-#pragma unroll
-            for (int j = 0; j < JT; ++j) ar[j] = s_cent[idx[v][j]];
-          }
-          __syncwarp();
-          tile_matmul<D, VPW, JT>(a_rows, LDA, b_pi, lane, acc);
-          __syncwarp();
-#pragma unroll
-          for (int v = 0; v < VPW; ++v) {
-            float x[JT];
-            if (xptr[v]) {
-              if constexpr (JT == 4) load4(xptr[v], x); else load2(xptr[v], x);
-            } else {
-#pragma unroll
-              for (int j = 0; j < JT; ++j) x[j] = 0.f;
-            }
-            float ss = 0.f;
-            float* ar = a_rows + v * LDA + lane * JT;
-#pragma unroll
-            for (int j = 0; j < JT; ++j) {
-              const float r = x[j] - acc[v][j] * nrm[v];
-              ar[j] = r;
-              ss = fmaf(r, r, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0 && row[v] >= 0)
-              *reinterpret_cast<float*>(p.gam + row[v] * p.gam_row_stride + head[v] * 4) =
-                  sqrtf(ss);
-          }
-          __syncwarp();
-          // ---- sign(r S^T) -----------------------------------------------------------
-          tile_matmul<D, VPW, JT>(a_rows, LDA, b_qjl, lane, acc);
-#pragma unroll
-          for (int v = 0; v < VPW; ++v) {
-            uint32_t bits = 0;
-#pragma unroll
-            for (int j = 0; j < JT; ++j) bits |= (acc[v][j] >= 0.f ? 1u : 0u) << j;
-            // 32 coordinates per word: lanes sharing lane/(32/JT) build one word
-            constexpr int LPW = 32 / JT;  // lanes per 32-bit word
-            uint32_t word = bits << (JT * (lane % LPW));
-#pragma unroll
-            for (int o = 1; o < LPW; o <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, o);
-            if ((lane % LPW) == 0 && row[v] >= 0)
-              *reinterpret_cast<uint32_t*>(p.sign + row[v] * p.sign_row_stride +
-                                           head[v] * (D / 8) + (lane / LPW) * 4) = word;
-          }
+          for (int j = 0; j < JT; ++j) xr[j] = cur.x[j];
         }
       }
-      __syncwarp();
+      if (lane == 0) {
+        s_nrm[warp] = nrm;
+        s_head[warp] = cur.head;
+        s_slot[warp] = cur.slot;
+        if (cur.slot >= 0)
+          *reinterpret_cast<float*>(p.norm[s] + cur.slot * p.norm_row_stride + cur.head * 4) = nrm;
+      }
     }
+    __syncthreads();
+
+    // ---- y = x_hat Pi^T, codes -------------------------------------------------------------
+    float acc[4];
+    int idx[4] = {0, 0, 0, 0};
+    const int64_t slot_lo = s_slot[g], slot_hi = s_slot[g + 8];
+    const int head_lo = s_head[g], head_hi = s_head[g + 8];
+    if (col_warp) {
+      plane_mma<D>(a_hi, a_lo, m_hi[0], m_lo[0], LD, warp, lane, acc);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) idx[c] = bucketize15(acc[c], sb);
+      // code byte = (even coordinate << 4) | odd coordinate; the four lanes of a row hold
+      // bytes 4*nt .. 4*nt+3 of it
+      uint32_t w_lo = uint32_t((idx[0] << 4) | idx[1]) << (8 * t);
+      uint32_t w_hi = uint32_t((idx[2] << 4) | idx[3]) << (8 * t);
+      w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 1);
+      w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 1);
+      w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 2);
+      w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 2);
+      if (t == 0 && slot_lo >= 0)
+        *reinterpret_cast<uint32_t*>(p.code[s] + slot_lo * p.code_row_stride +
+                                     int64_t(head_lo) * p.code_head_stride + 4 * warp) = w_lo;
+      if (t == 1 && slot_hi >= 0)
+        *reinterpret_cast<uint32_t*>(p.code[s] + slot_hi * p.code_row_stride +
+                                     int64_t(head_hi) * p.code_head_stride + 4 * warp) = w_hi;
+    }
+    __syncthreads();  // every warp has read x_hat: the planes may be overwritten
+
+    if constexpr (QJL) {
+      if (s == 0) {
+        // ---- x_tilde = (c[code] Pi) n ; r = x - x_tilde ; gamma = |r| ------------------------
+        const int col = 8 * warp + 2 * t;
+        if (col_warp) {
+          __half h[4], l[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) split_hi_lo(s_cent[idx[c]], h[c], l[c]);
+          *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
+          *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
+          *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
+          *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+        }
+        __syncthreads();
+        if (col_warp) plane_mma<D>(a_hi, a_lo, m_hi[1], m_lo[1], LD, warp, lane, acc);
+        __syncthreads();  // every warp has read the centroid planes
+        if (col_warp) {
+          const float n_lo = s_nrm[g], n_hi = s_nrm[g + 8];
+          const float2 x_lo = *reinterpret_cast<const float2*>(s_x + g * (D + 8) + col);
+          const float2 x_hi = *reinterpret_cast<const float2*>(s_x + (g + 8) * (D + 8) + col);
+          const float r0 = x_lo.x - acc[0] * n_lo, r1 = x_lo.y - acc[1] * n_lo;
+          const float r2 = x_hi.x - acc[2] * n_hi, r3 = x_hi.y - acc[3] * n_hi;
+          float ss_lo = fmaf(r0, r0, r1 * r1), ss_hi = fmaf(r2, r2, r3 * r3);
+          __half h[4], l[4];
+          split_hi_lo(r0, h[0], l[0]);
+          split_hi_lo(r1, h[1], l[1]);
+          split_hi_lo(r2, h[2], l[2]);
+          split_hi_lo(r3, h[3], l[3]);
+          *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
+          *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
+          *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
+          *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+          ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 1);
+          ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 1);
+          ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 2);
+          ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 2);
+          if (t == 0) {
+            s_gpart[warp * 16 + g] = ss_lo;
+            s_gpart[warp * 16 + g + 8] = ss_hi;
+          }
+        }
+        __syncthreads();
+        if (tid < 16 && s_slot[tid] >= 0) {
+          float ss = 0.f;
+#pragma unroll
+          for (int w = 0; w < NT; ++w) ss += s_gpart[w * 16 + tid];
+          *reinterpret_cast<float*>(p.gam + s_slot[tid] * p.gam_row_stride + s_head[tid] * 4) =
+              sqrtf(ss);
+        }
+        // ---- sign(r S^T): bit j%8 of byte j/8 is 1 for a projection >= 0 ---------------------
+        if (col_warp) {
+          plane_mma<D>(a_hi, a_lo, m_hi[2], m_lo[2], LD, warp, lane, acc);
+          uint32_t b_lo = ((acc[0] >= 0.f ? 1u : 0u) | (acc[1] >= 0.f ? 2u : 0u)) << (2 * t);
+          uint32_t b_hi = ((acc[2] >= 0.f ? 1u : 0u) | (acc[3] >= 0.f ? 2u : 0u)) << (2 * t);
+          b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 1);
+          b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 1);
+          b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 2);
+          b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 2);
+          // byte `warp` of the row's D/8 sign bytes
+          if (t == 0 && slot_lo >= 0)
+            p.sign[slot_lo * p.sign_row_stride + head_lo * (D / 8) + warp] = uint8_t(b_lo);
+          if (t == 1 && slot_hi >= 0)
+            p.sign[slot_hi * p.sign_row_stride + head_hi * (D / 8) + warp] = uint8_t(b_hi);
+        }
+        __syncthreads();  // planes and row data are rewritten by the next item
+      }
+    }
+    cur = nxt;
+    tile = tile_next;
+    s = s_next;
   }
 }
 
-template <int D, int TV, int DT, bool QJL>
+template <int D, int DT, bool QJL>
 static int launch_compress_t(const CompressArgs& a, cudaStream_t stream) {
-  using S = CompressSmem<D, TV, QJL>;
-  auto kern = compress_kernel<D, TV, DT, QJL>;
+  using S = CompressSmem<D, QJL>;
+  auto kern = compress_kernel<D, DT, QJL>;
   static thread_local int configured_device = -1;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail(FQ_ERR_CUDA, "cudaGetDevice failed");
@@ -294,8 +411,10 @@ static int launch_compress_t(const CompressArgs& a, cudaStream_t stream) {
     configured_device = dev;
   }
   const int64_t n_vec = a.n_tokens * a.heads;
-  const int64_t tiles = (n_vec + TV - 1) / TV;
+  const int64_t tiles = (n_vec + kTileRows - 1) / kTileRows;
   if (tiles == 0) return FQ_OK;
+  FQ_REQUIRE(n_vec < (int64_t(1) << 31) - 16 * 4096, FQ_ERR_UNSUPPORTED,
+             "compress: %lld vectors in one call (at most 2^31)", (long long)n_vec);
   const int per_sm = (S::kBytes <= 110 * 1024) ? 2 : 1;
   const int grid = int(tiles < int64_t(sm_count) * per_sm ? tiles : int64_t(sm_count) * per_sm);
   kern<<<grid, kCompressThreads, S::kBytes, stream>>>(a);
@@ -304,11 +423,10 @@ static int launch_compress_t(const CompressArgs& a, cudaStream_t stream) {
 
 template <int D, bool QJL>
 static int launch_compress_d(const CompressArgs& a, int dtype, cudaStream_t stream) {
-  constexpr int TV = QJL ? 32 : 64;
   switch (dtype) {
-    case FQ_F32: return launch_compress_t<D, TV, FQ_F32, QJL>(a, stream);
-    case FQ_F16: return launch_compress_t<D, TV, FQ_F16, QJL>(a, stream);
-    case FQ_BF16: return launch_compress_t<D, TV, FQ_BF16, QJL>(a, stream);
+    case FQ_F32: return launch_compress_t<D, FQ_F32, QJL>(a, stream);
+    case FQ_F16: return launch_compress_t<D, FQ_F16, QJL>(a, stream);
+    case FQ_BF16: return launch_compress_t<D, FQ_BF16, QJL>(a, stream);
   }
   return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
 }

@@ -136,11 +136,18 @@ def test_prod_quantize_vs_oracle_and_host_class(C):
     frac = bad.float().mean().item()
     assert frac <= 1e-4, f"sign mismatch fraction {frac:.2e}"
     if bad.any():
-        # a differing sign must belong to a projection that is ~0 relative to |r|
-        resid = k.float() - O.mse_dequantize(idx, norms, rot, c3)
+        # A differing sign must belong to a projection that is ~0 relative to |r|.  A vector
+        # whose code differs from the oracle's next to a boundary (allowed above) has another
+        # residual: its signs are judged against the residual of the codes the GPU stored.
+        gpu_idx = O.nibble_unpack(packed.cpu()).long()
+        resid = k.float() - O.mse_dequantize(gpu_idx, norms, rot, c3)
         proj = (resid.reshape(-1, 128).double() @ S.double().T).reshape(signs.shape)
         rel = proj.abs() / resid.double().norm(dim=-1, keepdim=True)
-        assert rel[bad].max().item() < 1e-5
+        own = torch.where(proj >= 0, 1.0, -1.0).to(got.dtype)
+        still_bad = got != own
+        assert rel[still_bad].max().item() < 1e-5 if still_bad.any() else True
+        same_codes = (gpu_idx == idx).all(dim=-1, keepdim=True).expand_as(bad)
+        assert rel[bad & same_codes].max().item() < 1e-5 if (bad & same_codes).any() else True
     # host class mirror
     q = fq.TurboQuantProd(128, 4, seed=0)
     q.mse_quantizer.rotation = rot  # identical matrices (QR is not reproducible across hosts)
