@@ -4,15 +4,48 @@
 // Mirrors FlashQuantAttentionImpl._fused_decode_path (src/flashquant/vllm/impl.py:362-395):
 // compress the step's new K/V token of every sequence into the paged cache, then run the
 // fused paged decode.  Around those two launches this entry point does the copies itself -
-// six host-to-device copies into a caller-owned device staging area, one device-to-host copy
-// of the result - and waits for the stream, so that one C call is the whole step and no
-// interpreter time sits between the pieces.  (Letting the kernels read page-locked host
+// six host-to-device copies into a caller-owned device staging area (those that only the
+// decode needs go through a side stream and overlap the compress-on-append), one
+// device-to-host copy of the result - and waits for the stream, so that one C call is the
+// whole step and no interpreter time sits between the pieces.  (Letting the kernels read page-locked host
 // arrays in place was measured and is slower: the sequence lengths and the block table sit
 // at the head of the decode kernel's dependency chain, and every CTA would fetch them over
 // the bus.)
+#include <mutex>
+
 #include "fq_common.cuh"
 
 namespace fq {
+
+// A second stream per device, so that the copies the decode needs (query, block table, lengths)
+// overlap the copies and the launch of the compress-on-append; created on first use.
+struct StepAux {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+static int step_aux(StepAux** out) {
+  constexpr int kMaxDevices = 64;
+  static StepAux aux[kMaxDevices];
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(FQ_ERR_CUDA, "decode step: cudaGetDevice: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  StepAux& a = aux[dev];
+  if (!a.stream) {
+    e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      a = StepAux{};
+      return fail(FQ_ERR_CUDA, "decode step: side stream: %s", cudaGetErrorString(e));
+    }
+  }
+  *out = &a;
+  return FQ_OK;
+}
 
 struct StepLayout {
   size_t q, k, v, slots, bt, sl, out, total;
@@ -83,28 +116,37 @@ extern "C" int fq_decode_step_host(
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   unsigned char* st = static_cast<unsigned char*>(staging);
   const size_t n = size_t(num_seqs);
+  StepAux* aux = nullptr;
+  int rc = step_aux(&aux);
+  if (rc != FQ_OK) return rc;
   struct Copy {
     size_t off;
     const void* src;
     size_t bytes;
+    bool side;  // on the side stream: only the decode needs it
   };
   const Copy copies[6] = {
-      {L.sl, seq_lens_host, n * 4},
-      {L.bt, block_table_host, n * size_t(block_table_stride) * 4},
-      {L.k, key_host, n * num_kv_heads * head_dim * 2},
-      {L.v, value_host, n * num_kv_heads * head_dim * 2},
-      {L.slots, slot_mapping_host, n * (slot_is_int64 ? 8 : 4)},
-      {L.q, q_host, n * num_q_heads * head_dim * 2},
+      {L.k, key_host, n * num_kv_heads * head_dim * 2, false},
+      {L.v, value_host, n * num_kv_heads * head_dim * 2, false},
+      {L.slots, slot_mapping_host, n * (slot_is_int64 ? 8 : 4), false},
+      {L.sl, seq_lens_host, n * 4, true},
+      {L.bt, block_table_host, n * size_t(block_table_stride) * 4, true},
+      {L.q, q_host, n * num_q_heads * head_dim * 2, true},
   };
+  // the side stream starts after whatever the caller's stream still has to do with the staging
+  cudaError_t ce = cudaEventRecord(aux->fork, stream);
+  if (ce == cudaSuccess) ce = cudaStreamWaitEvent(aux->stream, aux->fork, 0);
   for (const Copy& c : copies) {
-    cudaError_t e = cudaMemcpyAsync(st + c.off, c.src, c.bytes, cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess)
-      return fail(FQ_ERR_CUDA, "decode step: host-to-device copy: %s", cudaGetErrorString(e));
+    if (ce != cudaSuccess) break;
+    ce = cudaMemcpyAsync(st + c.off, c.src, c.bytes, cudaMemcpyHostToDevice,
+                         c.side ? aux->stream : stream);
   }
+  if (ce == cudaSuccess) ce = cudaEventRecord(aux->join, aux->stream);
+  if (ce != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "decode step: host-to-device copies: %s", cudaGetErrorString(ce));
   const void *q_d = st + L.q, *k_d = st + L.k, *v_d = st + L.v, *slots_d = st + L.slots;
   const void *bt_d = st + L.bt, *sl_d = st + L.sl;
   void* out_d = st + L.out;
-  int rc;
   const int64_t num_slots = num_blocks * block_size;
   if (kq_cache) {
     rc = fq_tq4_compress_append_qjl(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
@@ -119,6 +161,9 @@ extern "C" int fq_decode_step_host(
                                 slots_d, slot_is_int64, stream_);
   }
   if (rc != FQ_OK) return rc;
+  ce = cudaStreamWaitEvent(stream, aux->join, 0);
+  if (ce != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "decode step: joining the side stream: %s", cudaGetErrorString(ce));
   rc = fq_split_k_paged_decode(q_d, dtype, kv_cache, static_cast<const int32_t*>(bt_d),
                                block_table_stride, static_cast<const int32_t*>(sl_d), centroids_k,
                                n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs,
