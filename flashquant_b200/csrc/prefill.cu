@@ -23,6 +23,8 @@
 // The query arrives already rotated and rounded (fp16 copy of round(q Pi^T)), the output
 // leaves in rotated space as fp32 (the reference rounds only after the multiplication by
 // Pi); rotate.cu does both rotations.
+#include <type_traits>
+
 #include "fq_common.cuh"
 
 namespace fq {
@@ -157,8 +159,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   uint64_t* bar_o = bar_raw + 3;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_raw + 4);
   float* nk_s = reinterpret_cast<float*>(smem + S::kOffNorm);
-  float* lg_s = nk_s + kPfN;
-  float* lv_s = lg_s + kPfN;
+  float* vs_s = nk_s + kPfN;
+  float* lv_s = vs_s + kPfN;
   uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem + S::kOffLut);
   uint32_t* lut_v = lut_k + 256;
 
@@ -242,10 +244,9 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (tid < kPfN) {
       float nk = 0.f, nv = 0.f;
       if (tid < n_tok) { nk = kn_base[t0 + tid]; nv = vn_base[t0 + tid]; }
-      const float lg = fast_log2(nv);
       nk_s[tid] = nk * p.scale_log2;
-      lg_s[tid] = lg;
-      lv_s[tid] = fmaxf(lg, -40.f);
+      vs_s[tid] = nv * 16384.f;  // 2^kPfPScaleLog2
+      lv_s[tid] = fmaxf(fast_log2(nv), -40.f);
     }
     // ---- codes -> fp16 operands ------------------------------------------------------------
     if (!mbar_wait(bar_raw + buf, (tile >> 1) & 1)) { dead = true; }
@@ -284,52 +285,80 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     tc_fence_after();
 
     // ---- online softmax on row `tid` ---------------------------------------------------------
+    // A tile that lies wholly below the diagonal of every row of the CTA and is full needs no
+    // masking: the common case gets a loop body without predicates.
+    const bool unmasked = n_tok == kPfN && (!p.causal || t0 + kPfN - 1 <= m0);
     // pass 1: row maximum of logit*log2e + clamped log2|v| over the tile
     float mx = -INFINITY;
-    if (!dead) {
+    auto row_max = [&](auto masked) {
 #pragma unroll
       for (int c0 = 0; c0 < kPfN; c0 += 32) {
-        float s[32];
-        tmem_ld32(tmem_s + lane_sel + c0, s);
+        float sv[32];
+        tmem_ld32(tmem_s + lane_sel + c0, sv);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = c0 + j;
-          const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
-          const float e = s[j] * nk_s[col] + lv_s[col];
-          mx = fmaxf(mx, ok ? e : -INFINITY);
+        for (int j = 0; j < 32; j += 4) {
+          const float4 nk4 = *reinterpret_cast<const float4*>(nk_s + c0 + j);
+          const float4 lv4 = *reinterpret_cast<const float4*>(lv_s + c0 + j);
+          const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, lv[4] = {lv4.x, lv4.y, lv4.z, lv4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float e = fmaf(sv[j + u], nk[u], lv[u]);
+            if constexpr (decltype(masked)::value) {
+              const int col = c0 + j + u;
+              const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+              e = ok ? e : -INFINITY;
+            }
+            mx = fmaxf(mx, e);
+          }
         }
       }
+    };
+    if (!dead) {
+      if (unmasked) row_max(std::false_type{}); else row_max(std::true_type{});
     }
     const float m_new = fmaxf(m_run, mx);
     const float mref = (m_new == -INFINITY) ? 0.f : m_new;
     const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mref);
     m_run = m_new;
     l_run *= alpha;
-    // pass 2: weights -> fp16 A operand of the second product, [token chunk][row][16 B]
-    if (!dead) {
+    // pass 2: p = 2^(logit*log2e - m) feeds the denominator; the weight that meets the value
+    // codes is p*|v|*2^14 (<= 2^14 because m >= logit*log2e + log2|v|), stored as the fp16 A
+    // operand of the second product, [token chunk][row][16 B]
+    auto weights = [&](auto masked) {
+      const float neg_m = -mref;
 #pragma unroll
       for (int c0 = 0; c0 < kPfN; c0 += 32) {
-        float s[32];
-        tmem_ld32(tmem_s + lane_sel + c0, s);
+        float sv[32];
+        tmem_ld32(tmem_s + lane_sel + c0, sv);
         uint32_t packed[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float w2[2];
+        for (int j = 0; j < 32; j += 4) {
+          const float4 nk4 = *reinterpret_cast<const float4*>(nk_s + c0 + j);
+          const float4 vs4 = *reinterpret_cast<const float4*>(vs_s + c0 + j);
+          const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, vs[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+          float w[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c0 + j + u;
-            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
-            const float sv = s[j + u] * nk_s[col];
-            w2[u] = ok ? fast_exp2(sv + lg_s[col] - mref + kPfPScaleLog2) : 0.f;
-            l_run += ok ? fast_exp2(sv - mref) : 0.f;
+          for (int u = 0; u < 4; ++u) {
+            float pe = fast_exp2(fmaf(sv[j + u], nk[u], neg_m));
+            if constexpr (decltype(masked)::value) {
+              const int col = c0 + j + u;
+              const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+              pe = ok ? pe : 0.f;
+            }
+            l_run += pe;
+            w[u] = pe * vs[u];
           }
-          packed[j / 2] = pack_half2(w2[0], w2[1]);
+          packed[j / 2] = pack_half2(w[0], w[1]);
+          packed[j / 2 + 1] = pack_half2(w[2], w[3]);
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
           *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + tid * 16) =
               make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       }
+    };
+    if (!dead) {
+      if (unmasked) weights(std::false_type{}); else weights(std::true_type{});
     }
     fence_async_smem();
     tc_fence_before();
