@@ -11,8 +11,10 @@
 //   * thread r reads row r of S from TMEM (tcgen05.ld), applies |k|, the scale and the
 //     causal mask, updates the online softmax and writes the fp16 weights as the A operand
 //     of the second product;
-//   * one thread issues O_tile = P V into TMEM; thread r adds its row, rescaled, to the 128
-//     fp32 accumulators it keeps in registers.
+//   * one thread issues O += P V into TMEM, where the accumulator stays across all tiles: the
+//     reference exponent of the online softmax is raised lazily (only when a row's scores
+//     outgrow it by more than 6 bits), and only then do the threads of that warp rescale their
+//     rows of O in TMEM (tcgen05.ld / tcgen05.st); the epilogue reads O once.
 // Two such CTAs fit an SM (94 KB of shared memory, 256 of the 512 TMEM columns each), so one
 // CTA's softmax overlaps the other's tensor work.
 //
@@ -33,7 +35,8 @@ constexpr int kPfM = 128;       // query rows per CTA
 constexpr int kPfN = 64;        // KV tokens per tile
 constexpr int kPfThreads = 128;
 constexpr int kPfTmemCols = 256;
-constexpr float kPfPScaleLog2 = 14.f;
+constexpr float kPfPScaleLog2 = 8.f;  // fp16 weights are scaled by 2^8 ...
+constexpr float kPfMaxSlack = 6.f;    // ... and may exceed 1 by 2^6 before the reference exponent is raised
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder_smem, uint32_t cols) {
@@ -96,6 +99,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   tc_wait_ld();
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// the reverse: lane l stores 32 consecutive fp32 columns of TMEM lane (lane_base + l)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  uint32_t r[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(v[i]);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor, no swizzle, descriptor version 1.
@@ -229,9 +250,6 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   };
   if (tid == 0 && n_tiles > 0) issue_raw(0, 0);
 
-  float o_acc[D];
-#pragma unroll
-  for (int c = 0; c < D; ++c) o_acc[c] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   const int q_pos = m0 + tid;
   bool dead = false;
@@ -240,12 +258,15 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     const int buf = tile & 1;
     const int t0 = tile * kPfN;
     const int n_tok = kv_end - t0 < kPfN ? kv_end - t0 : kPfN;
+    // the previous tile's P V still reads the V and P operands in shared memory
+    if (tile > 0 && !mbar_wait(bar_o, (tile - 1) & 1)) dead = true;
+    tc_fence_after();
     // ---- norms of the tile --------------------------------------------------------------
     if (tid < kPfN) {
       float nk = 0.f, nv = 0.f;
       if (tid < n_tok) { nk = kn_base[t0 + tid]; nv = vn_base[t0 + tid]; }
       nk_s[tid] = nk * p.scale_log2;
-      vs_s[tid] = nv * 16384.f;  // 2^kPfPScaleLog2
+      vs_s[tid] = nv * 256.f;  // 2^kPfPScaleLog2
       lv_s[tid] = fmaxf(fast_log2(nv), -40.f);
     }
     // ---- codes -> fp16 operands ------------------------------------------------------------
@@ -316,11 +337,27 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (!dead) {
       if (unmasked) row_max(std::false_type{}); else row_max(std::true_type{});
     }
-    const float m_new = fmaxf(m_run, mx);
-    const float mref = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mref);
-    m_run = m_new;
-    l_run *= alpha;
+    // The reference exponent m only has to stay within kPfMaxSlack bits of the running maximum
+    // (weights then stay below 2^14 in fp16), so the accumulator O, which lives in TMEM across
+    // all tiles, is rescaled only when some row of the warp outgrows it by more than that.
+    const bool grew = mx > m_run + kPfMaxSlack;
+    if (__any_sync(0xffffffffu, grew) && !dead) {
+      const float m_new = grew ? mx : m_run;
+      const float alpha = (m_run == -INFINITY || !grew) ? 1.f : fast_exp2(m_run - m_new);
+      if (tile > 0) {
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_sel + c0, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= alpha;
+          tmem_st32(tmem_o + lane_sel + c0, o);
+        }
+      }
+      l_run *= alpha;
+      m_run = m_new;
+    }
+    const float mref = (m_run == -INFINITY) ? 0.f : m_run;
     // pass 2: p = 2^(logit*log2e - m) feeds the denominator; the weight that meets the value
     // codes is p*|v|*2^14 (<= 2^14 because m >= logit*log2e + log2|v|), stored as the fp16 A
     // operand of the second product, [token chunk][row][16 B]
@@ -370,32 +407,35 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 #pragma unroll
       for (int s = 0; s < kPfN / 16; ++s)
         umma_f16(tmem_o, smem_desc(pa + 2 * s * S::kSlabP, S::kSlabP, 128),
-                 smem_desc(va + s * 256, 128, S::kSlabKV), kIdescO, s > 0);
+                 smem_desc(va + s * 256, 128, S::kSlabKV), kIdescO, (tile > 0 || s > 0) ? 1u : 0u);
       umma_commit(bar_o);
-    }
-    if (!mbar_wait(bar_o, tile & 1)) dead = true;
-    tc_fence_after();
-    if (!dead) {
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float o[32];
-        tmem_ld32(tmem_o + lane_sel + c0, o);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_acc[c0 + j] = fmaf(o_acc[c0 + j], alpha, o[j]);
-      }
     }
     tc_fence_before();
   }
+  if (n_tiles > 0 && !dead && !mbar_wait(bar_o, (n_tiles - 1) & 1)) dead = true;
+  tc_fence_after();
 
   // ---- epilogue: normalise, round, store the rotated-space row -----------------------------
   if (dead && tid == 0 && p.status) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
-  if (tid < rows) {
-    const float inv = l_run > 0.f ? 1.f / (l_run * 16384.f) : 0.f;  // 2^-kPfPScaleLog2
+  {
+    const float inv = l_run > 0.f ? 1.f / (l_run * 256.f) : 0.f;  // 2^-kPfPScaleLog2
     float* dst = p.o_rot + ((int64_t(b) * p.hq + hq) * p.nq + q_pos) * D;
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 4)
-      *reinterpret_cast<float4*>(dst + c0) = make_float4(
-          o_acc[c0] * inv, o_acc[c0 + 1] * inv, o_acc[c0 + 2] * inv, o_acc[c0 + 3] * inv);
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      float o[32];
+      if (n_tiles > 0 && !dead) {
+        tmem_ld32(tmem_o + lane_sel + c0, o);  // whole warps: the load is warp-collective
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = 0.f;
+      }
+      if (tid < rows) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + c0 + j) =
+              make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+      }
+    }
   }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kPfTmemCols);
