@@ -202,8 +202,9 @@ int fq_split_k_paged_decode_static(const void* q, fq_dtype dtype, const uint8_t*
  *
  * fq_paged_decode_partials: `partials` (16-byte aligned) receives (num_seqs, num_q_heads,
  * head_dim+4) fp32 rows: head_dim un-normalised accumulator values, then m (base-2
- * reference exponent: the running maximum of logit*log2(e) + log2|v|), l (sum of
- * 2^(logit*log2(e) - m)) and two zero pads; a sequence of length 0 gives (0.., -inf, 0).
+ * reference exponent: within 6 of the running maximum of logit*log2(e) + log2|v|, never above
+ * it), l (sum of 2^(logit*log2(e) - m)) and two zero pads; a sequence of length 0 gives
+ * (0.., -inf, 0).  Rows merge like any online-softmax triple: only differences of m matter.
  * Workspace as for fq_split_k_paged_decode.  The partial-softmax triple follows the sketch
  * in csrc/cuda/paged_decode.cu:198-275.
  *
