@@ -192,6 +192,31 @@ def run_ours(args):
         barrier()
         ms = t0.elapsed_time(t1)
 
+        # ---- the same step with the two-stage (QJL) estimator in the logits --------------
+        qgraphs = []
+        with torch.cuda.stream(side):
+            for i in range(CACHE_COPIES):
+                K.split_k_paged_decode_qjl(q, caches[i], planes[i], bt, sl, ck, cv, rot, S, HKV, D,
+                                           BS, out=out, num_splits=SPLITS, workspace=ws)
+        side.synchronize()
+        for i in range(CACHE_COPIES):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                K.split_k_paged_decode_qjl(q, caches[i], planes[i], bt, sl, ck, cv, rot, S, HKV, D,
+                                           BS, out=out, num_splits=SPLITS, workspace=ws)
+            qgraphs.append(g)
+        qsteps = max(30, args.steps // 4)
+        for i in range(3):
+            qgraphs[i % CACHE_COPIES].replay()
+        torch.cuda.synchronize()
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for i in range(qsteps):
+            qgraphs[i % CACHE_COPIES].replay()
+        q1.record()
+        torch.cuda.synchronize()
+        qjl_ms = q0.elapsed_time(q1) / qsteps
+
         # ---- dominant kernel alone (the streaming kernel), same inputs ------------------
         q_rot16 = (q.float() @ rot.T).to(q.dtype).to(torch.float16).contiguous()
 
@@ -278,6 +303,10 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "fp16 mma operands, fp32 accumulate, bf16 in/out",
             "data": "synthetic", "config": workload_config(world),
             "hbm_tb_s_per_gpu_whole_call": alg / (ms / args.steps * 1e-3) / 1e12,
+            "two_stage_scoring": {
+                "ms_per_step": qjl_ms, "tokens_per_s_per_gpu": NUM_SEQS / (qjl_ms * 1e-3),
+                "what": "fq_split_k_paged_decode_qjl on the same inputs (156 B per token and KV "
+                        "head instead of 136)"},
             "clocks": sampler.summary(),
             "gpu_launches": launches_per_step * args.steps,
             "launches_per_step": launches_per_step,

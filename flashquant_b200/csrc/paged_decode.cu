@@ -88,6 +88,11 @@ struct DecodeArgs {
   uint32_t* q_count;      // [kMaxSeqs] rotated tiles of a sequence that are stored
   uint32_t* seg_count;    // [kMaxSeqs] (segment, warp) pairs of a sequence that are stored
   uint32_t* merge_count;  // [kMaxSeqs] merge jobs of a sequence that are finished
+  // two-stage (QJL) scoring only: logit += gamma * sqrt(pi/2)/m * <S q, signs>
+  const uint8_t* kq_cache;  // (num_blocks, block_size, Hkv * (D/8 + 4)): sign bits | gamma
+  const float* qjl;         // S (D, D)
+  __half* qs_w;             // where phase a writes fp16(q S^T), (num_seqs, Hq, D)
+  float corr_scale_log2;    // sqrt(pi/2) / m * sm_scale * log2(e)
 };
 
 // ------------------------------------------------------------------------------------
@@ -230,7 +235,7 @@ __device__ __forceinline__ void rotate_q_tile_load(RotTileOperands<D>& op, const
   }
 }
 
-template <int D, typename T>
+template <int D, typename T, bool kRound = true>
 __device__ __forceinline__ void rotate_q_tile_finish(const RotTileOperands<D>& op,
                                                      __half* __restrict__ out, int hq, int seq,
                                                      int mt, int nt, int lane) {
@@ -270,12 +275,16 @@ __device__ __forceinline__ void rotate_q_tile_finish(const RotTileOperands<D>& o
     }
   }
   const int col = 8 * nt + 2 * t;
+  if constexpr (kRound) {  // round to the query's type first, as the reference does
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[c] = to_f32(from_f32<T>(acc[c]));
+  }
   if (ok0)
-    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r0) * D + col) = __floats2half2_rn(
-        to_f32(from_f32<T>(acc[0])), to_f32(from_f32<T>(acc[1])));
+    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r0) * D + col) =
+        __floats2half2_rn(acc[0], acc[1]);
   if (ok1)
-    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r1) * D + col) = __floats2half2_rn(
-        to_f32(from_f32<T>(acc[2])), to_f32(from_f32<T>(acc[3])));
+    *reinterpret_cast<__half2*>(out + (int64_t(seq) * hq + r1) * D + col) =
+        __floats2half2_rn(acc[2], acc[3]);
 }
 
 // ------------------------------------------------------------------------------------
@@ -491,16 +500,25 @@ __device__ __forceinline__ uint32_t lds_u32(const unsigned char* smem, uint32_t 
   return *reinterpret_cast<const uint32_t*>(smem + off);
 }
 
+// fp16 pair (+-1, +-1) from two sign bits: value j is -1 when bit p+j of x is SET (x is the
+// complement of the stored word, where a set bit means +1)
+__device__ __forceinline__ uint32_t sign_pair(uint32_t x, int p) {
+  return 0x3C003C00u | (((x >> p) << 15) & 0x8000u) | ((x >> (p + 1)) << 31);
+}
+
 // (byte i of w) * 256 + lane4 in one instruction (lane4 < 128 sits in byte 0)
 template <int I>
 __device__ __forceinline__ uint32_t lut_addr(uint32_t w, uint32_t lane4) {
   return prmt(w, lane4, 0x5504u | (uint32_t(I) << 4));
 }
 
-// FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out
+// FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out;
+// 3 / 4 = the same with the two-stage (QJL) estimator in the logits
 template <int D, bool KPRMT, int FUSE>
 __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeArgs p) {
-  using TQ = typename std::conditional<FUSE == 2, __half, __nv_bfloat16>::type;
+  using TQ = typename std::conditional<FUSE == 2 || FUSE == 4, __half, __nv_bfloat16>::type;
+  constexpr bool QS = FUSE >= 3;
+  static_assert(!QS || D == 128, "the two-stage estimator is built for head_dim 128");
   constexpr int KS = D / 16;  // k-steps of the QK product = m-tiles of the PV product
   constexpr int KW = D / 32;  // 32-bit words of K codes per lane and row
   constexpr int VB = D / 16;  // bytes of V codes per lane and row
@@ -511,11 +529,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const uint32_t half_d = D / 2;
   const uint32_t row_bytes = uint32_t(p.hkv) * (D + 8);
   const uint32_t page_bytes = uint32_t(p.block_size) * row_bytes;
+  // side-plane page of the stage (QS): behind the cache page
+  const uint32_t qrow_bytes = QS ? uint32_t(p.hkv) * (D / 8 + 4) : 0u;
+  const uint32_t qpage_bytes = uint32_t(p.block_size) * qrow_bytes;
+  const uint32_t stage_bytes = page_bytes + qpage_bytes;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group = p.hq / p.hkv;  // q heads per KV head (<= 8)
   const uint32_t q_bytes = uint32_t(p.hq) * D * 2;
+  const uint32_t qbuf_bytes = q_bytes * (QS ? 2u : 1u);  // q_rot, then q S^T
   const int teams = kCW / p.hkv;
   const int team = warp / p.hkv;
   const int head = warp - team * p.hkv;
@@ -528,13 +551,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   uint64_t* empty_bar = full_bar + stages;
   uint64_t* qfull_bar = empty_bar + stages;
   uint64_t* qempty_bar = qfull_bar + 1;
-  const uint32_t ring_off = p.off_ring + uint32_t(team) * stages * page_bytes;
-  const uint32_t q_off = p.off_q + uint32_t(team) * q_bytes;
+  const uint32_t ring_off = p.off_ring + uint32_t(team) * stages * stage_bytes;
+  const uint32_t q_off = p.off_q + uint32_t(team) * qbuf_bytes;
 
   const int q_tiles = ((p.hq + 15) / 16) * (D / 8);  // rotated tiles per sequence
   [[maybe_unused]] RotTileOperands<D> rot_op;
   [[maybe_unused]] int rot_len = 0;
-  [[maybe_unused]] const int rot_jobs = p.num_seqs * q_tiles;
+  // with QS every tile exists twice: job < half rotates by Pi, the rest projects by S
+  [[maybe_unused]] const int rot_half = p.num_seqs * q_tiles;
+  [[maybe_unused]] const int rot_jobs = rot_half * (QS ? 2 : 1);
+  [[maybe_unused]] const uint32_t q_target = uint32_t(q_tiles) * (QS ? 2u : 1u);
   [[maybe_unused]] const int rot_job0 = blockIdx.x * kCW + warp;
   [[maybe_unused]] const int m_tiles = (p.hq + 15) / 16;
   // ---- set-up: barriers, page prefix (warp 0), look-up table (all warps) ---------------
@@ -564,9 +590,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   // that the rest of the set-up runs in the shadow of these (cold) loads -------------------
   if constexpr (FUSE != 0) {
     if (warp < kCW && rot_job0 < rot_jobs) {
-      const int seq = rot_job0 / q_tiles, r = rot_job0 - seq * q_tiles;
+      const int j0 = rot_job0 < rot_half ? rot_job0 : rot_job0 - rot_half;
+      const int seq = j0 / q_tiles, r = j0 - seq * q_tiles;
       rot_len = p.seq_lens[seq];
-      rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src), p.rotation, p.hq, seq,
+      rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src),
+                                rot_job0 < rot_half ? p.rotation : p.qjl, p.hq, seq,
                                 r % m_tiles, r / m_tiles, lane);
     }
     // first touch of the other buffers: address translation is warm when they are needed
@@ -606,8 +634,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     uint64_t* my_qfull = my_empty + stages;
     uint64_t* my_qempty = my_qfull + 1;
     const int4* my_desc = reinterpret_cast<const int4*>(smem + p.off_desc) + lane * kDescRing;
-    const uint32_t my_ring = p.off_ring + uint32_t(lane) * stages * page_bytes;
-    const uint32_t my_q = p.off_q + uint32_t(lane) * q_bytes;
+    const uint32_t my_ring = p.off_ring + uint32_t(lane) * stages * stage_bytes;
+    const uint32_t my_q = p.off_q + uint32_t(lane) * qbuf_bytes;
     int produced = 0, issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0, q_owed = -1;
     // descriptor of run page i of team T
     auto describe = [&](int T, int i, int n_run, int64_t f0) {
@@ -685,10 +713,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
             if (q_owed >= 0) break;  // the previous query copy has not gone out yet
             q_owed = d.z;
           }
-          mbar_expect_tx(my_full + issue_stage, page_bytes);
-          bulk_g2s(smem + my_ring + uint32_t(issue_stage) * page_bytes,
+          mbar_expect_tx(my_full + issue_stage, stage_bytes);
+          bulk_g2s(smem + my_ring + uint32_t(issue_stage) * stage_bytes,
                    p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
                    my_full + issue_stage);
+          if constexpr (QS)
+            bulk_g2s(smem + my_ring + uint32_t(issue_stage) * stage_bytes + page_bytes,
+                     p.kq_cache + int64_t(d.x) * int64_t(qpage_bytes), qpage_bytes,
+                     my_full + issue_stage);
           ++issue_idx;
           if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
           progress = true;
@@ -698,12 +730,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         if (q_owed >= 0 && (q_issued == 0 || mbar_test_wait(my_qempty, (q_issued - 1) & 1))) {
           bool rows_there = true;
           if constexpr (FUSE != 0) {
-            rows_there = ld_acquire_u32(p.q_count + q_owed) >= uint32_t(q_tiles);
+            rows_there = ld_acquire_u32(p.q_count + q_owed) >= q_target;
             if (rows_there) fence_proxy_async();
           }
           if (rows_there) {
-            mbar_expect_tx(my_qfull, q_bytes);
+            mbar_expect_tx(my_qfull, qbuf_bytes);
             bulk_g2s(smem + my_q, p.q_rot + int64_t(q_owed) * p.hq * D, q_bytes, my_qfull);
+            if constexpr (QS)
+              bulk_g2s(smem + my_q + q_bytes, p.qs_w + int64_t(q_owed) * p.hq * D, q_bytes,
+                       my_qfull);
             ++q_issued;
             q_owed = -1;
             progress = true;
@@ -733,14 +768,22 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   // ---- phase a: one rotated query tile per warp of the grid --------------------------------
   if constexpr (FUSE != 0) {
     for (int job = rot_job0; job < rot_jobs; job += gridDim.x * kCW) {
-      const int seq = job / q_tiles, r = job - seq * q_tiles;
+      const bool by_pi = job < rot_half;
+      const int j0 = by_pi ? job : job - rot_half;
+      const int seq = j0 / q_tiles, r = j0 - seq * q_tiles;
       if (job != rot_job0) {
         rot_len = p.seq_lens[seq];
-        rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src), p.rotation, p.hq, seq,
-                                  r % m_tiles, r / m_tiles, lane);
+        rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src),
+                                  by_pi ? p.rotation : p.qjl, p.hq, seq, r % m_tiles, r / m_tiles,
+                                  lane);
       }
       if (rot_len <= 0) continue;  // nobody reads the query of an empty sequence
-      rotate_q_tile_finish<D, TQ>(rot_op, p.q_rot_w, p.hq, seq, r % m_tiles, r / m_tiles, lane);
+      // q Pi^T is rounded to the query's type as the reference does; q S^T is not
+      if (by_pi)
+        rotate_q_tile_finish<D, TQ>(rot_op, p.q_rot_w, p.hq, seq, r % m_tiles, r / m_tiles, lane);
+      else
+        rotate_q_tile_finish<D, TQ, false>(rot_op, p.qs_w, p.hq, seq, r % m_tiles, r / m_tiles,
+                                           lane);
       __threadfence();
       __syncwarp();
       if (lane == 0) atomicAdd(p.q_count + seq, 1u);
@@ -845,7 +888,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       }
     }
 
-    const uint32_t page_off = ring_off + uint32_t(stage) * page_bytes;
+    const uint32_t page_off = ring_off + uint32_t(stage) * stage_bytes;
     for (int u = 0; u < units_per_page; ++u) {
       const int tok0 = u * 16;
       if (tok0 >= n_valid) break;
@@ -909,6 +952,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         mma_f16(sacc[1], a[1][0], a[1][1], a[1][2], a[1][3], qf[2 * w + 1][0], qf[2 * w + 1][1]);
       }
 
+      // ---------- two-stage estimator: C^T = signs (q S^T)^T, one more 16 x 8 product ---------
+      // lane (g,t) takes sign word t of the head (coordinates 32t .. 32t+31) of tokens g and
+      // g+8 and spends bits 4s .. 4s+3 on k-step s; the fragment of q S^T follows the same
+      // order (8 consecutive bytes of the row per k-step)
+      [[maybe_unused]] float cacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      [[maybe_unused]] float gs_lo = 0.f, gs_hi = 0.f;
+      if constexpr (QS) {
+        const uint32_t prow = page_off + page_bytes + uint32_t(tok0 + g) * qrow_bytes;
+        const uint32_t xa = ~lds_u32(smem, prow + uint32_t(head) * (D / 8) + 4 * t);
+        const uint32_t xb = ~lds_u32(smem, prow + 8 * qrow_bytes + uint32_t(head) * (D / 8) + 4 * t);
+        gs_lo = *reinterpret_cast<const float*>(smem + prow + p.hkv * (D / 8) + 4 * head) *
+                p.corr_scale_log2;
+        gs_hi = *reinterpret_cast<const float*>(smem + prow + 8 * qrow_bytes + p.hkv * (D / 8) +
+                                                4 * head) * p.corr_scale_log2;
+        const bool valid = g < group;
+        const uint32_t qs_off =
+            q_off + q_bytes + uint32_t(head * group + (valid ? g : 0)) * D * 2 + 64 * t;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint2 b = *reinterpret_cast<const uint2*>(smem + qs_off + 8 * ks);
+          if (!valid) b = make_uint2(0u, 0u);
+          mma_f16(cacc[ks & 1], sign_pair(xa, 4 * ks), sign_pair(xb, 4 * ks),
+                  sign_pair(xa, 4 * ks + 2), sign_pair(xb, 4 * ks + 2), b.x, b.y);
+        }
+      }
+
       // ---------- online softmax in the accumulator layout ---------------------------------
       const bool ok_lo = tok0 + g < n_valid, ok_hi = tok0 + g + 8 < n_valid;
       // log2 of the value norm is folded into the exponent so that the fp16 weights stay in
@@ -922,6 +991,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       for (int c = 0; c < 2; ++c) {
         s_lo[c] = (sacc[0][c] + sacc[1][c]) * ks_lo;
         s_hi[c] = (sacc[0][2 + c] + sacc[1][2 + c]) * ks_hi;
+        if constexpr (QS) {
+          s_lo[c] = fmaf(cacc[0][c] + cacc[1][c], gs_lo, s_lo[c]);
+          s_hi[c] = fmaf(cacc[0][2 + c] + cacc[1][2 + c], gs_hi, s_hi[c]);
+        }
         mx[c] = fmaxf(ok_lo ? s_lo[c] + lv_lo : -INFINITY, ok_hi ? s_hi[c] + lv_hi : -INFINITY);
       }
       // The reference exponent m only has to stay within kMaxSlack bits of the true running
@@ -1249,7 +1322,8 @@ static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits,
   WorkspaceLayout w;
   w.count_off = 256;
   w.q_rot_off = up256(w.count_off + 3 * size_t(kMaxSeqs) * sizeof(uint32_t));
-  w.slots_off = up256(w.q_rot_off + size_t(num_seqs) * hq * d * sizeof(__half));
+  // room for fp16(q Pi^T) and, behind it, fp16(q S^T) of the two-stage estimator
+  w.slots_off = up256(w.q_rot_off + 2 * size_t(num_seqs) * hq * d * sizeof(__half));
   w.total = up256(w.slots_off +
                   (size_t(num_seqs) * splits + ctas) * hq * (d + kPartPad) * sizeof(float));
   return w;
@@ -1264,12 +1338,14 @@ struct SmemPlan {
   uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent, total;
 };
 
-static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size) {
+// `qs`: stages also hold the page of the QJL side plane, query buffers also hold q S^T
+static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size, bool qs = false) {
   SmemPlan s{};
   const uint32_t teams = uint32_t(kCW / hkv);
-  const uint32_t page_bytes = uint32_t(block_size) * hkv * (d + 8);
+  const uint32_t page_bytes =
+      uint32_t(block_size) * hkv * (d + 8) + (qs ? uint32_t(block_size) * hkv * (d / 8 + 4) : 0u);
   auto up16 = [](uint32_t v) { return (v + 15u) & ~15u; };
-  const uint32_t q_all = teams * up16(uint32_t(hq) * d * 2);
+  const uint32_t q_all = teams * up16(uint32_t(hq) * d * 2) * (qs ? 2u : 1u);
   const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
   const uint32_t desc = teams * kDescRing * 16;
   const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16 + 96;
@@ -1338,8 +1414,12 @@ static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, int head_d
   if (head_dim == 128)
     return kprmt ? launch_stream_t<128, true, FUSE>(a, sp, ctas, stream)
                  : launch_stream_t<128, false, FUSE>(a, sp, ctas, stream);
-  return kprmt ? launch_stream_t<64, true, FUSE>(a, sp, ctas, stream)
-               : launch_stream_t<64, false, FUSE>(a, sp, ctas, stream);
+  if constexpr (FUSE >= 3) {
+    return fail(FQ_ERR_UNSUPPORTED, "two-stage scoring is built for head_dim 128");
+  } else {
+    return kprmt ? launch_stream_t<64, true, FUSE>(a, sp, ctas, stream)
+                 : launch_stream_t<64, false, FUSE>(a, sp, ctas, stream);
+  }
 }
 
 template <int D>
@@ -1440,13 +1520,14 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                         const float* centroids_v, int ncv, const float* rotation, int num_seqs,
                         int hq, int hkv, int head_dim, int block_size, int64_t num_blocks,
                         float sm_scale, int num_splits, void* workspace, size_t workspace_bytes,
-                        int ctas, cudaStream_t stream, void* fused_out = nullptr) {
+                        int ctas, cudaStream_t stream, void* fused_out = nullptr,
+                        const uint8_t* kq_cache = nullptr, const float* qjl = nullptr) {
   FQ_REQUIRE(workspace && aligned(workspace, 256), FQ_ERR_WORKSPACE,
              "paged decode: workspace is null or not 256-byte aligned");
   const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv));
   FQ_REQUIRE(workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
              "paged decode: workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
-  const SmemPlan sp = plan_smem(num_seqs, hq, hkv, head_dim, block_size);
+  const SmemPlan sp = plan_smem(num_seqs, hq, hkv, head_dim, block_size, kq_cache != nullptr);
   FQ_REQUIRE(sp.stages >= 2, FQ_ERR_UNSUPPORTED,
              "paged decode: a page of %d tokens x %d heads does not fit the shared-memory ring",
              block_size, hkv);
@@ -1486,6 +1567,15 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.q_count = reinterpret_cast<uint32_t*>(ws + w.count_off);
   a.seg_count = a.q_count + kMaxSeqs;
   a.merge_count = a.seg_count + kMaxSeqs;
+  if (kq_cache) {
+    a.kq_cache = kq_cache;
+    a.qjl = qjl;
+    a.qs_w = a.q_rot_w + size_t(num_seqs) * hq * head_dim;
+    // logit += gamma * sqrt(pi/2) / m * <S q, signs>, m = head_dim rows of S
+    a.corr_scale_log2 = 1.2533141373155003f / float(head_dim) * a.scale_log2;
+    return dtype == FQ_BF16 ? launch_stream<3>(a, sp, ctas, head_dim, stream)
+                            : launch_stream<4>(a, sp, ctas, head_dim, stream);
+  }
   return dtype == FQ_BF16 ? launch_stream<1>(a, sp, ctas, head_dim, stream)
                           : launch_stream<2>(a, sp, ctas, head_dim, stream);
 }
@@ -1541,6 +1631,32 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
                       n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                       num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
                       workspace, workspace_bytes, ctas, stream, out);
+}
+
+extern "C" int fq_split_k_paged_decode_qjl(
+    const void* q, fq_dtype dtype, const uint8_t* kv_cache, const uint8_t* kq_cache,
+    const int32_t* block_table, int64_t block_table_stride, const int32_t* seq_lens,
+    const float* centroids_k, int n_centroids_k, const float* centroids_v, int n_centroids_v,
+    const float* rotation, const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads,
+    int head_dim, int block_size, int64_t num_blocks, float sm_scale, void* out, int num_splits,
+    void* workspace, size_t workspace_bytes, fq_stream_t stream) {
+  int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
+                           centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                           num_kv_heads, head_dim, block_size, num_blocks, num_splits);
+  if (rc != FQ_OK) return rc;
+  FQ_REQUIRE(out && kq_cache && qjl, FQ_ERR_INVALID_ARGUMENT,
+             "paged decode (two-stage): null pointer");
+  FQ_REQUIRE(head_dim == 128, FQ_ERR_UNSUPPORTED,
+             "paged decode (two-stage): head_dim %d (built for 128)", head_dim);
+  FQ_REQUIRE(aligned(kq_cache, 16) && aligned(qjl, 16), FQ_ERR_ALIGNMENT,
+             "paged decode (two-stage): kq_cache and qjl must be 16-byte aligned");
+  if (num_seqs == 0) return FQ_OK;
+  const int ctas = device_sm_count();
+  if (num_splits == 0) num_splits = auto_splits();
+  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
+                      workspace, workspace_bytes, ctas, stream, out, kq_cache, qjl);
 }
 
 static int partials_common(const void* q, fq_dtype dtype, const uint8_t* kv_cache,

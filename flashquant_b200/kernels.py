@@ -295,6 +295,40 @@ def split_k_paged_decode(
     return out
 
 
+def split_k_paged_decode_qjl(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k,
+                             centroids_v, rotation, qjl_matrix, num_kv_heads, head_dim, block_size,
+                             sm_scale=None, out=None, num_splits=0, workspace=None):
+    """``split_k_paged_decode`` whose logits use the two-stage inner-product estimator
+    (``TurboQuantProd.estimate_inner_product``, src/flashquant/core/quantizer.py:349-370):
+    ``<q,k> ~ <q,k_mse> + gamma*sqrt(pi/2)/m*<S q, signs>`` with signs and gamma read from the
+    side plane ``kq_cache`` that ``tq4_compress_append_qjl`` fills."""
+    dev, num_seqs, hq, d, q, block_table, seq_lens, ck, cv, rot = _decode_args(
+        q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation, num_kv_heads,
+        head_dim, block_size)
+    N.require_cuda(kq_cache)
+    if kq_cache.dtype != torch.uint8 or not kq_cache.is_contiguous() or \
+            tuple(kq_cache.shape) != (kv_cache.shape[0], block_size, num_kv_heads * (d // 8 + 4)):
+        raise ValueError("kq_cache must be contiguous uint8 (num_blocks, block_size, H*(D/8+4))")
+    if tuple(qjl_matrix.shape) != (d, d):
+        raise ValueError("qjl_dim must equal head_dim")
+    s_mat = _f32(qjl_matrix, dev)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of q's shape and dtype")
+    if workspace is None:
+        workspace = decode_workspace(dev, num_seqs, hq, num_kv_heads, d, num_splits)
+    N.check(N.load().fq_split_k_paged_decode_qjl(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(kq_cache), N.ptr(block_table),
+        block_table.stride(0), N.ptr(seq_lens), N.ptr(ck), ck.numel(), N.ptr(cv), cv.numel(),
+        N.ptr(rot), N.ptr(s_mat), num_seqs, hq, num_kv_heads, d, block_size, kv_cache.shape[0],
+        float(sm_scale), N.ptr(out), int(num_splits), N.ptr(workspace), workspace.numel(),
+        N.stream_ptr(dev)))
+    return out
+
+
 class HostDecodeStep:
     """One decode step with host tensors in and out (``fq_decode_step_host``).
 

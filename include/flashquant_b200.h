@@ -174,6 +174,29 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
                             void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
 /*
+ * fq_split_k_paged_decode with the two-stage estimator in the logits:
+ *   logit = sm_scale * ( |k| <q_rot, c[code]> + gamma * sqrt(pi/2)/m * <S q, signs> )
+ * i.e. TurboQuantProd.estimate_inner_product (src/flashquant/core/quantizer.py:349-370,
+ * also KeyCompressor.asymmetric_attention_scores, src/flashquant/core/compressor.py:151-192)
+ * evaluated against the paged cache; the reference never runs it at decode time (its
+ * decode dequantises K through the first stage only), so this is an addition that gives the
+ * sign bits and gamma written by fq_tq4_compress_append_qjl a consumer.  Values as in
+ * fq_split_k_paged_decode.
+ *   kq_cache   (num_blocks, block_size, num_kv_heads*(head_dim/8+4)) side plane, 16-byte aligned
+ *   qjl        (head_dim, head_dim) fp32 row-major S; q S^T is computed in the same launch
+ * head_dim 128 only.  Traffic per (token, KV head): 156 bytes instead of 136.
+ */
+int fq_split_k_paged_decode_qjl(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                                const uint8_t* kq_cache, const int32_t* block_table,
+                                int64_t block_table_stride, const int32_t* seq_lens,
+                                const float* centroids_k, int n_centroids_k,
+                                const float* centroids_v, int n_centroids_v,
+                                const float* rotation, const float* qjl, int num_seqs,
+                                int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                int64_t num_blocks, float sm_scale, void* out, int num_splits,
+                                void* workspace, size_t workspace_bytes, fq_stream_t stream);
+
+/*
  * fq_split_k_paged_decode for callers that cannot allocate.  (No counterpart in the
  * reference.)  Same arguments and result as fq_split_k_paged_decode, minus the workspace:
  * the scratch is a 16 MiB array built into the library, so nothing is allocated by the

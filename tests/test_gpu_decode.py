@@ -282,3 +282,34 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
     # and against the oracle end to end
     attention_close(hout, O.split_k_paged_decode(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot, hkv,
                                                  d, bs, None))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_two_stage_scoring_vs_oracle(consts, dtype):
+    """Logits with the QJL correction read from the side plane: cache and plane written by the
+    GPU append, decode against the oracle's estimator on the same bytes."""
+    d, hkv, hq, bs = 128, 8, 32, 16
+    w = W.decode_workload(num_q_heads=hq, num_kv_heads=hkv, head_dim=d, block_size=bs, cfg=1,
+                          seq_lens=[70, 0, 513, 16, 1], dtype=dtype)
+    rot, S = consts["rotation_128_0"], consts["qjl_128_0"]
+    bk, ck = consts["boundaries_128_3"], consts["centroids_128_3"]
+    bv, cv = consts["boundaries_128_4"], consts["centroids_128_4"]
+    k, v = W.make_kv(w.total_tokens, hkv, d, 1, dtype)
+    cache = torch.zeros(w.num_blocks, bs, hkv * (d + 8), dtype=torch.uint8, device=DEV)
+    plane = torch.zeros(w.num_blocks, bs, hkv * (d // 8 + 4), dtype=torch.uint8, device=DEV)
+    K.tq4_compress_append_qjl(k.to(DEV), v.to(DEV), cache, plane, w.slot_mapping.to(DEV), rot, bk,
+                              ck, bv, S)
+    ref = O.qjl_paged_decode(w.q, cache.cpu(), plane.cpu(), w.block_table, w.seq_lens, ck, cv, rot,
+                             S, hkv, d, bs)
+    for splits in (0, 4):
+        out = K.split_k_paged_decode_qjl(w.q.to(DEV), cache, plane, w.block_table.to(DEV),
+                                         w.seq_lens.to(DEV), ck, cv, rot, S, hkv, d, bs,
+                                         num_splits=splits)
+        attention_close(out, ref)
+        assert (out[1] == 0).all()  # empty sequence
+    # the correction matters: the one-stage logits give another answer on the same cache
+    plain = K.split_k_paged_decode(w.q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV),
+                                   ck, cv, rot, hkv, d, bs)
+    assert (plain.float() - out.float()).abs().max().item() > 1e-2
+    ws = K.decode_workspace(torch.device(DEV), w.num_seqs, hq, hkv, d, 0)
+    assert K.workspace_status(ws) == 0
