@@ -11,8 +11,11 @@
 //
 // A CTA of 16 warps keeps the matrices resident in shared memory as fp16 hi / lo' planes (the
 // same bytes as fp32) and walks over tiles of 16 vectors: K of the tile, then V.  Warp w
-// loads and normalises vector w of the tile and owns column tile w of every product
-// (fragments by ldmatrix: three loads and three MMAs per 16 values of k); the left operand
+// loads and normalises vector w of the tile; the first eight warps (head_dim 128) own two
+// column tiles each of every product (fragments by ldmatrix: per 16 values of k two loads
+// for the left operand, shared by the tiles, then one load and three MMAs per tile: one tile
+// per warp is bound by the shared-memory instruction queue, four leave too few warps); the
+// left operand
 // (x_hat, then the centroid vector, then the residual) is exchanged through shared memory as
 // hi / lo' planes, so a K tile of the two-stage quantiser costs six block-wide barriers.  The operation order is the
 // reference's (normalise, then rotate); the tie rule is bucketize(right=False).
@@ -50,6 +53,9 @@ struct CompressArgs {
   int64_t num_slots;
 };
 
+#ifndef FQ_COMPRESS_NTW
+#define FQ_COMPRESS_NTW 2
+#endif
 constexpr int kTileRows = 16;         // vectors per tile = rows of one MMA
 constexpr float kLoScale = 2048.f;    // lo' = (v - hi) * 2^11
 constexpr float kLoUnscale = 1.f / 2048.f;
@@ -121,33 +127,44 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row_pt
                : "r"(smem_u32(row_ptr)));
 }
 
-// acc[c] = sum_k A[row][k] * B[n][k] for column tile `nt` (C-fragment layout: c0,c1 = row g,
-// columns 8*nt + 2t, +1; c2,c3 = row g+8), A and B as hi / lo' planes.  Three ldmatrix and
-// three MMAs per 16 values of k.
-template <int D>
+// acc[i][c] = sum_k A[row][k] * B[n][k] for the NTW column tiles nt0 .. nt0+NTW-1 (C-fragment
+// layout: c0,c1 = row g, columns 8*nt + 2t, +1; c2,c3 = row g+8), A and B as hi / lo' planes.
+// Per 16 values of k: two ldmatrix for the left operand, shared by the tiles, then one ldmatrix
+// and three MMAs per tile.
+template <int D, int NTW>
 __device__ __forceinline__ void plane_mma(const __half* __restrict__ ah,
                                           const __half* __restrict__ al,
                                           const __half* __restrict__ bh,
-                                          const __half* __restrict__ bl, int ld, int nt, int lane,
-                                          float (&acc)[4]) {
+                                          const __half* __restrict__ bl, int ld, int nt0, int lane,
+                                          float (&acc)[NTW][4]) {
   const int j = lane >> 3, r = lane & 7;  // ldmatrix: lanes 8j..8j+7 give the rows of matrix j
   // A: matrix j = rows 8*(j&1).., k-segment j>>1;  B: matrix j = plane j>>1 (hi, lo'), k-segment j&1
   const __half* pa_h = ah + ((j & 1) * 8 + r) * ld + 8 * (j >> 1);
   const __half* pa_l = al + ((j & 1) * 8 + r) * ld + 8 * (j >> 1);
-  const __half* pb = ((j >> 1) ? bl : bh) + (8 * nt + r) * ld + 8 * (j & 1);
-  float hi[4] = {0.f, 0.f, 0.f, 0.f}, co[4] = {0.f, 0.f, 0.f, 0.f};
+  const __half* pb = ((j >> 1) ? bl : bh) + (8 * nt0 + r) * ld + 8 * (j & 1);
+  float hi[NTW][4], co[NTW][4];
+#pragma unroll
+  for (int i = 0; i < NTW; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) hi[i][c] = co[i][c] = 0.f;
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t xh[4], xl[4], b[4];  // b: b0 hi, b1 hi, b0 lo', b1 lo'
+    uint32_t xh[4], xl[4];
     ldmatrix_x4(xh, pa_h + 16 * ks);
-    ldmatrix_x4(b, pb + 16 * ks);
     ldmatrix_x4(xl, pa_l + 16 * ks);
-    mma_f16(hi, xh[0], xh[1], xh[2], xh[3], b[0], b[1]);
-    mma_f16(co, xh[0], xh[1], xh[2], xh[3], b[2], b[3]);
-    mma_f16(co, xl[0], xl[1], xl[2], xl[3], b[0], b[1]);
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) {
+      uint32_t b[4];  // b0 hi, b1 hi, b0 lo', b1 lo'
+      ldmatrix_x4(b, pb + i * 8 * ld + 16 * ks);
+      mma_f16(hi[i], xh[0], xh[1], xh[2], xh[3], b[0], b[1]);
+      mma_f16(co[i], xh[0], xh[1], xh[2], xh[3], b[2], b[3]);
+      mma_f16(co[i], xl[0], xl[1], xl[2], xl[3], b[0], b[1]);
+    }
   }
 #pragma unroll
-  for (int c = 0; c < 4; ++c) acc[c] = fmaf(co[c], kLoUnscale, hi[c]);
+  for (int i = 0; i < NTW; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[i][c] = fmaf(co[i][c], kLoUnscale, hi[i][c]);
 }
 
 template <int D, int DT, bool QJL>
@@ -156,7 +173,9 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
   using S = CompressSmem<D, QJL>;
   constexpr int LD = S::kLd;
   constexpr int JT = D / 32;   // elements per lane when a warp walks one vector
-  constexpr int NT = D / 8;    // column tiles of a product: warps 0 .. NT-1 take one each
+  constexpr int NT = D / 8;    // column tiles of a product
+  constexpr int NTW = FQ_COMPRESS_NTW;  // ... of which a product warp takes this many
+  constexpr int MW = NT / NTW;          // product warps: warps 0 .. MW-1
   static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -180,7 +199,7 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const bool col_warp = warp < NT;  // takes part in the products
+  const bool col_warp = warp < MW;  // takes part in the products
 
   // ---- resident matrices -----------------------------------------------------------------
   // [0]: Pi as it is  (y = x_hat Pi^T:      B[k][n] = Pi[n][k])
@@ -295,63 +314,76 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
     __syncthreads();
 
     // ---- y = x_hat Pi^T, codes -------------------------------------------------------------
-    float acc[4];
-    int idx[4] = {0, 0, 0, 0};
+    float acc[NTW][4];
+    int idx[NTW][4];
     const int64_t slot_lo = s_slot[g], slot_hi = s_slot[g + 8];
     const int head_lo = s_head[g], head_hi = s_head[g + 8];
     if (col_warp) {
-      plane_mma<D>(a_hi, a_lo, m_hi[0], m_lo[0], LD, warp, lane, acc);
+      plane_mma<D, NTW>(a_hi, a_lo, m_hi[0], m_lo[0], LD, warp * NTW, lane, acc);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) idx[c] = bucketize15(acc[c], sb);
-      // code byte = (even coordinate << 4) | odd coordinate; the four lanes of a row hold
-      // bytes 4*nt .. 4*nt+3 of it
-      uint32_t w_lo = uint32_t((idx[0] << 4) | idx[1]) << (8 * t);
-      uint32_t w_hi = uint32_t((idx[2] << 4) | idx[3]) << (8 * t);
-      w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 1);
-      w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 1);
-      w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 2);
-      w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 2);
-      if (t == 0 && slot_lo >= 0)
-        *reinterpret_cast<uint32_t*>(p.code[s] + slot_lo * p.code_row_stride +
-                                     int64_t(head_lo) * p.code_head_stride + 4 * warp) = w_lo;
-      if (t == 1 && slot_hi >= 0)
-        *reinterpret_cast<uint32_t*>(p.code[s] + slot_hi * p.code_row_stride +
-                                     int64_t(head_hi) * p.code_head_stride + 4 * warp) = w_hi;
+      for (int i = 0; i < NTW; ++i) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) idx[i][c] = bucketize15(acc[i][c], sb);
+        // code byte = (even coordinate << 4) | odd coordinate; the four lanes of a row hold
+        // bytes 4*nt .. 4*nt+3 of it
+        uint32_t w_lo = uint32_t((idx[i][0] << 4) | idx[i][1]) << (8 * t);
+        uint32_t w_hi = uint32_t((idx[i][2] << 4) | idx[i][3]) << (8 * t);
+        w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 1);
+        w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 1);
+        w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 2);
+        w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 2);
+        const int byte0 = 4 * (warp * NTW + i);
+        if (t == 0 && slot_lo >= 0)
+          *reinterpret_cast<uint32_t*>(p.code[s] + slot_lo * p.code_row_stride +
+                                       int64_t(head_lo) * p.code_head_stride + byte0) = w_lo;
+        if (t == 1 && slot_hi >= 0)
+          *reinterpret_cast<uint32_t*>(p.code[s] + slot_hi * p.code_row_stride +
+                                       int64_t(head_hi) * p.code_head_stride + byte0) = w_hi;
+      }
     }
     __syncthreads();  // every warp has read x_hat: the planes may be overwritten
 
     if constexpr (QJL) {
       if (s == 0) {
         // ---- x_tilde = (c[code] Pi) n ; r = x - x_tilde ; gamma = |r| ------------------------
-        const int col = 8 * warp + 2 * t;
         if (col_warp) {
-          __half h[4], l[4];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) split_hi_lo(s_cent[idx[c]], h[c], l[c]);
-          *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
-          *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
-          *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
-          *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+          for (int i = 0; i < NTW; ++i) {
+            const int col = 8 * (warp * NTW + i) + 2 * t;
+            __half h[4], l[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) split_hi_lo(s_cent[idx[i][c]], h[c], l[c]);
+            *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
+            *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
+            *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
+            *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+          }
         }
         __syncthreads();
-        if (col_warp) plane_mma<D>(a_hi, a_lo, m_hi[1], m_lo[1], LD, warp, lane, acc);
+        if (col_warp) plane_mma<D, NTW>(a_hi, a_lo, m_hi[1], m_lo[1], LD, warp * NTW, lane, acc);
         __syncthreads();  // every warp has read the centroid planes
         if (col_warp) {
           const float n_lo = s_nrm[g], n_hi = s_nrm[g + 8];
-          const float2 x_lo = *reinterpret_cast<const float2*>(s_x + g * (D + 8) + col);
-          const float2 x_hi = *reinterpret_cast<const float2*>(s_x + (g + 8) * (D + 8) + col);
-          const float r0 = x_lo.x - acc[0] * n_lo, r1 = x_lo.y - acc[1] * n_lo;
-          const float r2 = x_hi.x - acc[2] * n_hi, r3 = x_hi.y - acc[3] * n_hi;
-          float ss_lo = fmaf(r0, r0, r1 * r1), ss_hi = fmaf(r2, r2, r3 * r3);
-          __half h[4], l[4];
-          split_hi_lo(r0, h[0], l[0]);
-          split_hi_lo(r1, h[1], l[1]);
-          split_hi_lo(r2, h[2], l[2]);
-          split_hi_lo(r3, h[3], l[3]);
-          *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
-          *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
-          *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
-          *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+          float ss_lo = 0.f, ss_hi = 0.f;
+#pragma unroll
+          for (int i = 0; i < NTW; ++i) {
+            const int col = 8 * (warp * NTW + i) + 2 * t;
+            const float2 x_lo = *reinterpret_cast<const float2*>(s_x + g * (D + 8) + col);
+            const float2 x_hi = *reinterpret_cast<const float2*>(s_x + (g + 8) * (D + 8) + col);
+            const float r0 = x_lo.x - acc[i][0] * n_lo, r1 = x_lo.y - acc[i][1] * n_lo;
+            const float r2 = x_hi.x - acc[i][2] * n_hi, r3 = x_hi.y - acc[i][3] * n_hi;
+            ss_lo = fmaf(r0, r0, fmaf(r1, r1, ss_lo));
+            ss_hi = fmaf(r2, r2, fmaf(r3, r3, ss_hi));
+            __half h[4], l[4];
+            split_hi_lo(r0, h[0], l[0]);
+            split_hi_lo(r1, h[1], l[1]);
+            split_hi_lo(r2, h[2], l[2]);
+            split_hi_lo(r3, h[3], l[3]);
+            *reinterpret_cast<uint32_t*>(a_hi + g * LD + col) = pack_h2(h[0], h[1]);
+            *reinterpret_cast<uint32_t*>(a_lo + g * LD + col) = pack_h2(l[0], l[1]);
+            *reinterpret_cast<uint32_t*>(a_hi + (g + 8) * LD + col) = pack_h2(h[2], h[3]);
+            *reinterpret_cast<uint32_t*>(a_lo + (g + 8) * LD + col) = pack_h2(l[2], l[3]);
+          }
           ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 1);
           ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 1);
           ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 2);
@@ -365,24 +397,31 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
         if (tid < 16 && s_slot[tid] >= 0) {
           float ss = 0.f;
 #pragma unroll
-          for (int w = 0; w < NT; ++w) ss += s_gpart[w * 16 + tid];
+          for (int w = 0; w < MW; ++w) ss += s_gpart[w * 16 + tid];
           *reinterpret_cast<float*>(p.gam + s_slot[tid] * p.gam_row_stride + s_head[tid] * 4) =
               sqrtf(ss);
         }
         // ---- sign(r S^T): bit j%8 of byte j/8 is 1 for a projection >= 0 ---------------------
         if (col_warp) {
-          plane_mma<D>(a_hi, a_lo, m_hi[2], m_lo[2], LD, warp, lane, acc);
-          uint32_t b_lo = ((acc[0] >= 0.f ? 1u : 0u) | (acc[1] >= 0.f ? 2u : 0u)) << (2 * t);
-          uint32_t b_hi = ((acc[2] >= 0.f ? 1u : 0u) | (acc[3] >= 0.f ? 2u : 0u)) << (2 * t);
+          plane_mma<D, NTW>(a_hi, a_lo, m_hi[2], m_lo[2], LD, warp * NTW, lane, acc);
+          uint32_t b_lo = 0, b_hi = 0;
+#pragma unroll
+          for (int i = 0; i < NTW; ++i) {
+            b_lo |= ((acc[i][0] >= 0.f ? 1u : 0u) | (acc[i][1] >= 0.f ? 2u : 0u)) << (8 * i + 2 * t);
+            b_hi |= ((acc[i][2] >= 0.f ? 1u : 0u) | (acc[i][3] >= 0.f ? 2u : 0u)) << (8 * i + 2 * t);
+          }
           b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 1);
           b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 1);
           b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 2);
           b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 2);
-          // byte `warp` of the row's D/8 sign bytes
-          if (t == 0 && slot_lo >= 0)
-            p.sign[slot_lo * p.sign_row_stride + head_lo * (D / 8) + warp] = uint8_t(b_lo);
-          if (t == 1 && slot_hi >= 0)
-            p.sign[slot_hi * p.sign_row_stride + head_hi * (D / 8) + warp] = uint8_t(b_hi);
+          // bytes NTW*warp .. of the row's D/8 sign bytes
+          uint8_t* d_lo = p.sign + slot_lo * p.sign_row_stride + head_lo * (D / 8) + NTW * warp;
+          uint8_t* d_hi = p.sign + slot_hi * p.sign_row_stride + head_hi * (D / 8) + NTW * warp;
+#pragma unroll
+          for (int i = 0; i < NTW; ++i) {
+            if (t == 0 && slot_lo >= 0) d_lo[i] = uint8_t(b_lo >> (8 * i));
+            if (t == 1 && slot_hi >= 0) d_hi[i] = uint8_t(b_hi >> (8 * i));
+          }
         }
         __syncthreads();  // planes and row data are rewritten by the next item
       }
