@@ -637,6 +637,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     const uint32_t my_ring = p.off_ring + uint32_t(lane) * stages * stage_bytes;
     const uint32_t my_q = p.off_q + uint32_t(lane) * qbuf_bytes;
     int produced = 0, issue_idx = 0, issue_stage = 0, issue_phase = 1, q_issued = 0, q_owed = -1;
+    const uint64_t stream_policy = l2_evict_first_policy();  // pages are read once
     // descriptor of run page i of team T
     auto describe = [&](int T, int i, int n_run, int64_t f0) {
       const int64_t wk = int64_t(blockIdx.x) * teams + T;
@@ -714,13 +715,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
             q_owed = d.z;
           }
           mbar_expect_tx(my_full + issue_stage, stage_bytes);
-          bulk_g2s(smem + my_ring + uint32_t(issue_stage) * stage_bytes,
-                   p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
-                   my_full + issue_stage);
+          bulk_g2s_hint(smem + my_ring + uint32_t(issue_stage) * stage_bytes,
+                        p.kv_cache + int64_t(d.x) * int64_t(page_bytes), page_bytes,
+                        my_full + issue_stage, stream_policy);
           if constexpr (QS)
-            bulk_g2s(smem + my_ring + uint32_t(issue_stage) * stage_bytes + page_bytes,
-                     p.kq_cache + int64_t(d.x) * int64_t(qpage_bytes), qpage_bytes,
-                     my_full + issue_stage);
+            bulk_g2s_hint(smem + my_ring + uint32_t(issue_stage) * stage_bytes + page_bytes,
+                          p.kq_cache + int64_t(d.x) * int64_t(qpage_bytes), qpage_bytes,
+                          my_full + issue_stage, stream_policy);
           ++issue_idx;
           if (++issue_stage == stages) { issue_stage = 0; issue_phase ^= 1; }
           progress = true;
