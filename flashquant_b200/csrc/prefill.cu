@@ -33,7 +33,7 @@ namespace fq {
 
 constexpr int kPfM = 128;       // query rows per CTA
 constexpr int kPfN = 64;        // KV tokens per tile
-constexpr int kPfThreads = 128;
+constexpr int kPfThreads = 256;  // two threads per query row: each takes half of the columns
 constexpr int kPfTmemCols = 256;
 constexpr float kPfPScaleLog2 = 8.f;  // fp16 weights are scaled by 2^8 ...
 constexpr float kPfMaxSlack = 6.f;    // ... and may exceed 1 by 2^6 before the reference exponent is raised
@@ -165,7 +165,8 @@ struct PrefillSmem {
   static constexpr uint32_t kRawTile = kPfN * (D / 2);
   static constexpr uint32_t kOffNorm = kOffRaw + 4 * kRawTile;      // nk*scale, lg2 nv, clamped
   static constexpr uint32_t kOffLut = kOffNorm + 3 * kPfN * 4;
-  static constexpr uint32_t kOffBar = kOffLut + 2 * 256 * 4;
+  static constexpr uint32_t kOffXch = kOffLut + 2 * 256 * 4;       // row maxima / sums exchange
+  static constexpr uint32_t kOffBar = kOffXch + kPfThreads * 4;
   static constexpr uint32_t kBytes = kOffBar + 64;
 };
 
@@ -184,8 +185,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   float* lv_s = vs_s + kPfN;
   uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem + S::kOffLut);
   uint32_t* lut_v = lut_k + 256;
+  float* xch = reinterpret_cast<float*>(smem + S::kOffXch);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  // threads r and r + 128 share query row r: the first takes columns 0..31 of a score tile
+  // (0..63 of the output), the second the rest; a warp reaches TMEM lanes 32*(warp%4)..+31
+  const int row = tid & (kPfM - 1), half = tid >> 7;
   // heavy (late) query tiles first: the causal work per tile grows with its index
   const int m_tile = int(gridDim.x) - 1 - int(blockIdx.x);
   const int hq = blockIdx.y, b = blockIdx.z;
@@ -236,7 +241,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;        // 64 columns
   const uint32_t tmem_o = tmem_base + 64;   // D columns
-  const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+  const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
 
   auto issue_raw = [&](int tile, int buf) {  // thread 0 only
     const int t0 = tile * kPfN;
@@ -251,7 +256,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   if (tid == 0 && n_tiles > 0) issue_raw(0, 0);
 
   float m_run = -INFINITY, l_run = 0.f;
-  const int q_pos = m0 + tid;
+  const int q_pos = m0 + row;
   bool dead = false;
 
   for (int tile = 0; tile < n_tiles && !dead; ++tile) {
@@ -312,8 +317,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     // pass 1: row maximum of logit*log2e + clamped log2|v| over the tile
     float mx = -INFINITY;
     auto row_max = [&](auto masked) {
-#pragma unroll
-      for (int c0 = 0; c0 < kPfN; c0 += 32) {
+      {
+        const int c0 = half * 32;
         float sv[32];
         tmem_ld32(tmem_s + lane_sel + c0, sv);
 #pragma unroll
@@ -337,6 +342,9 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (!dead) {
       if (unmasked) row_max(std::false_type{}); else row_max(std::true_type{});
     }
+    xch[tid] = mx;
+    __syncthreads();
+    mx = fmaxf(mx, xch[tid ^ kPfM]);  // the other half of the row
     // The reference exponent m only has to stay within kPfMaxSlack bits of the running maximum
     // (weights then stay below 2^14 in fp16), so the accumulator O, which lives in TMEM across
     // all tiles, is rescaled only when some row of the warp outgrows it by more than that.
@@ -346,7 +354,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
       const float alpha = (m_run == -INFINITY || !grew) ? 1.f : fast_exp2(m_run - m_new);
       if (tile > 0) {
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
           float o[32];
           tmem_ld32(tmem_o + lane_sel + c0, o);
 #pragma unroll
@@ -363,8 +371,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     // operand of the second product, [token chunk][row][16 B]
     auto weights = [&](auto masked) {
       const float neg_m = -mref;
-#pragma unroll
-      for (int c0 = 0; c0 < kPfN; c0 += 32) {
+      {
+        const int c0 = half * 32;
         float sv[32];
         tmem_ld32(tmem_s + lane_sel + c0, sv);
         uint32_t packed[16];
@@ -390,7 +398,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + tid * 16) =
+          *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + row * 16) =
               make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       }
     };
@@ -418,10 +426,14 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   // ---- epilogue: normalise, round, store the rotated-space row -----------------------------
   if (dead && tid == 0 && p.status) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
   {
-    const float inv = l_run > 0.f ? 1.f / (l_run * 256.f) : 0.f;  // 2^-kPfPScaleLog2
+    __syncthreads();  // the last tile's maxima have been read
+    xch[tid] = l_run;
+    __syncthreads();
+    const float l_row = l_run + xch[tid ^ kPfM];  // both halves of the row
+    const float inv = l_row > 0.f ? 1.f / (l_row * 256.f) : 0.f;  // 2^-kPfPScaleLog2
     float* dst = p.o_rot + ((int64_t(b) * p.hq + hq) * p.nq + q_pos) * D;
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
       float o[32];
       if (n_tiles > 0 && !dead) {
         tmem_ld32(tmem_o + lane_sel + c0, o);  // whole warps: the load is warp-collective
@@ -429,7 +441,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = 0.f;
       }
-      if (tid < rows) {
+      if (row < rows) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(dst + c0 + j) =
