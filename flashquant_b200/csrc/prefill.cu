@@ -1,22 +1,24 @@
 // Fused causal TQ4 FlashAttention-2 prefill for sm_100a on the 5th-generation tensor cores.
 //
-// One CTA of 128 threads owns 128 query rows of one (batch, query head) and walks the KV
-// sequence in tiles of 64 tokens, skipping tiles above the causal diagonal.  Per tile:
-//   * the packed K and V codes of the tile arrive by 1-D bulk copy (4 KB each, the next
-//     tile's copy is in flight while this one is processed);
+// One CTA of 256 threads owns 128 query rows of one (batch, query head) - two threads per
+// row, each with half of the columns - and walks the KV sequence in tiles of 64 tokens,
+// skipping tiles above the causal diagonal.  Per tile:
+//   * the packed K and V codes and their norms arrive by 1-D bulk copies, one tile ahead;
 //   * all threads turn codes into fp16 centroids (256-entry table of fp16 pairs) and store
 //     them as tcgen05 shared-memory operands; the norms are NOT applied here: |k| scales the
 //     score column, |v| is folded into the softmax weight, as in the decode kernel;
-//   * one thread issues S = Q K^T (tcgen05.mma, fp16 x fp16 -> fp32 in TMEM);
-//   * thread r reads row r of S from TMEM (tcgen05.ld), applies |k|, the scale and the
-//     causal mask, updates the online softmax and writes the fp16 weights as the A operand
-//     of the second product;
+//   * one thread issues S = Q K^T (tcgen05.mma, fp16 x fp16 -> fp32 in TMEM) - for the NEXT
+//     tile, into the other of two score buffers, so that it runs under this tile's softmax;
+//   * the two threads of row r read their halves of row r of S from TMEM (tcgen05.ld), apply
+//     |k|, the scale and - on tiles that touch the diagonal or the end - the causal mask,
+//     update the online softmax and write the fp16 weights as the A operand of the second
+//     product;
 //   * one thread issues O += P V into TMEM, where the accumulator stays across all tiles: the
 //     reference exponent of the online softmax is raised lazily (only when a row's scores
 //     outgrow it by more than 6 bits), and only then do the threads of that warp rescale their
-//     rows of O in TMEM (tcgen05.ld / tcgen05.st); the epilogue reads O once.
-// Two such CTAs fit an SM (94 KB of shared memory, 256 of the 512 TMEM columns each), so one
-// CTA's softmax overlaps the other's tensor work.
+//     rows of O in TMEM (tcgen05.ld / tcgen05.st); the epilogue reads O once.  The product
+//     runs under the next tile's key dequantisation.
+// Two such CTAs fit an SM (110 KB of shared memory, 256 of the 512 TMEM columns each).
 //
 // Shared-memory operands use the un-swizzled canonical layout: 8 x 16-byte core matrices,
 // laid out [k-chunk of 8 elements][row][16 bytes]; each k-chunk slab is padded by 16 bytes
@@ -157,31 +159,44 @@ struct PrefillSmem {
   static constexpr uint32_t kSlabQ = (kPfM + 1) * 16;             // one k-chunk of the Q tile
   static constexpr uint32_t kSlabKV = (kPfN + 1) * 16;            // one k-chunk of a K/V tile
   static constexpr uint32_t kSlabP = (kPfM + 1) * 16;             // one k-chunk of the P tile
+  static constexpr uint32_t kOpKV = kChunks * kSlabKV;            // one K or V operand tile
   static constexpr uint32_t kOffQ = 0;
-  static constexpr uint32_t kOffK = kOffQ + kChunks * kSlabQ;
-  static constexpr uint32_t kOffV = kOffK + kChunks * kSlabKV;
-  static constexpr uint32_t kOffP = kOffV + kChunks * kSlabKV;
-  static constexpr uint32_t kOffRaw = kOffP + (kPfN / 8) * kSlabP;  // 2 x (K codes, V codes)
+  static constexpr uint32_t kOffK = kOffQ + kChunks * kSlabQ;     // two K operand tiles
+  static constexpr uint32_t kOffV = kOffK + 2 * kOpKV;
+  static constexpr uint32_t kOffP = kOffV + kOpKV;
+  static constexpr uint32_t kOffRaw = kOffP + (kPfN / 8) * kSlabP;  // K codes, V codes
   static constexpr uint32_t kRawTile = kPfN * (D / 2);
-  static constexpr uint32_t kOffNorm = kOffRaw + 4 * kRawTile;      // nk*scale, lg2 nv, clamped
-  static constexpr uint32_t kOffLut = kOffNorm + 3 * kPfN * 4;
+  static constexpr uint32_t kOffNormRaw = kOffRaw + 2 * kRawTile;   // |k|, |v| as they arrive
+  static constexpr uint32_t kOffNorm = kOffNormRaw + 2 * kPfN * 4;  // 2 x nk*scale, nv*2^8, lg2 nv
+  static constexpr uint32_t kOffLut = kOffNorm + 4 * kPfN * 4;
   static constexpr uint32_t kOffXch = kOffLut + 2 * 256 * 4;       // row maxima / sums exchange
   static constexpr uint32_t kOffBar = kOffXch + kPfThreads * 4;
   static constexpr uint32_t kBytes = kOffBar + 64;
 };
 
+// Per tile the CUDA cores turn codes into operands and run the softmax, the tensor cores run
+// two products; the loop is arranged so that the two overlap inside one CTA as well:
+//   iteration t:  dequantise K(t+1)  |  wait for PV(t-1)  |  dequantise V(t)
+//                 issue S(t+1) = Q K(t+1)^T into the other score buffer        (tensor)
+//                 softmax of S(t) (issued one iteration earlier) -> P           (CUDA cores)
+//                 issue O += P V(t)                                             (tensor)
+// so a score product always has a whole softmax to complete in, and the PV product the next
+// tile's key dequantisation.  Codes and norms arrive by bulk copies one tile ahead.
 template <int D>
 __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(PrefillArgs p) {
   using S = PrefillSmem<D>;
   constexpr uint32_t kIdescS = umma_idesc(kPfM, kPfN, false);
   constexpr uint32_t kIdescO = umma_idesc(kPfM, D, true);
   extern __shared__ __align__(1024) unsigned char smem[];
-  uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + S::kOffBar);  // [2]
-  uint64_t* bar_s = bar_raw + 2;
-  uint64_t* bar_o = bar_raw + 3;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_raw + 4);
-  float* nk_s = reinterpret_cast<float*>(smem + S::kOffNorm);
-  float* vs_s = nk_s + kPfN;
+  uint64_t* bar_k = reinterpret_cast<uint64_t*>(smem + S::kOffBar);  // K codes (+ norms) landed
+  uint64_t* bar_v = bar_k + 1;
+  uint64_t* bar_s = bar_k + 2;  // [2]: score product of an even / odd tile completed
+  uint64_t* bar_o = bar_k + 4;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_k + 5);
+  float* nk_raw = reinterpret_cast<float*>(smem + S::kOffNormRaw);
+  float* nv_raw = nk_raw + kPfN;
+  float* nk_s = reinterpret_cast<float*>(smem + S::kOffNorm);  // [2][64], by tile parity
+  float* vs_s = nk_s + 2 * kPfN;
   float* lv_s = vs_s + kPfN;
   uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem + S::kOffLut);
   uint32_t* lut_v = lut_k + 256;
@@ -207,12 +222,15 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   const uint8_t* vc_base = p.v_packed + (int64_t(b) * p.hkv + hkv) * p.nkv * (D / 2);
   const float* kn_base = p.k_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
   const float* vn_base = p.v_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
+  // norms ride along with the codes when a bulk copy can take them (16-byte granularity)
+  const bool norm_bulk = ((reinterpret_cast<uintptr_t>(kn_base) | reinterpret_cast<uintptr_t>(vn_base)) & 15) == 0;
 
   // ---- set-up ---------------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(bar_raw, 1);
-    mbar_init(bar_raw + 1, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_s + 1, 1);
     mbar_init(bar_o, 1);
     mbar_fence_init();
   }
@@ -229,113 +247,185 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   {
     const __half* qsrc = p.q_rot + ((int64_t(b) * p.hq + hq) * p.nq + m0) * D;
     for (int i = tid; i < kPfM * int(S::kChunks); i += kPfThreads) {
-      const int row = i / int(S::kChunks), kc = i % int(S::kChunks);
+      const int r = i / int(S::kChunks), kc = i % int(S::kChunks);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row < rows) v = *reinterpret_cast<const uint4*>(qsrc + int64_t(row) * D + kc * 8);
-      *reinterpret_cast<uint4*>(smem + S::kOffQ + kc * S::kSlabQ + row * 16) = v;
+      if (r < rows) v = *reinterpret_cast<const uint4*>(qsrc + int64_t(r) * D + kc * 8);
+      *reinterpret_cast<uint4*>(smem + S::kOffQ + kc * S::kSlabQ + r * 16) = v;
     }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_s = tmem_base;        // 64 columns
-  const uint32_t tmem_o = tmem_base + 64;   // D columns
+  const uint32_t tmem_o = tmem_base + 2 * kPfN;  // behind the two score buffers; D columns
   const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
 
-  auto issue_raw = [&](int tile, int buf) {  // thread 0 only
-    const int t0 = tile * kPfN;
-    const int n_tok = kv_end - t0 < kPfN ? kv_end - t0 : kPfN;
-    const uint32_t bytes = uint32_t(n_tok) * (D / 2);
-    mbar_expect_tx(bar_raw + buf, 2 * bytes);
-    bulk_g2s(smem + S::kOffRaw + (2 * buf) * S::kRawTile, kc_base + int64_t(t0) * (D / 2), bytes,
-             bar_raw + buf);
-    bulk_g2s(smem + S::kOffRaw + (2 * buf + 1) * S::kRawTile, vc_base + int64_t(t0) * (D / 2),
-             bytes, bar_raw + buf);
+  // 8-entry key table in registers: low and high bytes of the fp16 centroids
+  const bool k_by_permute = p.nck <= 8;
+  uint32_t tl0 = 0, tl1 = 0, th0 = 0, th1 = 0;
+  if (k_by_permute) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t h =
+          uint32_t(__half_as_ushort(__float2half_rn(i < p.nck ? p.cent_k[i] : 0.f)));
+      const uint32_t lo8 = (h & 0xffu) << (8 * (i & 3)), hi8 = (h >> 8) << (8 * (i & 3));
+      if (i < 4) { tl0 |= lo8; th0 |= hi8; } else { tl1 |= lo8; th1 |= hi8; }
+    }
+  }
+  auto tile_tokens = [&](int tile) {
+    const int left = kv_end - tile * kPfN;
+    return left < kPfN ? left : kPfN;
   };
-  if (tid == 0 && n_tiles > 0) issue_raw(0, 0);
+  // thread 0: codes of one tile (and its norms, when a bulk copy can take them)
+  auto issue_codes = [&](int tile, bool is_k) {
+    const int t0 = tile * kPfN, n_tok = tile_tokens(tile);
+    const uint32_t bytes = uint32_t(n_tok) * (D / 2);
+    const bool with_norms = norm_bulk && n_tok == kPfN;
+    uint64_t* bar = is_k ? bar_k : bar_v;
+    mbar_expect_tx(bar, bytes + (with_norms ? kPfN * 4 : 0));
+    bulk_g2s(smem + S::kOffRaw + (is_k ? 0 : S::kRawTile),
+             (is_k ? kc_base : vc_base) + int64_t(t0) * (D / 2), bytes, bar);
+    if (with_norms)
+      bulk_g2s(is_k ? nk_raw : nv_raw, (is_k ? kn_base : vn_base) + t0, kPfN * 4, bar);
+  };
+  // all threads: codes of the landed tile -> fp16 operand tile at `op_off`
+  auto dequantise = [&](int tile, bool is_k, uint32_t op_off) {
+    const int n_tok = tile_tokens(tile);
+    const uint32_t* raw =
+        reinterpret_cast<const uint32_t*>(smem + S::kOffRaw + (is_k ? 0 : S::kRawTile));
+    const uint32_t* lut = is_k ? lut_k : lut_v;
+    constexpr int kWords = kPfN * (D / 8);  // 4 code bytes = 8 values = one 16-byte chunk
+    if (is_k && k_by_permute) {
+      // at most 8 key centroids: the codes select bytes of a register-resident table, no
+      // shared-memory look-ups (whose random addresses conflict in the banks)
+      for (int i = tid; i < kWords; i += kPfThreads) {
+        const int tok = i / int(S::kChunks), kc = i % int(S::kChunks);
+        const uint32_t w = tok < n_tok ? raw[i] : 0u;
+        // nibbles of w, low to high: odd0, even0, odd1, even1, ...
+        const uint32_t la = prmt(tl0, tl1, w), ha = prmt(th0, th1, w);
+        const uint32_t lb = prmt(tl0, tl1, w >> 16), hb = prmt(th0, th1, w >> 16);
+        uint4 o;
+        o.x = prmt(la, ha, 0x4051);  // (even0, odd0)
+        o.y = prmt(la, ha, 0x6273);
+        o.z = prmt(lb, hb, 0x4051);
+        o.w = prmt(lb, hb, 0x6273);
+        *reinterpret_cast<uint4*>(smem + op_off + kc * S::kSlabKV + tok * 16) = o;
+      }
+      return;
+    }
+    for (int i = tid; i < kWords; i += kPfThreads) {
+      const int tok = i / int(S::kChunks), kc = i % int(S::kChunks);
+      const uint32_t w = tok < n_tok ? raw[i] : 0u;
+      uint4 o;
+      o.x = lut[w & 0xff]; o.y = lut[(w >> 8) & 0xff];
+      o.z = lut[(w >> 16) & 0xff]; o.w = lut[w >> 24];
+      *reinterpret_cast<uint4*>(smem + op_off + kc * S::kSlabKV + tok * 16) = o;
+    }
+  };
+  // threads 0..63: the norm of token `tid` of the tile, from the bulk copy or from memory
+  auto tile_norm = [&](int tile, bool is_k) {
+    const int t0 = tile * kPfN, n_tok = tile_tokens(tile);
+    if (norm_bulk && n_tok == kPfN) return (is_k ? nk_raw : nv_raw)[tid];
+    return tid < n_tok ? (is_k ? kn_base : vn_base)[t0 + tid] : 0.f;
+  };
+  auto issue_scores = [&](int tile) {  // thread 0
+    const uint32_t qa = smem_u32(smem + S::kOffQ);
+    const uint32_t ka = smem_u32(smem + S::kOffK + (tile & 1) * S::kOpKV);
+#pragma unroll
+    for (int s = 0; s < D / 16; ++s)
+      umma_f16(tmem_base + (tile & 1) * kPfN, smem_desc(qa + 2 * s * S::kSlabQ, S::kSlabQ, 128),
+               smem_desc(ka + 2 * s * S::kSlabKV, S::kSlabKV, 128), kIdescS, s > 0);
+    umma_commit(bar_s + (tile & 1));
+  };
 
   float m_run = -INFINITY, l_run = 0.f;
   const int q_pos = m0 + row;
   bool dead = false;
 
-  for (int tile = 0; tile < n_tiles && !dead; ++tile) {
-    const int buf = tile & 1;
-    const int t0 = tile * kPfN;
-    const int n_tok = kv_end - t0 < kPfN ? kv_end - t0 : kPfN;
-    // the previous tile's P V still reads the V and P operands in shared memory
-    if (tile > 0 && !mbar_wait(bar_o, (tile - 1) & 1)) dead = true;
-    tc_fence_after();
-    // ---- norms of the tile --------------------------------------------------------------
-    if (tid < kPfN) {
-      float nk = 0.f, nv = 0.f;
-      if (tid < n_tok) { nk = kn_base[t0 + tid]; nv = vn_base[t0 + tid]; }
-      nk_s[tid] = nk * p.scale_log2;
-      vs_s[tid] = nv * 256.f;  // 2^kPfPScaleLog2
-      lv_s[tid] = fmaxf(fast_log2(nv), -40.f);
+  // ---- prologue: K(0) -> operand, S(0) issued, K(1) and V(0) on their way ------------------
+  if (n_tiles > 0) {
+    if (tid == 0) {
+      issue_codes(0, true);
+      issue_codes(0, false);
     }
-    // ---- codes -> fp16 operands ------------------------------------------------------------
-    if (!mbar_wait(bar_raw + buf, (tile >> 1) & 1)) { dead = true; }
+    if (!mbar_wait(bar_k, 0)) dead = true;
     if (!dead) {
-      const uint32_t* rk = reinterpret_cast<const uint32_t*>(smem + S::kOffRaw + (2 * buf) * S::kRawTile);
-      const uint32_t* rv = reinterpret_cast<const uint32_t*>(smem + S::kOffRaw + (2 * buf + 1) * S::kRawTile);
-      constexpr int kWords = kPfN * (D / 8);  // 4 code bytes = 8 values = one 16-byte chunk
-      for (int i = tid; i < kWords; i += kPfThreads) {
-        const int tok = i / int(S::kChunks), kc = i % int(S::kChunks);
-        uint32_t wk = 0, wv = 0;
-        if (tok < n_tok) { wk = rk[i]; wv = rv[i]; }
-        uint4 ko, vo;
-        ko.x = lut_k[wk & 0xff]; ko.y = lut_k[(wk >> 8) & 0xff];
-        ko.z = lut_k[(wk >> 16) & 0xff]; ko.w = lut_k[wk >> 24];
-        vo.x = lut_v[wv & 0xff]; vo.y = lut_v[(wv >> 8) & 0xff];
-        vo.z = lut_v[(wv >> 16) & 0xff]; vo.w = lut_v[wv >> 24];
-        *reinterpret_cast<uint4*>(smem + S::kOffK + kc * S::kSlabKV + tok * 16) = ko;
-        *reinterpret_cast<uint4*>(smem + S::kOffV + kc * S::kSlabKV + tok * 16) = vo;
-      }
+      if (tid < kPfN) nk_s[tid] = tile_norm(0, true) * p.scale_log2;
+      dequantise(0, true, S::kOffK);
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- S = Q K^T ----------------------------------------------------------------------------
     if (tid == 0 && !dead) {
       tc_fence_after();
-      if (tile + 1 < n_tiles) issue_raw(tile + 1, buf ^ 1);
-      const uint32_t qa = smem_u32(smem + S::kOffQ), ka = smem_u32(smem + S::kOffK);
-#pragma unroll
-      for (int s = 0; s < D / 16; ++s)
-        umma_f16(tmem_s, smem_desc(qa + 2 * s * S::kSlabQ, S::kSlabQ, 128),
-                 smem_desc(ka + 2 * s * S::kSlabKV, S::kSlabKV, 128), kIdescS, s > 0);
-      umma_commit(bar_s);
+      issue_scores(0);
+      if (n_tiles > 1) issue_codes(1, true);
     }
-    if (!mbar_wait(bar_s, tile & 1)) dead = true;
-    tc_fence_after();
+  }
 
-    // ---- online softmax on row `tid` ---------------------------------------------------------
+  for (int tile = 0; tile < n_tiles && !dead; ++tile) {
+    const int t0 = tile * kPfN;
+    const int n_tok = tile_tokens(tile);
+    const bool more = tile + 1 < n_tiles;
+    // ---- K(t+1): codes -> operand (the other K buffer), |k| * scale by tile parity -----------
+    if (more) {
+      if (!mbar_wait(bar_k, (tile + 1) & 1)) dead = true;
+      if (!dead) {
+        if (tid < kPfN) nk_s[((tile + 1) & 1) * kPfN + tid] = tile_norm(tile + 1, true) * p.scale_log2;
+        dequantise(tile + 1, true, S::kOffK + ((tile + 1) & 1) * S::kOpKV);
+      }
+    }
+    // ---- V(t): the previous tile's P V still reads the V and P operands ----------------------
+    if (tile > 0 && !mbar_wait(bar_o, (tile - 1) & 1)) dead = true;
+    tc_fence_after();
+    if (!mbar_wait(bar_v, tile & 1)) dead = true;
+    if (!dead) {
+      if (tid < kPfN) {
+        const float nv = tile_norm(tile, false);
+        vs_s[tid] = nv * 256.f;  // 2^kPfPScaleLog2
+        lv_s[tid] = fmaxf(fast_log2(nv), -40.f);
+      }
+      dequantise(tile, false, S::kOffV);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && !dead) {
+      tc_fence_after();
+      if (more) issue_scores(tile + 1);  // runs while this tile's softmax does
+      if (tile + 2 < n_tiles) issue_codes(tile + 2, true);
+      if (more) issue_codes(tile + 1, false);
+    }
+    // ---- S(t), issued one iteration ago -----------------------------------------------------
+    if (!mbar_wait(bar_s + (tile & 1), (tile >> 1) & 1)) dead = true;
+    tc_fence_after();
+    const uint32_t tmem_s = tmem_base + (tile & 1) * kPfN;
+    const float* nk_t = nk_s + (tile & 1) * kPfN;
+
+    // ---- online softmax on row `row` ---------------------------------------------------------
     // A tile that lies wholly below the diagonal of every row of the CTA and is full needs no
     // masking: the common case gets a loop body without predicates.
     const bool unmasked = n_tok == kPfN && (!p.causal || t0 + kPfN - 1 <= m0);
-    // pass 1: row maximum of logit*log2e + clamped log2|v| over the tile
+    // pass 1: row maximum of logit*log2e + clamped log2|v| over this thread's half of the tile
     float mx = -INFINITY;
     auto row_max = [&](auto masked) {
-      {
-        const int c0 = half * 32;
-        float sv[32];
-        tmem_ld32(tmem_s + lane_sel + c0, sv);
+      const int c0 = half * 32;
+      float sv[32];
+      tmem_ld32(tmem_s + lane_sel + c0, sv);
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 nk4 = *reinterpret_cast<const float4*>(nk_s + c0 + j);
-          const float4 lv4 = *reinterpret_cast<const float4*>(lv_s + c0 + j);
-          const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, lv[4] = {lv4.x, lv4.y, lv4.z, lv4.w};
+      for (int j = 0; j < 32; j += 4) {
+        const float4 nk4 = *reinterpret_cast<const float4*>(nk_t + c0 + j);
+        const float4 lv4 = *reinterpret_cast<const float4*>(lv_s + c0 + j);
+        const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, lv[4] = {lv4.x, lv4.y, lv4.z, lv4.w};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float e = fmaf(sv[j + u], nk[u], lv[u]);
-            if constexpr (decltype(masked)::value) {
-              const int col = c0 + j + u;
-              const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
-              e = ok ? e : -INFINITY;
-            }
-            mx = fmaxf(mx, e);
+        for (int u = 0; u < 4; ++u) {
+          float e = fmaf(sv[j + u], nk[u], lv[u]);
+          if constexpr (decltype(masked)::value) {
+            const int col = c0 + j + u;
+            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+            e = ok ? e : -INFINITY;
           }
+          mx = fmaxf(mx, e);
         }
       }
     };
@@ -367,40 +457,38 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     }
     const float mref = (m_run == -INFINITY) ? 0.f : m_run;
     // pass 2: p = 2^(logit*log2e - m) feeds the denominator; the weight that meets the value
-    // codes is p*|v|*2^14 (<= 2^14 because m >= logit*log2e + log2|v|), stored as the fp16 A
+    // codes is p*|v|*2^8 (<= 2^14 because m >= logit*log2e + log2|v| - 6), stored as the fp16 A
     // operand of the second product, [token chunk][row][16 B]
     auto weights = [&](auto masked) {
       const float neg_m = -mref;
-      {
-        const int c0 = half * 32;
-        float sv[32];
-        tmem_ld32(tmem_s + lane_sel + c0, sv);
-        uint32_t packed[16];
+      const int c0 = half * 32;
+      float sv[32];
+      tmem_ld32(tmem_s + lane_sel + c0, sv);
+      uint32_t packed[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 nk4 = *reinterpret_cast<const float4*>(nk_s + c0 + j);
-          const float4 vs4 = *reinterpret_cast<const float4*>(vs_s + c0 + j);
-          const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, vs[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
-          float w[4];
+      for (int j = 0; j < 32; j += 4) {
+        const float4 nk4 = *reinterpret_cast<const float4*>(nk_t + c0 + j);
+        const float4 vs4 = *reinterpret_cast<const float4*>(vs_s + c0 + j);
+        const float nk[4] = {nk4.x, nk4.y, nk4.z, nk4.w}, vs[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+        float w[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float pe = fast_exp2(fmaf(sv[j + u], nk[u], neg_m));
-            if constexpr (decltype(masked)::value) {
-              const int col = c0 + j + u;
-              const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
-              pe = ok ? pe : 0.f;
-            }
-            l_run += pe;
-            w[u] = pe * vs[u];
+        for (int u = 0; u < 4; ++u) {
+          float pe = fast_exp2(fmaf(sv[j + u], nk[u], neg_m));
+          if constexpr (decltype(masked)::value) {
+            const int col = c0 + j + u;
+            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+            pe = ok ? pe : 0.f;
           }
-          packed[j / 2] = pack_half2(w[0], w[1]);
-          packed[j / 2 + 1] = pack_half2(w[2], w[3]);
+          l_run += pe;
+          w[u] = pe * vs[u];
         }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + row * 16) =
-              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+        packed[j / 2] = pack_half2(w[0], w[1]);
+        packed[j / 2 + 1] = pack_half2(w[2], w[3]);
       }
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(smem + S::kOffP + (c0 / 8 + ch) * S::kSlabP + row * 16) =
+            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
     };
     if (!dead) {
       if (unmasked) weights(std::false_type{}); else weights(std::true_type{});
@@ -408,7 +496,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- O_tile = P V ---------------------------------------------------------------------------
+    // ---- O += P V(t) ------------------------------------------------------------------------------
     if (tid == 0 && !dead) {
       tc_fence_after();
       const uint32_t pa = smem_u32(smem + S::kOffP), va = smem_u32(smem + S::kOffV);
