@@ -1,13 +1,13 @@
-// Row rotation for sm_100a: out[r] = round_T(x[r] Pi^T) or round_T(x[r] Pi), fp32 FMA.
+// Row rotation for sm_100a: out[r] = round_T(x[r] Pi^T) or round_T(x[r] Pi).
 //
 // Used around the prefill attention kernel, which works in rotated space: the query rows go
 // through Pi^T before it, the attention rows through Pi after it.  The reference does both
 // as fp32 matmuls followed by a cast to the activation type
 // (src/flashquant/kernels/attention.py:99-101, src/flashquant/kernels/cpu_reference.py:225-226),
-// so the contraction here is fp32 as well and only the result is rounded.
-//
-// Persistent CTAs keep the matrix in shared memory; a warp owns 8 rows of a 64-row tile, a
-// lane 4 consecutive output coordinates (head_dim 128) or 2 (head_dim 64).
+// so the contraction here has fp32-level accuracy as well and only the result is rounded:
+// head_dim 128 runs on the tensor pipe with split-fp16 operands (below), head_dim 64 as an
+// fp32 FMA contraction (persistent CTAs keep the matrix in shared memory; a warp owns 8 rows
+// of a 64-row tile, a lane 2 consecutive output coordinates).
 #include "fq_common.cuh"
 
 namespace fq {
@@ -104,6 +104,162 @@ __global__ void __launch_bounds__(kRotThreads, 1) rotate_rows_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------
+// head_dim 128 on the tensor pipe.  Products of fp32-level accuracy from fp16 MMAs: every
+// operand is split into hi = fp16(v) and lo' = fp16((v - hi) * 2^11); hi*hi goes to one fp32
+// accumulator, hi*lo' + lo'*hi to a second one scaled by 2^-11 at the end (lo*lo, 2^-22 of a
+// product, is dropped).  The matrix stays in shared memory as hi / lo' planes; a warp owns
+// 16 rows end to end: their fragments come straight from global memory and stay in
+// registers while the warp walks the 16 column tiles four at a time (ldmatrix for the matrix
+// fragments), so the row loop has no barrier.
+// ------------------------------------------------------------------------------------
+constexpr int kRtThreads = 256;
+constexpr int kRtLd = 128 + 8;  // halves per plane row: ldmatrix rows then hit 32 banks
+
+__device__ __forceinline__ void rt_split(float v, __half& hi, __half& lo) {
+  hi = __float2half_rn(v);
+  lo = __float2half_rn((v - __half2float(hi)) * 2048.f);
+}
+__device__ __forceinline__ uint32_t rt_pack(__half a, __half b) {
+  return uint32_t(__half_as_ushort(a)) | (uint32_t(__half_as_ushort(b)) << 16);
+}
+__device__ __forceinline__ float2 rt_load2(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+__device__ __forceinline__ float2 rt_load2(const __half* p) {
+  return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
+__device__ __forceinline__ float2 rt_load2(const __nv_bfloat16* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <typename TOut>
+__device__ __forceinline__ void rt_store2(TOut* p, float a, float b);
+template <>
+__device__ __forceinline__ void rt_store2<__half>(__half* p, float a, float b) {
+  *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b);
+}
+template <>
+__device__ __forceinline__ void rt_store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
+__global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
+    const TIn* __restrict__ x, const float* __restrict__ rotation, TOut* __restrict__ out,
+    int64_t n_rows) {
+  constexpr int D = 128;
+  extern __shared__ __align__(16) unsigned char rt_smem[];
+  __half* b_hi = reinterpret_cast<__half*>(rt_smem);  // plane[n][k] = B[k][n]
+  __half* b_lo = b_hi + D * kRtLd;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  // out = x Pi^T: B[k][n] = Pi[n][k] (the matrix as it is); out = x Pi: B[k][n] = Pi[k][n]
+  for (int b0 = 0; b0 < D * D / kRtThreads; b0 += 16) {
+    float v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) v[u] = rotation[tid + (b0 + u) * kRtThreads];  // coalesced
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int i = tid + (b0 + u) * kRtThreads;
+      const int r = i / D, c = i % D;  // element Pi[r][c]
+      const int n = kTranspose ? r : c, k = kTranspose ? c : r;
+      __half h, l;
+      rt_split(v[u], h, l);
+      b_hi[n * kRtLd + k] = h;
+      b_lo[n * kRtLd + k] = l;
+    }
+  }
+  __syncthreads();
+
+  const int j = lane >> 3, r8 = lane & 7;  // ldmatrix: lanes 8j..8j+7 give the rows of matrix j
+  // matrix j = plane j>>1 (hi, lo'), k-segment j&1 of the column tile's 8 rows
+  const __half* pb = ((j >> 1) ? b_lo : b_hi) + r8 * kRtLd + 8 * (j & 1);
+  const int64_t n_mtiles = (n_rows + 15) / 16;
+  for (int64_t mt = int64_t(blockIdx.x) * (kRtThreads / 32) + warp; mt < n_mtiles;
+       mt += int64_t(gridDim.x) * (kRtThreads / 32)) {
+    const int64_t r0 = mt * 16 + g, r1 = r0 + 8;
+    const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
+    const TIn* x0 = x + (ok0 ? r0 : 0) * D + 2 * t;
+    const TIn* x1 = x + (ok1 ? r1 : 0) * D + 2 * t;
+    uint32_t xh[D / 16][4], xl[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      float2 f[4];
+      f[0] = ok0 ? rt_load2(x0 + 16 * ks) : make_float2(0.f, 0.f);
+      f[1] = ok1 ? rt_load2(x1 + 16 * ks) : make_float2(0.f, 0.f);
+      f[2] = ok0 ? rt_load2(x0 + 16 * ks + 8) : make_float2(0.f, 0.f);
+      f[3] = ok1 ? rt_load2(x1 + 16 * ks + 8) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __half h0, l0, h1, l1;
+        rt_split(f[i].x, h0, l0);
+        rt_split(f[i].y, h1, l1);
+        xh[ks][i] = rt_pack(h0, h1);
+        xl[ks][i] = rt_pack(l0, l1);
+      }
+    }
+#pragma unroll 1
+    for (int grp = 0; grp < 4; ++grp) {  // column tiles 4*grp .. 4*grp+3
+      float hi[4][4], co[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) hi[i][c] = co[i][c] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t b[4];  // b0 hi, b1 hi, b0 lo', b1 lo'
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
+                       : "r"(smem_u32(pb + (grp * 4 + i) * 8 * kRtLd + 16 * ks)));
+          mma_f16(hi[i], xh[ks][0], xh[ks][1], xh[ks][2], xh[ks][3], b[0], b[1]);
+          mma_f16(co[i], xh[ks][0], xh[ks][1], xh[ks][2], xh[ks][3], b[2], b[3]);
+          mma_f16(co[i], xl[ks][0], xl[ks][1], xl[ks][2], xl[ks][3], b[0], b[1]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          v[c] = fmaf(co[i][c], 1.f / 2048.f, hi[i][c]);
+          if constexpr (kRoundViaIn) v[c] = to_f32(from_f32<TIn>(v[c]));  // round to x's type first
+        }
+        const int col = 8 * (grp * 4 + i) + 2 * t;
+        if (ok0) rt_store2<TOut>(out + r0 * D + col, v[0], v[1]);
+        if (ok1) rt_store2<TOut>(out + r1 * D + col, v[2], v[3]);
+      }
+    }
+  }
+}
+
+template <typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
+static int launch_rotate_tc(const void* x, const float* rotation, void* out, int64_t n_rows,
+                            cudaStream_t stream) {
+  const size_t smem = size_t(2) * 128 * kRtLd * sizeof(__half);
+  auto kern = rotate_rows_tc_kernel<TIn, TOut, kTranspose, kRoundViaIn>;
+  static thread_local int set_dev = -1;
+  static thread_local int sms = 148;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (set_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "rotate: shared memory opt-in refused: %s", cudaGetErrorString(e));
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    set_dev = dev;
+  }
+  const int64_t warp_tiles = (n_rows + 15) / 16;
+  if (warp_tiles == 0) return FQ_OK;
+  const int64_t ctas_needed = (warp_tiles + kRtThreads / 32 - 1) / (kRtThreads / 32);
+  const int grid = int(ctas_needed < 2 * int64_t(sms) ? ctas_needed : 2 * int64_t(sms));
+  kern<<<grid, kRtThreads, smem, stream>>>(static_cast<const TIn*>(x), rotation,
+                                          static_cast<TOut*>(out), n_rows);
+  return check_launch("rotate kernel launch");
+}
+
 template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 static int launch_rotate_t(const void* x, const float* rotation, void* out, int64_t n_rows,
                            cudaStream_t stream) {
@@ -133,8 +289,8 @@ int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* ou
                      int64_t n_rows, int head_dim, cudaStream_t stream) {
   if (head_dim == 128)
     return dtype == FQ_BF16
-               ? launch_rotate_t<128, __nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream)
-               : launch_rotate_t<128, __half, __half, true, true>(q, rotation, out, n_rows, stream);
+               ? launch_rotate_tc<__nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream)
+               : launch_rotate_tc<__half, __half, true, true>(q, rotation, out, n_rows, stream);
   return dtype == FQ_BF16
              ? launch_rotate_t<64, __nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream)
              : launch_rotate_t<64, __half, __half, true, true>(q, rotation, out, n_rows, stream);
@@ -145,8 +301,8 @@ int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out,
                 int head_dim, cudaStream_t stream) {
   if (head_dim == 128)
     return dtype == FQ_BF16
-               ? launch_rotate_t<128, float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)
-               : launch_rotate_t<128, float, __half, false, false>(o_rot, rotation, out, n_rows, stream);
+               ? launch_rotate_tc<float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)
+               : launch_rotate_tc<float, __half, false, false>(o_rot, rotation, out, n_rows, stream);
   return dtype == FQ_BF16
              ? launch_rotate_t<64, float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)
              : launch_rotate_t<64, float, __half, false, false>(o_rot, rotation, out, n_rows, stream);
