@@ -9,22 +9,20 @@
 // either side with any summation order) at a third of the multiply-add issue slots of an fp32
 // FMA contraction, which was the bound of this kernel before.
 //
-// A CTA of 16 warps keeps the matrices resident in shared memory as fp16 hi / lo' planes (the
-// same bytes as fp32) and walks over tiles of 16 vectors: K of the tile, then V.  Warp w
-// loads and normalises vector w of the tile; the first eight warps (head_dim 128) own two
-// column tiles each of every product (fragments by ldmatrix: per 16 values of k two loads
-// for the left operand, shared by the tiles, then one load and three MMAs per tile: one tile
-// per warp is bound by the shared-memory instruction queue, four leave too few warps); the
-// left operand
-// (x_hat, then the centroid vector, then the residual) is exchanged through shared memory as
-// hi / lo' planes, so a K tile of the two-stage quantiser costs six block-wide barriers.  The operation order is the
+// A CTA of 8 warps keeps the matrices resident in shared memory as fp16 hi / lo' planes (the
+// same bytes as fp32).  A warp owns a tile of 16 vectors end to end, K of the tile then V:
+// the rows come from global memory straight into MMA fragments, the products walk the column
+// tiles four at a time with the matrix fragments from ldmatrix, and the chain of the
+// two-stage quantiser stays in registers - an accumulator tile pair is exactly the left
+// operand fragment of the next product (codes -> centroids -> x_tilde -> residual -> signs) -
+// so the tile loop has no barrier and no shared-memory exchange.  The operation order is the
 // reference's (normalise, then rotate); the tie rule is bucketize(right=False).
 #include "fq_common.cuh"
 
 namespace fq {
 
-constexpr int kCompressThreads = 512;
-constexpr int kCompressWarps = 16;
+constexpr int kCompressThreads = 256;
+constexpr int kCompressWarps = 8;
 
 struct CompressArgs {
   const void* src[2];  // [0]: K (or the only source), [1]: V
@@ -53,9 +51,6 @@ struct CompressArgs {
   int64_t num_slots;
 };
 
-#ifndef FQ_COMPRESS_NTW
-#define FQ_COMPRESS_NTW 2
-#endif
 constexpr int kTileRows = 16;         // vectors per tile = rows of one MMA
 constexpr float kLoScale = 2048.f;    // lo' = (v - hi) * 2^11
 constexpr float kLoUnscale = 1.f / 2048.f;
@@ -66,13 +61,10 @@ template <int D, bool QJL>
 struct CompressSmem {
   static constexpr int kLd = D + 8;                        // halves per row
   static constexpr size_t kPlane = size_t(D) * kLd * 2;    // one matrix plane, bytes
-  static constexpr size_t kAPlane = size_t(kTileRows) * kLd * 2;
   static constexpr int kMats = QJL ? 3 : 1;
-  static constexpr size_t kOffA = kPlane * 2 * kMats;      // hi and lo' plane per matrix
-  static constexpr size_t kOffX = kOffA + 2 * kAPlane;      // the tile's vectors as fp32
-  static constexpr size_t kOffMeta = kOffX + (QJL ? size_t(kTileRows) * (D + 8) * 4 : 0);
-  // meta: nrm[16] f32, gpart[16][16] f32, bnd[2][16] f32, cent[16] f32, slot[16] i64, head[16] i32
-  static constexpr size_t kBytes = kOffMeta + (16 + 256 + 32 + 16) * 4 + 16 * 8 + 16 * 4;
+  static constexpr size_t kOffMeta = kPlane * 2 * kMats;   // hi and lo' plane per matrix
+  // meta: bnd[2][16] f32, cent[16] f32
+  static constexpr size_t kBytes = kOffMeta + (32 + 16) * 4;
 };
 
 __device__ __forceinline__ void split_hi_lo(float v, __half& hi, __half& lo) {
@@ -95,10 +87,10 @@ __device__ __forceinline__ int bucketize15(float y, const float* __restrict__ sb
 // Stage one D x D matrix as hi / lo' planes: plane[n][k] = get(n, k).  Thread i walks the
 // matrix in the order that makes `get` read global memory contiguously (`k_fast`: k runs
 // fastest, else n).
-template <int D, typename Get>
+template <int D, int kThreads = kCompressThreads, typename Get>
 __device__ __forceinline__ void stage_matrix(__half* hi, __half* lo, int ld, bool k_fast, Get get,
                                              int tid) {
-  constexpr int kPer = D * D / kCompressThreads;  // elements per thread
+  constexpr int kPer = D * D / kThreads;  // elements per thread
   constexpr int kBatch = kPer < 16 ? kPer : 16;   // loads in flight per thread
   static_assert(kPer % kBatch == 0, "matrix size must be a multiple of the batch");
 #pragma unroll 1
@@ -106,12 +98,12 @@ __device__ __forceinline__ void stage_matrix(__half* hi, __half* lo, int ld, boo
     float v[kBatch];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const int i = tid + (b + u) * kCompressThreads;
+      const int i = tid + (b + u) * kThreads;
       v[u] = get(k_fast ? i / D : i % D, k_fast ? i % D : i / D);
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const int i = tid + (b + u) * kCompressThreads;
+      const int i = tid + (b + u) * kThreads;
       const int n = k_fast ? i / D : i % D, k = k_fast ? i % D : i / D;
       __half h, l;
       split_hi_lo(v[u], h, l);
@@ -126,6 +118,309 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row_pt
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(smem_u32(row_ptr)));
 }
+
+// One product of a 16-row tile held in registers with a resident matrix, four column tiles at
+// a time: acc[i][c] (C-fragment layout: c0,c1 = row g, columns 8*nt + 2t, +1; c2,c3 = row g+8)
+// for nt = 4*grp + i.  ah / al: the left operand's hi / lo' fragments, [k-step][a0..a3].
+template <int D>
+__device__ __forceinline__ void reg_mma_group(const uint32_t (&ah)[D / 16][4],
+                                              const uint32_t (&al)[D / 16][4],
+                                              const __half* __restrict__ pb, int ld, int grp,
+                                              float (&acc)[4][4]) {
+  float hi[4][4], co[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) hi[i][c] = co[i][c] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t b[4];  // b0 hi, b1 hi, b0 lo', b1 lo'
+      ldmatrix_x4(b, pb + (grp * 4 + i) * 8 * ld + 16 * ks);
+      mma_f16(hi[i], ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], b[0], b[1]);
+      mma_f16(co[i], ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], b[2], b[3]);
+      mma_f16(co[i], al[ks][0], al[ks][1], al[ks][2], al[ks][3], b[0], b[1]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[i][c] = fmaf(co[i][c], kLoUnscale, hi[i][c]);
+}
+
+__device__ __forceinline__ float2 load_pair(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+__device__ __forceinline__ float2 load_pair(const __half* p) {
+  return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+template <int D, int DT, bool QJL>
+__global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel(CompressArgs p) {
+  using T = typename Elem<DT>::type;
+  using S = CompressSmem<D, QJL>;
+  constexpr int LD = S::kLd;
+  constexpr int KS = D / 16;  // k-steps of a product
+  constexpr int NG = D / 32;  // groups of four column tiles
+  static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* m_hi[3];
+  __half* m_lo[3];
+#pragma unroll
+  for (int m = 0; m < 3; ++m) {
+    m_hi[m] = reinterpret_cast<__half*>(smem_raw + S::kPlane * 2 * (m < S::kMats ? m : 0));
+    m_lo[m] = m_hi[m] + D * LD;
+  }
+  float* s_bnd = reinterpret_cast<float*>(smem_raw + S::kOffMeta);  // [2][16]
+  float* s_cent = s_bnd + 32;                                       // [16]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- resident matrices -----------------------------------------------------------------
+  // [0]: Pi as it is  (y = x_hat Pi^T:      B[k][n] = Pi[n][k])
+  // [1]: Pi transposed (x_tilde = y_tilde Pi: B[k][n] = Pi[k][n])
+  // [2]: S as it is   (r S^T:               B[k][n] = S[n][k])
+  if (p.rot_split) {
+    stage_matrix<D>(m_hi[0], m_lo[0], LD, false, [&](int n, int k) {
+      return ((n & 1) ? p.mat_b : p.mat_a)[k * (D / 2) + (n >> 1)];
+    }, tid);
+  } else {
+    stage_matrix<D>(m_hi[0], m_lo[0], LD, true, [&](int n, int k) { return p.mat_a[n * D + k]; }, tid);
+  }
+  if constexpr (QJL) {
+    stage_matrix<D>(m_hi[1], m_lo[1], LD, false, [&](int n, int k) { return p.mat_a[k * D + n]; }, tid);
+    stage_matrix<D>(m_hi[2], m_lo[2], LD, true, [&](int n, int k) { return p.qjl[n * D + k]; }, tid);
+  }
+  if (tid < 32) {
+    const int s = tid >> 4, i = tid & 15;
+    const int src = (s < p.n_src) ? s : 0;
+    s_bnd[tid] = (i < p.nb[src]) ? p.bnd[src][i] : __int_as_float(0x7f800000);
+  }
+  if (tid < 16) s_cent[tid] = (QJL && tid <= p.nb[0]) ? p.cent0[tid] : 0.f;
+  __syncthreads();
+
+  // ldmatrix: lanes 8j..8j+7 give the rows of matrix j = plane j>>1 (hi, lo'), k-segment j&1
+  const int lj = lane >> 3, lr = lane & 7;
+  const __half* pb[3];
+#pragma unroll
+  for (int m = 0; m < 3; ++m) pb[m] = ((lj >> 1) ? m_lo[m] : m_hi[m]) + lr * LD + 8 * (lj & 1);
+
+  // (the host side keeps n_vec below 2^31: 32-bit index arithmetic, no 64-bit divisions)
+  const uint32_t n_vec = uint32_t(p.n_tokens * p.heads);
+  const uint32_t n_tiles = (n_vec + kTileRows - 1) / kTileRows;
+  const uint32_t heads = uint32_t(p.heads);
+  const uint32_t warps_total = gridDim.x * kCompressWarps;
+
+  // A warp owns a tile of 16 vectors end to end, K of the tile then V: no barrier in the loop.
+  for (uint32_t tile = blockIdx.x * kCompressWarps + warp; tile < n_tiles; tile += warps_total) {
+    // rows g and g+8 of the tile
+    const uint32_t v0 = tile * kTileRows + g, v1 = v0 + 8;
+    const bool ok0 = v0 < n_vec, ok1 = v1 < n_vec;
+    const uint32_t tok0 = ok0 ? v0 / heads : 0u, tok1 = ok1 ? v1 / heads : 0u;
+    const int head0 = int(v0 - tok0 * heads), head1 = int(v1 - tok1 * heads);
+    int64_t slot0 = ok0 ? int64_t(tok0) : -1, slot1 = ok1 ? int64_t(tok1) : -1;
+    if (p.slots) {
+      if (ok0)
+        slot0 = p.slot64 ? reinterpret_cast<const int64_t*>(p.slots)[tok0]
+                         : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok0]);
+      if (ok1)
+        slot1 = p.slot64 ? reinterpret_cast<const int64_t*>(p.slots)[tok1]
+                         : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok1]);
+      if (slot0 >= p.num_slots) slot0 = -1;
+      if (slot1 >= p.num_slots) slot1 = -1;
+    }
+
+    for (int s = 0; s < p.n_src; ++s) {
+      const T* src = reinterpret_cast<const T*>(p.src[s]);
+      const float* sb = s_bnd + 16 * s;
+      // the lane's share of the two rows: columns 16*ks + 2t, +1 and 16*ks + 8 + 2t, +1
+      const T* x0 = src + int64_t(tok0) * p.token_stride + int64_t(head0) * D + 2 * t;
+      const T* x1 = src + int64_t(tok1) * p.token_stride + int64_t(head1) * D + 2 * t;
+
+      // ---- norms: sum of squares over the lane's share, then over the four lanes of a row ----
+      float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        if (ok0) {
+          const float2 a = load_pair(x0 + 16 * ks), b = load_pair(x0 + 16 * ks + 8);
+          ss0 = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss0))));
+        }
+        if (ok1) {
+          const float2 a = load_pair(x1 + 16 * ks), b = load_pair(x1 + 16 * ks + 8);
+          ss1 = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss1))));
+        }
+      }
+      ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1);
+      ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1);
+      ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+      ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+      const float nrm0 = sqrtf(ss0), nrm1 = sqrtf(ss1);
+      // one reciprocal per vector instead of a division per coordinate: x_hat may differ from
+      // x / (n + 1e-10) in the last bit, far inside the rounding of the contraction
+      const float inv0 = 1.f / (nrm0 + 1e-10f), inv1 = 1.f / (nrm1 + 1e-10f);
+      if (t == 0 && slot0 >= 0)
+        *reinterpret_cast<float*>(p.norm[s] + slot0 * p.norm_row_stride + head0 * 4) = nrm0;
+      if (t == 1 && slot1 >= 0)
+        *reinterpret_cast<float*>(p.norm[s] + slot1 * p.norm_row_stride + head1 * 4) = nrm1;
+
+      // ---- x_hat as hi / lo' fragments (the rows come from the L1 this time) ----------------
+      uint32_t xh[KS][4], xl[KS][4];
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        float2 f[4];
+        f[0] = ok0 ? load_pair(x0 + 16 * ks) : make_float2(0.f, 0.f);
+        f[1] = ok1 ? load_pair(x1 + 16 * ks) : make_float2(0.f, 0.f);
+        f[2] = ok0 ? load_pair(x0 + 16 * ks + 8) : make_float2(0.f, 0.f);
+        f[3] = ok1 ? load_pair(x1 + 16 * ks + 8) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float sc = (i & 1) ? inv1 : inv0;
+          __half h0, l0, h1, l1;
+          split_hi_lo(f[i].x * sc, h0, l0);
+          split_hi_lo(f[i].y * sc, h1, l1);
+          xh[ks][i] = pack_h2(h0, h1);
+          xl[ks][i] = pack_h2(l0, l1);
+        }
+      }
+
+      // ---- y = x_hat Pi^T, codes; for the two-stage quantiser the centroid vector becomes the
+      // left operand of the next product: C tiles 2ks, 2ks+1 are A k-step ks -----------------
+      [[maybe_unused]] uint32_t yh[KS][4], yl[KS][4];
+#pragma unroll
+      for (int grp = 0; grp < NG; ++grp) {
+        float acc[4][4];
+        reg_mma_group<D>(xh, xl, pb[0], LD, grp, acc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int nt = grp * 4 + i;
+          int idx[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) idx[c] = bucketize15(acc[i][c], sb);
+          // code byte = (even coordinate << 4) | odd coordinate; the four lanes of a row hold
+          // bytes 4*nt .. 4*nt+3 of it
+          uint32_t w_lo = uint32_t((idx[0] << 4) | idx[1]) << (8 * t);
+          uint32_t w_hi = uint32_t((idx[2] << 4) | idx[3]) << (8 * t);
+          w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 1);
+          w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 1);
+          w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 2);
+          w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 2);
+          if (t == 0 && slot0 >= 0)
+            *reinterpret_cast<uint32_t*>(p.code[s] + slot0 * p.code_row_stride +
+                                         int64_t(head0) * p.code_head_stride + 4 * nt) = w_lo;
+          if (t == 1 && slot1 >= 0)
+            *reinterpret_cast<uint32_t*>(p.code[s] + slot1 * p.code_row_stride +
+                                         int64_t(head1) * p.code_head_stride + 4 * nt) = w_hi;
+          if constexpr (QJL) {
+            if (s == 0) {
+              __half h[4], l[4];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) split_hi_lo(s_cent[idx[c]], h[c], l[c]);
+              yh[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(h[0], h[1]);  // a0 / a2: row g
+              yh[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(h[2], h[3]);  // a1 / a3: row g+8
+              yl[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(l[0], l[1]);
+              yl[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(l[2], l[3]);
+            }
+          }
+        }
+      }
+
+      if constexpr (QJL) {
+        if (s == 0) {
+          // ---- x_tilde = (c[code] Pi) n ; r = x - x_tilde ; gamma = |r| ; r becomes the left
+          // operand of the last product (the registers of x_hat are free now) ------------------
+          float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+          for (int grp = 0; grp < NG; ++grp) {
+            float acc[4][4];
+            reg_mma_group<D>(yh, yl, pb[1], LD, grp, acc);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int nt = grp * 4 + i;
+              const float2 a = ok0 ? load_pair(x0 + 8 * nt) : make_float2(0.f, 0.f);
+              const float2 b = ok1 ? load_pair(x1 + 8 * nt) : make_float2(0.f, 0.f);
+              const float r0 = a.x - acc[i][0] * nrm0, r1 = a.y - acc[i][1] * nrm0;
+              const float r2 = b.x - acc[i][2] * nrm1, r3 = b.y - acc[i][3] * nrm1;
+              rs0 = fmaf(r0, r0, fmaf(r1, r1, rs0));
+              rs1 = fmaf(r2, r2, fmaf(r3, r3, rs1));
+              __half h[4], l[4];
+              split_hi_lo(r0, h[0], l[0]);
+              split_hi_lo(r1, h[1], l[1]);
+              split_hi_lo(r2, h[2], l[2]);
+              split_hi_lo(r3, h[3], l[3]);
+              xh[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(h[0], h[1]);
+              xh[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(h[2], h[3]);
+              xl[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(l[0], l[1]);
+              xl[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(l[2], l[3]);
+            }
+          }
+          rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
+          rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
+          rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
+          rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
+          if (t == 0 && slot0 >= 0)
+            *reinterpret_cast<float*>(p.gam + slot0 * p.gam_row_stride + head0 * 4) = sqrtf(rs0);
+          if (t == 1 && slot1 >= 0)
+            *reinterpret_cast<float*>(p.gam + slot1 * p.gam_row_stride + head1 * 4) = sqrtf(rs1);
+          // ---- sign(r S^T): bit j%8 of byte j/8 is 1 for a projection >= 0 -------------------
+#pragma unroll
+          for (int grp = 0; grp < NG; ++grp) {
+            float acc[4][4];
+            reg_mma_group<D>(xh, xl, pb[2], LD, grp, acc);
+            uint32_t b_lo = 0, b_hi = 0;  // bytes 4*grp .. 4*grp+3 of the row's sign bytes
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              b_lo |= ((acc[i][0] >= 0.f ? 1u : 0u) | (acc[i][1] >= 0.f ? 2u : 0u)) << (8 * i + 2 * t);
+              b_hi |= ((acc[i][2] >= 0.f ? 1u : 0u) | (acc[i][3] >= 0.f ? 2u : 0u)) << (8 * i + 2 * t);
+            }
+            b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 1);
+            b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 1);
+            b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 2);
+            b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 2);
+            if (t == 0 && slot0 >= 0)
+              *reinterpret_cast<uint32_t*>(p.sign + slot0 * p.sign_row_stride + head0 * (D / 8) +
+                                           4 * grp) = b_lo;
+            if (t == 1 && slot1 >= 0)
+              *reinterpret_cast<uint32_t*>(p.sign + slot1 * p.sign_row_stride + head1 * (D / 8) +
+                                           4 * grp) = b_hi;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Small calls (a decode step appends one token per sequence: a few tiles in all): the whole
+// CTA works on one tile at a time.  16 warps; warp w loads and normalises vector w of the tile,
+// the first eight warps (head_dim 128) own two column tiles each of every product; the left
+// operand (x_hat, then the centroid vector, then the residual) is exchanged through shared
+// memory as hi / lo' planes, six block-wide barriers per K tile of the two-stage quantiser.
+// Latency of one tile is what counts here: the products of a tile are spread over the warps
+// instead of running one after the other in a single warp.
+// ------------------------------------------------------------------------------------
+constexpr int kCoopThreads = 512;
+constexpr int kCoopWarps = 16;
+
+template <int D, bool QJL>
+struct CoopSmem {
+  static constexpr int kLd = D + 8;                        // halves per row
+  static constexpr size_t kPlane = size_t(D) * kLd * 2;    // one matrix plane, bytes
+  static constexpr size_t kAPlane = size_t(kTileRows) * kLd * 2;
+  static constexpr int kMats = QJL ? 3 : 1;
+  static constexpr size_t kOffA = kPlane * 2 * kMats;      // hi and lo' plane per matrix
+  static constexpr size_t kOffX = kOffA + 2 * kAPlane;      // the tile's vectors as fp32
+  static constexpr size_t kOffMeta = kOffX + (QJL ? size_t(kTileRows) * (D + 8) * 4 : 0);
+  // meta: nrm[16] f32, gpart[16][16] f32, bnd[2][16] f32, cent[16] f32, slot[16] i64, head[16] i32
+  static constexpr size_t kBytes = kOffMeta + (16 + 256 + 32 + 16) * 4 + 16 * 8 + 16 * 4;
+};
 
 // acc[i][c] = sum_k A[row][k] * B[n][k] for the NTW column tiles nt0 .. nt0+NTW-1 (C-fragment
 // layout: c0,c1 = row g, columns 8*nt + 2t, +1; c2,c3 = row g+8), A and B as hi / lo' planes.
@@ -168,13 +463,13 @@ __device__ __forceinline__ void plane_mma(const __half* __restrict__ ah,
 }
 
 template <int D, int DT, bool QJL>
-__global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel(CompressArgs p) {
+__global__ void __launch_bounds__(kCoopThreads, QJL ? 1 : 2) compress_coop_kernel(CompressArgs p) {
   using T = typename Elem<DT>::type;
-  using S = CompressSmem<D, QJL>;
+  using S = CoopSmem<D, QJL>;
   constexpr int LD = S::kLd;
   constexpr int JT = D / 32;   // elements per lane when a warp walks one vector
   constexpr int NT = D / 8;    // column tiles of a product
-  constexpr int NTW = FQ_COMPRESS_NTW;  // ... of which a product warp takes this many
+  constexpr int NTW = 2;  // ... of which a product warp takes this many
   constexpr int MW = NT / NTW;          // product warps: warps 0 .. MW-1
   static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
 
@@ -206,15 +501,15 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
   // [1]: Pi transposed (x_tilde = y_tilde Pi: B[k][n] = Pi[k][n])
   // [2]: S as it is   (r S^T:               B[k][n] = S[n][k])
   if (p.rot_split) {
-    stage_matrix<D>(m_hi[0], m_lo[0], LD, false, [&](int n, int k) {
+    stage_matrix<D, kCoopThreads>(m_hi[0], m_lo[0], LD, false, [&](int n, int k) {
       return ((n & 1) ? p.mat_b : p.mat_a)[k * (D / 2) + (n >> 1)];
     }, tid);
   } else {
-    stage_matrix<D>(m_hi[0], m_lo[0], LD, true, [&](int n, int k) { return p.mat_a[n * D + k]; }, tid);
+    stage_matrix<D, kCoopThreads>(m_hi[0], m_lo[0], LD, true, [&](int n, int k) { return p.mat_a[n * D + k]; }, tid);
   }
   if constexpr (QJL) {
-    stage_matrix<D>(m_hi[1], m_lo[1], LD, false, [&](int n, int k) { return p.mat_a[k * D + n]; }, tid);
-    stage_matrix<D>(m_hi[2], m_lo[2], LD, true, [&](int n, int k) { return p.qjl[n * D + k]; }, tid);
+    stage_matrix<D, kCoopThreads>(m_hi[1], m_lo[1], LD, false, [&](int n, int k) { return p.mat_a[k * D + n]; }, tid);
+    stage_matrix<D, kCoopThreads>(m_hi[2], m_lo[2], LD, true, [&](int n, int k) { return p.qjl[n * D + k]; }, tid);
   }
   if (tid < 32) {
     const int s = tid >> 4, i = tid & 15;
@@ -432,6 +727,34 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
   }
 }
 
+// below this many tiles the CTA-per-tile kernel is the faster one (measured cross-over at
+// about 1000 tiles: it starts in 12 us and needs 6.6 us per wave of tiles, the warp-per-tile
+// kernel 30 us and 33 us per eight tiles and SM)
+constexpr int64_t kCoopMaxTiles = 1024;
+
+template <int D, int DT, bool QJL>
+static int launch_compress_coop(const CompressArgs& a, int64_t tiles, cudaStream_t stream) {
+  using S = CoopSmem<D, QJL>;
+  auto kern = compress_coop_kernel<D, DT, QJL>;
+  static thread_local int configured_device = -1;
+  static thread_local int sm_count = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(FQ_ERR_CUDA, "cudaGetDevice failed");
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(S::kBytes));
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "compress: shared memory opt-in of %zu bytes refused: %s",
+                  S::kBytes, cudaGetErrorString(e));
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    configured_device = dev;
+  }
+  const int per_sm = (S::kBytes <= 110 * 1024) ? 2 : 1;
+  const int grid = int(tiles < int64_t(sm_count) * per_sm ? tiles : int64_t(sm_count) * per_sm);
+  kern<<<grid, kCoopThreads, S::kBytes, stream>>>(a);
+  return check_launch("compress kernel launch");
+}
+
 template <int D, int DT, bool QJL>
 static int launch_compress_t(const CompressArgs& a, cudaStream_t stream) {
   using S = CompressSmem<D, QJL>;
@@ -452,10 +775,12 @@ static int launch_compress_t(const CompressArgs& a, cudaStream_t stream) {
   const int64_t n_vec = a.n_tokens * a.heads;
   const int64_t tiles = (n_vec + kTileRows - 1) / kTileRows;
   if (tiles == 0) return FQ_OK;
+  if (tiles < kCoopMaxTiles) return launch_compress_coop<D, DT, QJL>(a, tiles, stream);
   FQ_REQUIRE(n_vec < (int64_t(1) << 31) - 16 * 4096, FQ_ERR_UNSUPPORTED,
              "compress: %lld vectors in one call (at most 2^31)", (long long)n_vec);
-  const int per_sm = (S::kBytes <= 110 * 1024) ? 2 : 1;
-  const int grid = int(tiles < int64_t(sm_count) * per_sm ? tiles : int64_t(sm_count) * per_sm);
+  const int per_sm = QJL ? 1 : 2;
+  const int64_t ctas = (tiles + kCompressWarps - 1) / kCompressWarps;  // a warp per tile
+  const int grid = int(ctas < int64_t(sm_count) * per_sm ? ctas : int64_t(sm_count) * per_sm);
   kern<<<grid, kCompressThreads, S::kBytes, stream>>>(a);
   return check_launch("compress kernel launch");
 }
