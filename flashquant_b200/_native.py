@@ -59,6 +59,7 @@ SIGNATURES = {
     "fq_fused_tq_attention": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i,
                                    _i, _f, _i, _p, _p, _sz, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
+    "fq_paged_decode_set_single_launch": (None, [_i]),
     "fq_split_k_paged_decode_qjl": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _p, _i,
                                          _i, _i, _i, _i, _i64, _f, _p, _i, _p, _sz, _p]),
     "fq_decode_step_host_staging_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),

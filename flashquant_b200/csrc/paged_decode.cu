@@ -31,6 +31,7 @@
 // Pages reach shared memory by 1-D bulk copies into per-team rings of stages guarded by
 // full/empty mbarriers; every wait is bounded and reports through the status word instead
 // of spinning forever.
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -1334,6 +1335,11 @@ static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits,
 // only add partial rows, so one split per sequence is the automatic choice.
 static int auto_splits() { return 1; }
 
+constexpr int kCoopRefused = 1001;  // internal: the single-launch form could not be launched
+
+// 1: fq_split_k_paged_decode uses the single cooperative launch (default); 0: three launches
+static std::atomic<int> g_single_launch{1};
+
 struct SmemPlan {
   int stages;  // per team
   uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent, total;
@@ -1401,8 +1407,16 @@ static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStre
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorLaunchOutOfResources) {
+      // the GPU cannot hold one CTA per SM of this launch right now (shared with other work,
+      // partitioned): the caller falls back to the three-launch form
+      cudaGetLastError();
+      fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs refused: %s", ctas,
+           cudaGetErrorString(e));
+      return kCoopRefused;
+    }
     if (e != cudaSuccess)
-      return fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs refused: %s", ctas,
+      return fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs failed: %s", ctas,
                   cudaGetErrorString(e));
   }
   return check_launch("paged decode kernel launch");
@@ -1628,10 +1642,28 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
   if (num_seqs == 0) return FQ_OK;
   const int ctas = device_sm_count();
   if (num_splits == 0) num_splits = auto_splits();
-  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+  if (g_single_launch.load(std::memory_order_relaxed)) {
+    rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
                       n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                       num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
                       workspace, workspace_bytes, ctas, stream, out);
+    if (rc != kCoopRefused) return rc;
+  }
+  // three launches: q rotation, streaming, merge (no CTA waits for another one)
+  rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                    num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
+                    workspace, workspace_bytes, ctas, stream);
+  if (rc != FQ_OK) return rc;
+  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                num_splits, ctas, seq_lens, block_size);
+  m.rotation = rotation;
+  m.out = out;
+  return launch_merge<true, true>(m, head_dim, dtype, stream);
+}
+
+extern "C" void fq_paged_decode_set_single_launch(int enabled) {
+  g_single_launch.store(enabled ? 1 : 0, std::memory_order_relaxed);
 }
 
 extern "C" int fq_split_k_paged_decode_qjl(

@@ -227,6 +227,13 @@ def decode_workspace(device, num_seqs: int, num_q_heads: int, num_kv_heads: int,
     return ws
 
 
+def set_single_launch(enabled: bool) -> None:
+    """``split_k_paged_decode`` as one cooperative launch (default) or as three ordinary launches
+    (for a GPU shared with other work; the call also falls back by itself when the cooperative
+    launch is refused)."""
+    N.load().fq_paged_decode_set_single_launch(1 if enabled else 0)
+
+
 def workspace_status(ws: torch.Tensor) -> int:
     """Device status word of a decode workspace (0 = no error); synchronises the stream."""
     st = C.c_uint32(0)

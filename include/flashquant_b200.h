@@ -174,6 +174,15 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
                             void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
 /*
+ * fq_split_k_paged_decode normally is one cooperative launch with one CTA per SM.  On a GPU
+ * that cannot hold such a launch (shared with other contexts, partitioned) the call falls
+ * back by itself to three ordinary launches (q rotation, streaming, merge) with the same
+ * result; fq_paged_decode_set_single_launch(0) selects that form for the whole process,
+ * (1) restores the default.  (No counterpart in the reference.)
+ */
+void fq_paged_decode_set_single_launch(int enabled);
+
+/*
  * fq_split_k_paged_decode with the two-stage estimator in the logits:
  *   logit = sm_scale * ( |k| <q_rot, c[code]> + gamma * sqrt(pi/2)/m * <S q, signs> )
  * i.e. TurboQuantProd.estimate_inner_product (src/flashquant/core/quantizer.py:349-370,

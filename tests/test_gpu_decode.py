@@ -313,3 +313,25 @@ def test_two_stage_scoring_vs_oracle(consts, dtype):
     assert (plain.float() - out.float()).abs().max().item() > 1e-2
     ws = K.decode_workspace(torch.device(DEV), w.num_seqs, hq, hkv, d, 0)
     assert K.workspace_status(ws) == 0
+
+
+def test_three_launch_form_gives_the_same_answer(consts):
+    """The fallback for GPUs that cannot hold the cooperative launch: rotation, streaming and
+    merge as separate launches, same contract."""
+    w = W.decode_workload(num_q_heads=32, num_kv_heads=8, head_dim=128, block_size=16, cfg=1,
+                          seq_lens=[300, 0, 17, 2048, 64])
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    one = run_gpu(w, cache, consts, num_splits=3)
+    K.set_single_launch(False)
+    try:
+        n0 = K.N.load().fq_launch_count()
+        three = run_gpu(w, cache, consts, num_splits=3)
+        assert K.N.load().fq_launch_count() - n0 == 3
+    finally:
+        K.set_single_launch(True)
+    attention_close(three, ref)
+    attention_close(one, ref)
+    assert (three[1] == 0).all()
+    # both forms round the same rotated query and merge the same partial rows
+    assert (one.float() - three.float()).abs().max().item() <= 2.0 ** -6
