@@ -282,3 +282,37 @@ def test_native_errors(C):
         fq.tq4_compress_append(torch.randn(4, 2, 128, device=DEV), torch.randn(4, 2, 128, device=DEV),
                                torch.zeros(1, 16, 100, dtype=torch.uint8, device=DEV),
                                torch.zeros(4, dtype=torch.int64, device=DEV), rot, b4)
+
+
+@pytest.mark.parametrize("dim,bits,dtype", [(64, 4, torch.float32), (64, 3, torch.bfloat16),
+                                            (128, 4, torch.float16), (128, 3, torch.float32)])
+def test_compress_bulk_sizes_use_the_warp_per_tile_kernel(C, dim, bits, dtype):
+    """More than 1024 tiles of 16 vectors: the bulk kernel, for both head sizes and all input
+    types (the smaller cases above stay on the CTA-per-tile kernel)."""
+    rot = C.get(f"rotation_{dim}_0")
+    bnd = C[f"boundaries_{dim}_{bits}"] if f"boundaries_{dim}_{bits}" in C else \
+        O.lloyd_max_codebook(dim, bits)[1]
+    g = torch.Generator().manual_seed(200 + dim + bits)
+    x = torch.randn(5001, 4, dim, generator=g)  # 20004 vectors: 1251 tiles, the last one ragged
+    x[..., W.outlier_channels(dim)] *= 10
+    x = x.to(dtype)
+    p, n = fq.tq4_compress(x.to(DEV), rot, bnd)
+    pr, nr = O.compress(x, rot, bnd)
+    check_codes(p, x.float(), rot, bnd, pr)
+    check_norms(n, nr)
+
+
+def test_prod_quantize_bulk_head_dim_64(C):
+    """Two-stage quantiser, head_dim 64, bulk kernel: codes, norms, gamma and signs."""
+    d = 64
+    q = fq.TurboQuantProd(d, 4, seed=0)
+    rot, S = q.mse_quantizer.rotation, q.qjl_matrix
+    b3, c3 = q.mse_quantizer.boundaries, q.mse_quantizer.centroids
+    k = torch.randn(4200, 4, d, generator=torch.Generator().manual_seed(5)).bfloat16()
+    idx, norms, signs, gamma = O.prod_quantize(k, rot, c3, b3, S)
+    packed, n2, bits, g2 = fq.tq_prod_quantize(k.to(DEV), rot, b3, c3, S)
+    check_codes(packed, k.float(), rot, b3, O.nibble_pack(idx))
+    check_norms(n2, norms)
+    check_norms(g2, gamma, rtol=2e-6)
+    bad = O.sign_bits_unpack(bits.cpu()) != signs
+    assert bad.float().mean().item() <= 1e-4
