@@ -294,6 +294,9 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
       // ---- y = x_hat Pi^T, codes; for the two-stage quantiser the centroid vector becomes the
       // left operand of the next product: C tiles 2ks, 2ks+1 are A k-step ks -----------------
       [[maybe_unused]] uint32_t yh[KS][4], yl[KS][4];
+      // code bytes: after the shuffles all four lanes of a row hold the 16 bytes of a group;
+      // lane t keeps those of group t, so that the row leaves in one 64-byte store instruction
+      uint32_t keep0[4] = {0u, 0u, 0u, 0u}, keep1[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
       for (int grp = 0; grp < NG; ++grp) {
         float acc[4][4];
@@ -312,12 +315,10 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
           w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 1);
           w_lo |= __shfl_xor_sync(0xffffffffu, w_lo, 2);
           w_hi |= __shfl_xor_sync(0xffffffffu, w_hi, 2);
-          if (t == 0 && slot0 >= 0)
-            *reinterpret_cast<uint32_t*>(p.code[s] + slot0 * p.code_row_stride +
-                                         int64_t(head0) * p.code_head_stride + 4 * nt) = w_lo;
-          if (t == 1 && slot1 >= 0)
-            *reinterpret_cast<uint32_t*>(p.code[s] + slot1 * p.code_row_stride +
-                                         int64_t(head1) * p.code_head_stride + 4 * nt) = w_hi;
+          if (t == grp) {
+            keep0[i] = w_lo;
+            keep1[i] = w_hi;
+          }
           if constexpr (QJL) {
             if (s == 0) {
               __half h[4], l[4];
@@ -328,6 +329,27 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
               yl[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(l[0], l[1]);
               yl[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(l[2], l[3]);
             }
+          }
+        }
+      }
+
+      if (t < NG) {  // 16 bytes of each row per lane: whole sectors when the row is aligned
+        uint8_t* d0 = p.code[s] + slot0 * p.code_row_stride + int64_t(head0) * p.code_head_stride + 16 * t;
+        uint8_t* d1 = p.code[s] + slot1 * p.code_row_stride + int64_t(head1) * p.code_head_stride + 16 * t;
+        if (slot0 >= 0) {
+          if ((reinterpret_cast<uintptr_t>(d0) & 15) == 0) {
+            *reinterpret_cast<uint4*>(d0) = make_uint4(keep0[0], keep0[1], keep0[2], keep0[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(d0)[i] = keep0[i];
+          }
+        }
+        if (slot1 >= 0) {
+          if ((reinterpret_cast<uintptr_t>(d1) & 15) == 0) {
+            *reinterpret_cast<uint4*>(d1) = make_uint4(keep1[0], keep1[1], keep1[2], keep1[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(d1)[i] = keep1[i];
           }
         }
       }
@@ -370,6 +392,7 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
           if (t == 1 && slot1 >= 0)
             *reinterpret_cast<float*>(p.gam + slot1 * p.gam_row_stride + head1 * 4) = sqrtf(rs1);
           // ---- sign(r S^T): bit j%8 of byte j/8 is 1 for a projection >= 0 -------------------
+          uint32_t sb0 = 0, sb1 = 0;  // lane t keeps bytes 4t .. 4t+3 of the rows' sign bytes
 #pragma unroll
           for (int grp = 0; grp < NG; ++grp) {
             float acc[4][4];
@@ -384,12 +407,18 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
             b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 1);
             b_lo |= __shfl_xor_sync(0xffffffffu, b_lo, 2);
             b_hi |= __shfl_xor_sync(0xffffffffu, b_hi, 2);
-            if (t == 0 && slot0 >= 0)
+            if (t == grp) {
+              sb0 = b_lo;
+              sb1 = b_hi;
+            }
+          }
+          if (t < NG) {
+            if (slot0 >= 0)
               *reinterpret_cast<uint32_t*>(p.sign + slot0 * p.sign_row_stride + head0 * (D / 8) +
-                                           4 * grp) = b_lo;
-            if (t == 1 && slot1 >= 0)
+                                           4 * t) = sb0;
+            if (slot1 >= 0)
               *reinterpret_cast<uint32_t*>(p.sign + slot1 * p.sign_row_stride + head1 * (D / 8) +
-                                           4 * grp) = b_hi;
+                                           4 * t) = sb1;
           }
         }
       }
