@@ -491,9 +491,10 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
 // time, one chunk ahead.  Warps of a team never synchronise with each other except through
 // the stage barriers, and every warp writes its own partial rows.
 // ------------------------------------------------------------------------------------
-#ifndef FQ_KMIX
-#define FQ_KMIX 1
-#endif
+// With at most 8 key centroids every second word of key codes goes through the shared-memory
+// table and the others through byte permutes on a register table: the permutes issue at half
+// rate on the ALU pipe, the look-ups load the shared-memory pipe; the mix balances the two.
+constexpr bool kMixKeyLookups = true;
 constexpr uint32_t kLutStride = 256;  // bytes per table entry: K copy per lane, then V copy
 constexpr int kDescRing = 64;
 
@@ -929,7 +930,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       for (int w = 0; w < KW; ++w) {
         // word w of the lane's chunk = cache bytes 4w..4w+3 = k-steps 2w (bytes 0,1), 2w+1
         uint32_t a[2][4];
-        if (KPRMT && !(FQ_KMIX && (w & 1))) {
+        if (KPRMT && !(kMixKeyLookups && (w & 1))) {
 #pragma unroll
           for (int hw = 0; hw < 2; ++hw) {
             const uint32_t sa = hw ? (ka[w] >> 16) : ka[w], sb = hw ? (kb[w] >> 16) : kb[w];

@@ -69,7 +69,7 @@ def test_golden_fixture(consts):
     assert K.workspace_status(ws) == 0
 
 
-@pytest.mark.parametrize("hkv,hq", [(8, 32), (1, 8), (2, 2), (4, 8), (8, 64)])
+@pytest.mark.parametrize("hkv,hq", [(8, 32), (1, 8), (2, 2), (4, 8), (8, 64), (16, 32)])
 def test_ragged_lengths_vs_oracle(consts, hkv, hq):
     lens = [0, 1, 15, 16, 17, 31, 33, 100, 257, 700]
     w = W.decode_workload(seq_lens=lens, num_q_heads=hq, num_kv_heads=hkv, cfg=11, spare_blocks=5)
