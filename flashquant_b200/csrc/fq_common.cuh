@@ -208,7 +208,12 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }
 
-// Counters in global memory that CTAs of one launch signal each other through.
+// Counters in global memory that CTAs of one launch signal each other through.  The add is a
+// release: everything the warp wrote before its __syncwarp() is visible to whoever acquires
+// the new count, and the warp does not wait for that (no fence, no returned value).
+__device__ __forceinline__ void red_release_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -608,6 +608,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
   __syncthreads();
 
+  // ---- phase a: one rotated query tile per warp of the grid (before the warps change their
+  // register budgets: the tile needs few registers and the counters should go out early) ----
+  if constexpr (FUSE != 0) {
+    if (warp < kCW)
+    for (int job = rot_job0; job < rot_jobs; job += gridDim.x * kCW) {
+      const bool by_pi = job < rot_half;
+      const int j0 = by_pi ? job : job - rot_half;
+      const int seq = j0 / q_tiles, r = j0 - seq * q_tiles;
+      if (job != rot_job0) {
+        rot_len = p.seq_lens[seq];
+        rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src),
+                                  by_pi ? p.rotation : p.qjl, p.hq, seq, r % m_tiles, r / m_tiles,
+                                  lane);
+      }
+      if (rot_len <= 0) continue;  // nobody reads the query of an empty sequence
+      // q Pi^T is rounded to the query's type as the reference does; q S^T is not
+      if (by_pi)
+        rotate_q_tile_finish<D, TQ>(rot_op, p.q_rot_w, p.hq, seq, r % m_tiles, r / m_tiles, lane);
+      else
+        rotate_q_tile_finish<D, TQ, false>(rot_op, p.qs_w, p.hq, seq, r % m_tiles, r / m_tiles,
+                                           lane);
+      __syncwarp();
+      if (lane == 0) red_release_add(p.q_count + seq, 1u);
+    }
+  }
+
   // ---- the flat page list and its cut into runs ---------------------------------------------
   const int64_t total = prefix[p.num_seqs];
   const int64_t workers = int64_t(gridDim.x) * teams;
@@ -767,31 +793,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   // ---- compute warps: this team's run ---------------------------------------------------------
   const int64_t wk = int64_t(blockIdx.x) * teams + team;
   const int n_run = wk < active ? int(total * (wk + 1) / active - total * wk / active) : 0;
-
-  // ---- phase a: one rotated query tile per warp of the grid --------------------------------
-  if constexpr (FUSE != 0) {
-    for (int job = rot_job0; job < rot_jobs; job += gridDim.x * kCW) {
-      const bool by_pi = job < rot_half;
-      const int j0 = by_pi ? job : job - rot_half;
-      const int seq = j0 / q_tiles, r = j0 - seq * q_tiles;
-      if (job != rot_job0) {
-        rot_len = p.seq_lens[seq];
-        rotate_q_tile_load<D, TQ>(rot_op, static_cast<const TQ*>(p.q_src),
-                                  by_pi ? p.rotation : p.qjl, p.hq, seq, r % m_tiles, r / m_tiles,
-                                  lane);
-      }
-      if (rot_len <= 0) continue;  // nobody reads the query of an empty sequence
-      // q Pi^T is rounded to the query's type as the reference does; q S^T is not
-      if (by_pi)
-        rotate_q_tile_finish<D, TQ>(rot_op, p.q_rot_w, p.hq, seq, r % m_tiles, r / m_tiles, lane);
-      else
-        rotate_q_tile_finish<D, TQ, false>(rot_op, p.qs_w, p.hq, seq, r % m_tiles, r / m_tiles,
-                                           lane);
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) atomicAdd(p.q_count + seq, 1u);
-    }
-  }
 
   // ---- look-up table -------------------------------------------------------------------------
   for (int i = tid; i < 256 * 32; i += kComputeThreads) {
@@ -1113,9 +1114,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         if (g == 0) *reinterpret_cast<float4*>(row + D) = make_float4(m_run[c], l_run[c], 0.f, 0.f);
       }
       if constexpr (FUSE != 0) {
-        __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(p.seg_count + d.z, 1u);
+        if (lane == 0) red_release_add(p.seg_count + d.z, 1u);
       }
     }
 
