@@ -368,7 +368,8 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
             break;
           }
         }
-        __threadfence();
+        // the acquire above orders the rows' stores (released with the count) before the
+        // loads below, which go to the L2 (ld.global.cg) after the barrier
       }
     }
     compute_sync();
