@@ -279,6 +279,18 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
         assert torch.equal(plane, ref_plane)
     assert torch.equal(hout.view(torch.int16), ref.cpu().view(torch.int16))
     assert K.workspace_status(step.workspace) == 0
+    # A serving loop reuses its arrays: new contents in the same arrays must be seen.
+    hq_buf = host(w.q)
+    hk, hv, hs, hb, hl = host(new_k), host(new_v), host(new_slots), host(bt), host(lens)
+    for it in range(4):
+        q_it = (w.q.float() * (1.0 + 0.25 * it)).to(w.q.dtype)
+        hq_buf.copy_(q_it)
+        step(hq_buf, hk, hv, hs, hb, hl, hout)
+        ref_it = K.split_k_paged_decode(q_it.to(DEV), ref_cache, bt.to(DEV), lens.to(DEV), ck, cv,
+                                        rot, hkv, d, bs, num_splits=2)
+        assert torch.equal(hout.view(torch.int16), ref_it.cpu().view(torch.int16)), f"call {it}"
+    assert K.workspace_status(step.workspace) == 0
+    hout.copy_(ref.cpu())
     # and against the oracle end to end
     attention_close(hout, O.split_k_paged_decode(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot, hkv,
                                                  d, bs, None))
