@@ -7,6 +7,7 @@ raises if ``libflashquant_b200.so`` has not been built (``python -m flashquant_b
 from .kernels import (  # noqa: F401
     HostDecodeStep,
     fused_tq_attention,
+    fused_tq_attention_kv,
     paged_decode_partials,
     split_k_merge,
     split_k_paged_decode,
@@ -14,8 +15,16 @@ from .kernels import (  # noqa: F401
     tq4_compress,
     tq4_compress_append,
     tq4_compress_append_qjl,
+    tq4_compress_into,
     tq4_decompress,
+    tq4_decompress_original,
     tq_prod_quantize,
+)
+from .cache import (  # noqa: F401
+    CompressedBuffer,
+    CompressedDynamicCache,
+    FlashQuantCacheError,
+    ValueCompressor,
 )
 from .quantizer import TurboQuantMSE, TurboQuantProd, haar_orthogonal, lloyd_max_codebook  # noqa: F401
 

@@ -59,6 +59,11 @@ SIGNATURES = {
     "fq_fused_tq_attention": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i,
                                    _i, _f, _i, _p, _p, _sz, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
+    "fq_tq4_compress_into": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _i64, _i64, _i64, _i64, _i, _p]),
+    "fq_tq4_decompress_original_workspace_bytes": (_sz, [_i64, _i]),
+    "fq_tq4_decompress_original": (_i, [_p, _p, _p, _i, _p, _p, _i, _i64, _i, _p, _sz, _p]),
+    "fq_fused_tq_attention_kv": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i,
+                                      _i, _i, _i64, _i, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_set_single_launch": (None, [_i]),
     "fq_split_k_paged_decode_qjl": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _p, _i,
                                          _i, _i, _i, _i, _i64, _f, _p, _i, _p, _sz, _p]),

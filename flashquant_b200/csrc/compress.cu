@@ -49,7 +49,18 @@ struct CompressArgs {
   const void* slots;  // null: destination row = token index
   int slot64;
   int64_t num_slots;
+  // Without a slot list and with seg_len > 0 the tokens form runs of seg_len that land in
+  // segments of seg_stride rows: row = (token / seg_len) * seg_stride + seg_offset + token % seg_len
+  // (the per-head buffers of a contiguous cache, each with room for seg_stride tokens).
+  uint32_t seg_len;
+  int64_t seg_stride;
+  int64_t seg_offset;
 };
+
+__device__ __forceinline__ int64_t segment_row(const CompressArgs& p, uint32_t tok) {
+  const uint32_t seg = tok / p.seg_len;
+  return int64_t(seg) * p.seg_stride + p.seg_offset + int64_t(tok - seg * p.seg_len);
+}
 
 constexpr int kTileRows = 16;         // vectors per tile = rows of one MMA
 constexpr float kLoScale = 2048.f;    // lo' = (v - hi) * 2^11
@@ -236,6 +247,9 @@ __global__ void __launch_bounds__(kCompressThreads, QJL ? 1 : 2) compress_kernel
                          : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok1]);
       if (slot0 >= p.num_slots) slot0 = -1;
       if (slot1 >= p.num_slots) slot1 = -1;
+    } else if (p.seg_len) {
+      if (ok0) slot0 = segment_row(p, tok0);
+      if (ok1) slot1 = segment_row(p, tok1);
     }
 
     for (int s = 0; s < p.n_src; ++s) {
@@ -578,6 +592,8 @@ __global__ void __launch_bounds__(kCoopThreads, QJL ? 1 : 2) compress_coop_kerne
         slot = p.slot64 ? reinterpret_cast<const int64_t*>(p.slots)[tok]
                         : int64_t(reinterpret_cast<const int32_t*>(p.slots)[tok]);
         if (slot >= p.num_slots) slot = -1;
+      } else if (p.seg_len) {
+        slot = segment_row(p, tok32);
       }
       f.slot = slot;
     }
@@ -861,6 +877,36 @@ extern "C" int fq_tq4_compress(const void* x, fq_dtype dtype, const float* rot_T
   a.bnd[0] = a.bnd[1] = boundaries; a.nb[0] = a.nb[1] = n_boundaries;
   a.code[0] = packed; a.code_row_stride = head_dim / 2; a.code_head_stride = 0;
   a.norm[0] = reinterpret_cast<uint8_t*>(norms); a.norm_row_stride = 4;
+  return launch_compress(a, dtype, head_dim, false, stream);
+}
+
+extern "C" int fq_tq4_compress_into(const void* x, fq_dtype dtype, const float* rot_T_even,
+                                    const float* rot_T_odd, const float* boundaries,
+                                    int n_boundaries, uint8_t* packed, float* norms,
+                                    int64_t n_segments, int64_t n_new, int64_t capacity,
+                                    int64_t position, int head_dim, fq_stream_t stream) {
+  FQ_REQUIRE(n_segments >= 0 && n_new >= 0 && capacity >= 0 && position >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "fq_tq4_compress_into: negative size");
+  FQ_REQUIRE(position + n_new <= capacity, FQ_ERR_INVALID_ARGUMENT,
+             "fq_tq4_compress_into: %lld tokens at position %lld exceed the capacity %lld",
+             (long long)n_new, (long long)position, (long long)capacity);
+  if (n_segments == 0 || n_new == 0) return FQ_OK;
+  FQ_REQUIRE(x && rot_T_even && rot_T_odd && boundaries && packed && norms,
+             FQ_ERR_INVALID_ARGUMENT, "fq_tq4_compress_into: null pointer");
+  FQ_REQUIRE(n_boundaries >= 1 && n_boundaries <= 15, FQ_ERR_INVALID_ARGUMENT,
+             "n_boundaries %d outside [1, 15]", n_boundaries);
+  FQ_REQUIRE(n_new < (int64_t(1) << 31), FQ_ERR_UNSUPPORTED,
+             "fq_tq4_compress_into: %lld new tokens per segment", (long long)n_new);
+  FQ_REQUIRE(aligned(x, 4 * elem_bytes(dtype)) && aligned(packed, 4) && aligned(norms, 4),
+             FQ_ERR_ALIGNMENT, "fq_tq4_compress_into: x must be aligned to 4 elements");
+  CompressArgs a{};
+  a.src[0] = x; a.n_src = 1;
+  a.n_tokens = n_segments * n_new; a.heads = 1; a.token_stride = head_dim;
+  a.mat_a = rot_T_even; a.mat_b = rot_T_odd; a.rot_split = 1;
+  a.bnd[0] = a.bnd[1] = boundaries; a.nb[0] = a.nb[1] = n_boundaries;
+  a.code[0] = packed; a.code_row_stride = head_dim / 2; a.code_head_stride = 0;
+  a.norm[0] = reinterpret_cast<uint8_t*>(norms); a.norm_row_stride = 4;
+  a.seg_len = uint32_t(n_new); a.seg_stride = capacity; a.seg_offset = position;
   return launch_compress(a, dtype, head_dim, false, stream);
 }
 

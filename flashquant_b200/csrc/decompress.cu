@@ -86,3 +86,36 @@ extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
   }
   return check_launch("decompress kernel launch");
 }
+
+// Decompress to the ORIGINAL space: (c[code] * norm) Pi, rounded to out_dtype.  The codes are
+// expanded in fp32 into `workspace` (n_vectors x head_dim floats) and rotated back by the
+// split-fp16 tensor-core product (fp32-level accuracy), so the result differs from
+// centroids[idx] @ Pi * norm evaluated in fp32 only by fp32 rounding before the final cast.
+extern "C" size_t fq_tq4_decompress_original_workspace_bytes(int64_t n_vectors, int head_dim) {
+  if (n_vectors < 0 || head_dim < 0) return 0;
+  return size_t(n_vectors) * size_t(head_dim) * sizeof(float);
+}
+
+extern "C" int fq_tq4_decompress_original(const uint8_t* packed, const float* norms,
+                                          const float* centroids, int n_centroids,
+                                          const float* rotation, void* out, fq_dtype out_dtype,
+                                          int64_t n_vectors, int head_dim, void* workspace,
+                                          size_t workspace_bytes, fq_stream_t stream) {
+  FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
+  if (n_vectors == 0) return FQ_OK;
+  FQ_REQUIRE(rotation && out, FQ_ERR_INVALID_ARGUMENT, "fq_tq4_decompress_original: null pointer");
+  FQ_REQUIRE(head_dim == 64 || head_dim == 128, FQ_ERR_UNSUPPORTED,
+             "head_dim %d: the rotation kernels are built for 64 and 128", head_dim);
+  FQ_REQUIRE(out_dtype == FQ_F32 || out_dtype == FQ_F16 || out_dtype == FQ_BF16,
+             FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", int(out_dtype));
+  const size_t need = fq_tq4_decompress_original_workspace_bytes(n_vectors, head_dim);
+  FQ_REQUIRE(workspace && aligned(workspace, 16) && workspace_bytes >= need, FQ_ERR_WORKSPACE,
+             "fq_tq4_decompress_original: workspace of %zu bytes needed (16-byte aligned)", need);
+  FQ_REQUIRE(aligned(out, 16), FQ_ERR_ALIGNMENT,
+             "fq_tq4_decompress_original: out must be 16-byte aligned");
+  int rc = fq_tq4_decompress(packed, norms, centroids, n_centroids, workspace, FQ_F32, n_vectors,
+                             head_dim, stream);
+  if (rc != FQ_OK) return rc;
+  return rotate_back(static_cast<const float*>(workspace), int(out_dtype), rotation, out,
+                     n_vectors, head_dim, stream);
+}

@@ -148,6 +148,7 @@ struct PrefillArgs {
   int ncv;
   float* o_rot;  // (B, Hq, Nq, D) fp32, rotated space (the reference rounds only after Pi)
   int batch, hq, hkv, nq, nkv;
+  int64_t kv_stride;  // tokens between consecutive (batch, head) rows of the K/V buffers (>= nkv)
   float scale_log2;
   int causal;
   uint32_t* status;
@@ -218,10 +219,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   if (p.causal && m0 + rows < kv_end) kv_end = m0 + rows;
   const int n_tiles = (kv_end + kPfN - 1) / kPfN;
 
-  const uint8_t* kc_base = p.k_packed + (int64_t(b) * p.hkv + hkv) * p.nkv * (D / 2);
-  const uint8_t* vc_base = p.v_packed + (int64_t(b) * p.hkv + hkv) * p.nkv * (D / 2);
-  const float* kn_base = p.k_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
-  const float* vn_base = p.v_norms + (int64_t(b) * p.hkv + hkv) * p.nkv;
+  const uint8_t* kc_base = p.k_packed + (int64_t(b) * p.hkv + hkv) * p.kv_stride * (D / 2);
+  const uint8_t* vc_base = p.v_packed + (int64_t(b) * p.hkv + hkv) * p.kv_stride * (D / 2);
+  const float* kn_base = p.k_norms + (int64_t(b) * p.hkv + hkv) * p.kv_stride;
+  const float* vn_base = p.v_norms + (int64_t(b) * p.hkv + hkv) * p.kv_stride;
   // norms ride along with the codes when a bulk copy can take them (16-byte granularity)
   const bool norm_bulk = ((reinterpret_cast<uintptr_t>(kn_base) | reinterpret_cast<uintptr_t>(vn_base)) & 15) == 0;
 
@@ -585,20 +586,21 @@ extern "C" size_t fq_fused_tq_attention_workspace_bytes(int batch, int num_q_hea
   return prefill_workspace(int64_t(batch) * num_q_heads * n_q, head_dim).total;
 }
 
-extern "C" int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed,
-                                     const float* k_norms, const uint8_t* v_packed,
-                                     const float* v_norms, const float* centroids_k,
-                                     int n_centroids_k, const float* centroids_v,
-                                     int n_centroids_v, const float* rotation, int batch,
-                                     int num_q_heads, int num_kv_heads, int n_q, int n_kv,
-                                     int head_dim, float sm_scale, int is_causal, void* out,
-                                     void* workspace, size_t workspace_bytes,
-                                     fq_stream_t stream) {
+static int attention_common(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                            const float* k_norms, const uint8_t* v_packed, const float* v_norms,
+                            const float* centroids_k, int n_centroids_k,
+                            const float* centroids_v, int n_centroids_v, const float* rotation,
+                            const float* rotation_v, int batch, int num_q_heads,
+                            int num_kv_heads, int n_q, int n_kv, int64_t kv_stride, int head_dim,
+                            float sm_scale, int is_causal, void* out, void* workspace,
+                            size_t workspace_bytes, fq_stream_t stream) {
   FQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && num_kv_heads >= 1 && n_q >= 0 && n_kv >= 0,
              FQ_ERR_INVALID_ARGUMENT, "fused attention: negative size");
   FQ_REQUIRE(q && k_packed && k_norms && v_packed && v_norms && centroids_k && centroids_v &&
-                 rotation && out,
+                 rotation && rotation_v && out,
              FQ_ERR_INVALID_ARGUMENT, "fused attention: null pointer");
+  FQ_REQUIRE(kv_stride >= n_kv, FQ_ERR_INVALID_ARGUMENT,
+             "fused attention: %d tokens do not fit a buffer of %lld", n_kv, (long long)kv_stride);
   FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
              "fused attention: q must be fp16 or bf16");
   FQ_REQUIRE(head_dim == 128, FQ_ERR_UNSUPPORTED,
@@ -631,10 +633,42 @@ extern "C" int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_
   a.cent_v = centroids_v; a.ncv = n_centroids_v;
   a.o_rot = o_rot;
   a.batch = batch; a.hq = num_q_heads; a.hkv = num_kv_heads; a.nq = n_q; a.nkv = n_kv;
+  a.kv_stride = kv_stride;
   a.scale_log2 = sm_scale * 1.4426950408889634f;
   a.causal = (is_causal && n_q > 1) ? 1 : 0;  // a single query token never needs the mask
   a.status = reinterpret_cast<uint32_t*>(ws);
   rc = launch_prefill_t<128>(a, stream);
   if (rc != FQ_OK) return rc;
-  return rotate_back(o_rot, dtype, rotation, out, rows, head_dim, stream);
+  return rotate_back(o_rot, dtype, rotation_v, out, rows, head_dim, stream);
+}
+
+extern "C" int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                                     const float* k_norms, const uint8_t* v_packed,
+                                     const float* v_norms, const float* centroids_k,
+                                     int n_centroids_k, const float* centroids_v,
+                                     int n_centroids_v, const float* rotation, int batch,
+                                     int num_q_heads, int num_kv_heads, int n_q, int n_kv,
+                                     int head_dim, float sm_scale, int is_causal, void* out,
+                                     void* workspace, size_t workspace_bytes,
+                                     fq_stream_t stream) {
+  return attention_common(q, dtype, k_packed, k_norms, v_packed, v_norms, centroids_k,
+                          n_centroids_k, centroids_v, n_centroids_v, rotation, rotation, batch,
+                          num_q_heads, num_kv_heads, n_q, n_kv, n_kv, head_dim, sm_scale,
+                          is_causal, out, workspace, workspace_bytes, stream);
+}
+
+extern "C" int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                                        const float* k_norms, const uint8_t* v_packed,
+                                        const float* v_norms, const float* centroids_k,
+                                        int n_centroids_k, const float* centroids_v,
+                                        int n_centroids_v, const float* rotation_k,
+                                        const float* rotation_v, int batch, int num_q_heads,
+                                        int num_kv_heads, int n_q, int n_kv,
+                                        int64_t kv_capacity, int head_dim, float sm_scale,
+                                        int is_causal, void* out, void* workspace,
+                                        size_t workspace_bytes, fq_stream_t stream) {
+  return attention_common(q, dtype, k_packed, k_norms, v_packed, v_norms, centroids_k,
+                          n_centroids_k, centroids_v, n_centroids_v, rotation_k, rotation_v,
+                          batch, num_q_heads, num_kv_heads, n_q, n_kv, kv_capacity, head_dim,
+                          sm_scale, is_causal, out, workspace, workspace_bytes, stream);
 }

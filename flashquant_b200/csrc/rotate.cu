@@ -143,6 +143,10 @@ template <>
 __device__ __forceinline__ void rt_store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
+template <>
+__device__ __forceinline__ void rt_store2<float>(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
 
 template <typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 __global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
@@ -299,6 +303,10 @@ int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* ou
 // o_rot (fp32) -> round_dtype(o_rot Pi)
 int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out, int64_t n_rows,
                 int head_dim, cudaStream_t stream) {
+  if (dtype == FQ_F32)
+    return head_dim == 128
+               ? launch_rotate_tc<float, float, false, false>(o_rot, rotation, out, n_rows, stream)
+               : launch_rotate_t<64, float, float, false, false>(o_rot, rotation, out, n_rows, stream);
   if (head_dim == 128)
     return dtype == FQ_BF16
                ? launch_rotate_tc<float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)

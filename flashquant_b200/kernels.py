@@ -98,6 +98,77 @@ def tq4_decompress(
     return out
 
 
+def _split_rotation(rotation: torch.Tensor, dev):
+    rt = rotation.to(dev).T.contiguous()
+    return rt[:, 0::2].contiguous(), rt[:, 1::2].contiguous()
+
+
+def tq4_compress_into(
+    x: torch.Tensor,
+    rotation: torch.Tensor,
+    boundaries: torch.Tensor,
+    packed: torch.Tensor,
+    norms: torch.Tensor,
+    position: int,
+    *,
+    rotation_T_even: Optional[torch.Tensor] = None,
+    rotation_T_odd: Optional[torch.Tensor] = None,
+) -> None:
+    """Compress ``x (B, H, S, D)`` into rows ``position .. position+S-1`` of the pre-allocated
+    ``packed (B, H, capacity, D/2)`` uint8 and ``norms (B, H, capacity, 1)`` fp32 buffers.
+
+    One launch for what the reference does as compress + nibble_pack + two slice copies
+    (src/flashquant/cache/hf_cache.py:170-194, src/flashquant/cache/buffer_pool.py:86-110).
+    """
+    N.require_cuda(x, packed, norms)
+    b, h, s, d = x.shape
+    cap = packed.shape[2]
+    if packed.shape != (b, h, cap, d // 2) or norms.shape[:3] != (b, h, cap):
+        raise ValueError("buffers must be (B, H, capacity, D/2) and (B, H, capacity, 1)")
+    if not (packed.is_contiguous() and norms.is_contiguous()):
+        raise ValueError("the cache buffers must be contiguous")
+    if packed.dtype != torch.uint8 or norms.dtype != torch.float32:
+        raise ValueError("buffers must be uint8 codes and fp32 norms")
+    dev = x.device
+    if rotation_T_even is None or rotation_T_odd is None:
+        rotation_T_even, rotation_T_odd = _split_rotation(rotation, dev)
+    even, odd = _f32(rotation_T_even, dev), _f32(rotation_T_odd, dev)
+    bnd = _f32(boundaries, dev)
+    x = _contig(x)
+    lib = N.load()
+    N.check(lib.fq_tq4_compress_into(N.ptr(x), N.dtype_code(x.dtype), N.ptr(even), N.ptr(odd),
+                                     N.ptr(bnd), bnd.numel(), N.ptr(packed), N.ptr(norms), b * h,
+                                     s, cap, int(position), d, N.stream_ptr(dev)))
+
+
+def tq4_decompress_original(
+    packed: torch.Tensor,
+    norms: torch.Tensor,
+    centroids: torch.Tensor,
+    rotation: torch.Tensor,
+    dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """packed ``(..., D/2)`` + norms ``(..., 1)`` -> ``(..., D)`` in ``dtype``, ORIGINAL space.
+
+    ``round_dtype((c[code] * n) Pi)``: what the reference's cache returns from a read
+    (src/flashquant/cache/hf_cache.py:196-219).
+    """
+    N.require_cuda(packed, norms)
+    lead, half = packed.shape[:-1], packed.shape[-1]
+    dev = packed.device
+    n_vec = packed.numel() // half if half else 0
+    cent, rot = _f32(centroids, dev), _f32(rotation, dev)
+    packed, norms = _contig(packed), _contig(norms.float())
+    out = torch.empty(*lead, 2 * half, dtype=dtype, device=dev)
+    lib = N.load()
+    need = lib.fq_tq4_decompress_original_workspace_bytes(n_vec, 2 * half)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    N.check(lib.fq_tq4_decompress_original(N.ptr(packed), N.ptr(norms), N.ptr(cent), cent.numel(),
+                                           N.ptr(rot), N.ptr(out), N.dtype_code(dtype), n_vec,
+                                           2 * half, N.ptr(ws), ws.numel(), N.stream_ptr(dev)))
+    return out
+
+
 def tq_prod_quantize(x, rotation, boundaries, centroids, qjl_matrix):
     """Two-stage quantiser on ``(..., D)``: packed codes, norms, packed sign bits, gamma.
 
@@ -499,6 +570,73 @@ def fused_tq_attention(
         N.ptr(q), N.dtype_code(q.dtype), N.ptr(kp), N.ptr(kn), N.ptr(vp), N.ptr(vn), N.ptr(ck),
         ck.numel(), N.ptr(cv), cv.numel(), N.ptr(rot), b, hq, hkv, nq, nkv, d, float(sm_scale),
         int(bool(is_causal)), N.ptr(out), N.ptr(ws), ws.numel(), N.stream_ptr(dev)))
+    return out
+
+
+def _buffer_view_capacity(codes: torch.Tensor, norms: torch.Tensor) -> int:
+    """Tokens per (batch, head) row of the buffers that ``codes`` / ``norms`` are views of."""
+    b, h, n, half = codes.shape
+    if n == 0:
+        return 0
+    if codes.stride(3) != 1 or codes.stride(2) != half or codes.stride(1) % half:
+        raise ValueError("packed codes must be a [:, :, :n] view of a contiguous buffer")
+    cap = codes.stride(1) // half
+    if b > 1 and codes.stride(0) != h * codes.stride(1):
+        raise ValueError("packed codes must be a [:, :, :n] view of a contiguous buffer")
+    nn = norms.reshape(b, h, n) if norms.dim() == 4 else norms
+    if nn.stride(2) != 1 or nn.stride(1) != cap or (b > 1 and nn.stride(0) != h * cap):
+        raise ValueError("norms must be a view of a buffer with the capacity of the codes")
+    return cap
+
+
+def fused_tq_attention_kv(
+    q: torch.Tensor,
+    k_packed: torch.Tensor,
+    k_norms: torch.Tensor,
+    v_packed: torch.Tensor,
+    v_norms: torch.Tensor,
+    centroids_k: torch.Tensor,
+    centroids_v: torch.Tensor,
+    rotation_k: torch.Tensor,
+    rotation_v: torch.Tensor,
+    sm_scale: Optional[float] = None,
+    is_causal: bool = False,
+) -> torch.Tensor:
+    """``fused_tq_attention`` over the views a compressed cache hands out, read in place.
+
+    ``k_packed`` .. ``v_norms`` are what ``CompressedDynamicCache.get_compressed`` returns
+    (src/flashquant/cache/hf_cache.py:387-414): ``[:, :, :n_kv]`` views of buffers with room
+    for more tokens; keys and values carry their own rotation (seeds 42 / 43).
+    """
+    N.require_cuda(q, k_packed, k_norms, v_packed, v_norms)
+    b, hq, nq, d = q.shape
+    _, hkv, nkv, half = k_packed.shape
+    if half * 2 != d or v_packed.shape != k_packed.shape:
+        raise ValueError("packed K/V must be (B, H_KV, N_KV, D/2)")
+    if k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32:
+        raise ValueError("norms must be fp32")
+    cap = _buffer_view_capacity(k_packed, k_norms)
+    if _buffer_view_capacity(v_packed, v_norms) != cap:
+        raise ValueError("K and V buffers must have the same capacity")
+    dev = q.device
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    q = _contig(q)
+    ck, cv = _f32(centroids_k, dev), _f32(centroids_v, dev)
+    rk, rv = _f32(rotation_k, dev), _f32(rotation_v, dev)
+    out = torch.empty_like(q)
+    lib = N.load()
+    need = lib.fq_fused_tq_attention_workspace_bytes(b, hq, nq, d)
+    key = (dev.type, dev.index)
+    ws = _attn_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+        _attn_workspaces[key] = ws
+    N.check(lib.fq_fused_tq_attention_kv(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(k_packed), N.ptr(k_norms), N.ptr(v_packed),
+        N.ptr(v_norms), N.ptr(ck), ck.numel(), N.ptr(cv), cv.numel(), N.ptr(rk), N.ptr(rv), b, hq,
+        hkv, nq, nkv, cap, d, float(sm_scale), int(bool(is_causal)), N.ptr(out), N.ptr(ws),
+        ws.numel(), N.stream_ptr(dev)))
     return out
 
 

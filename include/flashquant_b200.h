@@ -65,6 +65,25 @@ int fq_tq4_compress(const void* x, fq_dtype dtype, const float* rot_T_even,
                     fq_stream_t stream);
 
 /*
+ * TQ4 compress straight into the pre-allocated per-head buffers of a contiguous cache.
+ * Replaces CompressedDynamicCache._compress_tensor (src/flashquant/cache/hf_cache.py:170-194:
+ * ValueCompressor.compress + nibble_pack) followed by CompressedBuffer.append
+ * (src/flashquant/cache/buffer_pool.py:86-110: two slice copies): the codes and norms of
+ * the new tokens are written at their final place, rows position .. position+n_new-1 of
+ * every segment, in one launch.
+ *   x         (n_segments, n_new, head_dim) values of `dtype`, contiguous; a segment is one
+ *             (batch, head) pair
+ *   packed    (n_segments, capacity, head_dim/2) bytes, 4-byte aligned
+ *   norms     (n_segments, capacity) fp32
+ * position + n_new must not exceed capacity (FQ_ERR_INVALID_ARGUMENT, nothing written).
+ * Arithmetic and the other arguments as fq_tq4_compress.
+ */
+int fq_tq4_compress_into(const void* x, fq_dtype dtype, const float* rot_T_even,
+                         const float* rot_T_odd, const float* boundaries, int n_boundaries,
+                         uint8_t* packed, float* norms, int64_t n_segments, int64_t n_new,
+                         int64_t capacity, int64_t position, int head_dim, fq_stream_t stream);
+
+/*
  * Stage-1 + stage-2 (QJL) quantiser, contiguous outputs.
  * Arithmetic of TurboQuantProd.quantize (src/flashquant/core/quantizer.py:270-304):
  * codes/norm as above with the (bits-1)-bit tables, r = x - (c[code] Pi) n,
@@ -90,6 +109,23 @@ int fq_tq_prod_quantize(const void* x, fq_dtype dtype, const float* rotation,
 int fq_tq4_decompress(const uint8_t* packed, const float* norms, const float* centroids,
                       int n_centroids, void* out, fq_dtype out_dtype, int64_t n_vectors,
                       int head_dim, fq_stream_t stream);
+
+/*
+ * TQ4 decompress to the ORIGINAL space: out[v] = round_dtype((c[code] * n) Pi).
+ * Replaces CompressedDynamicCache._dequantize_tensor (src/flashquant/cache/hf_cache.py:196-219:
+ * nibble_unpack + ValueCompressor.decompress, src/flashquant/core/compressor.py:252-262, i.e.
+ *  TurboQuantMSE.dequantize, src/flashquant/core/quantizer.py:161-195, cast to the model dtype).
+ *   rotation    (head_dim, head_dim) fp32 row-major Pi
+ *   out         n_vectors x head_dim values of out_dtype (FQ_F32, FQ_F16 or FQ_BF16), 16-byte aligned
+ *   workspace   caller-owned, 16-byte aligned, fq_tq4_decompress_original_workspace_bytes(...)
+ *               bytes (the fp32 rotated-space rows)
+ * head_dim is 64 or 128.
+ */
+size_t fq_tq4_decompress_original_workspace_bytes(int64_t n_vectors, int head_dim);
+int fq_tq4_decompress_original(const uint8_t* packed, const float* norms, const float* centroids,
+                               int n_centroids, const float* rotation, void* out,
+                               fq_dtype out_dtype, int64_t n_vectors, int head_dim,
+                               void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
 /*
  * Compress-on-append: K and V of n_tokens new tokens are compressed and their packed
@@ -308,6 +344,26 @@ int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_t* k_packed
                           int num_kv_heads, int n_q, int n_kv, int head_dim, float sm_scale,
                           int is_causal, void* out, void* workspace, size_t workspace_bytes,
                           fq_stream_t stream);
+
+/*
+ * The same attention over the buffers of a contiguous cache whose keys and values were
+ * compressed with different rotations (CompressedDynamicCache: key seed 42, value seed 43,
+ * src/flashquant/cache/hf_cache.py:137-142) and read in place: get_compressed
+ * (hf_cache.py:387-414) hands out views of n_kv valid tokens inside buffers with room for
+ * kv_capacity tokens per (batch, head).  q_rot = round(q Pi_k^T), out = round(o_rot Pi_v).
+ *   k_packed, v_packed  (batch, num_kv_heads, kv_capacity, head_dim/2) bytes
+ *   k_norms, v_norms    (batch, num_kv_heads, kv_capacity) fp32
+ * Everything else as fq_fused_tq_attention (same workspace).
+ */
+int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uint8_t* k_packed,
+                             const float* k_norms, const uint8_t* v_packed,
+                             const float* v_norms, const float* centroids_k, int n_centroids_k,
+                             const float* centroids_v, int n_centroids_v,
+                             const float* rotation_k, const float* rotation_v, int batch,
+                             int num_q_heads, int num_kv_heads, int n_q, int n_kv,
+                             int64_t kv_capacity, int head_dim, float sm_scale, int is_causal,
+                             void* out, void* workspace, size_t workspace_bytes,
+                             fq_stream_t stream);
 
 /*
  * One decode step with HOST buffers: the host-side form of

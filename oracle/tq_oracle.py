@@ -328,8 +328,13 @@ def attention(q, k, v, sm_scale=None, is_causal=False):
 
 
 def fused_tq_attention(q, k_packed, k_norms, v_packed, v_norms, centroids_k, centroids_v,
-                       rotation, sm_scale=None, is_causal=False, q_chunk: int = 0):
+                       rotation, sm_scale=None, is_causal=False, q_chunk: int = 0,
+                       rotation_v=None):
     """Un-rotated q in, original-space output out.
+
+    ``rotation_v`` (default: ``rotation``) is the rotation the values were compressed with,
+    for the cache whose keys and values use different seeds
+    (src/flashquant/cache/hf_cache.py:137-142): the output is rotated back by it.
 
     src/flashquant/kernels/attention.py:99-107 (q_rot = (q.float() @ Pi^T).to(dtype)) then
     src/flashquant/kernels/cpu_reference.py:154-227 (decompress K and V in rotated space,
@@ -370,7 +375,44 @@ def fused_tq_attention(q, k_packed, k_norms, v_packed, v_norms, centroids_k, cen
                         torch.softmax(s, dim=-1), vd[bi, h, :kv_hi])
     # flash_attention_reference casts to its q dtype, which is fp32 here
     # (cpu_reference.py:195 passes q_rot.float()), so no rounding before the rotation.
-    return torch.matmul(out_rot.float(), rotation).to(q.dtype)
+    return torch.matmul(out_rot.float(), rotation if rotation_v is None else rotation_v).to(q.dtype)
+
+
+class CompressedCacheOracle:
+    """What CompressedDynamicCache keeps and returns, layer by layer, on the CPU.
+
+    src/flashquant/cache/hf_cache.py:260-365 with src/flashquant/core/compressor.py:235-262:
+    an update quantises ``x.float()`` (keys with the key tables, values with the value
+    tables), appends the nibble-packed codes and fp32 norms to the layer, de-quantises the
+    NEW tokens only, casts them to the dtype of the update and returns them appended to what
+    earlier updates returned.
+    """
+
+    def __init__(self, rotation_k, rotation_v, centroids, boundaries):
+        self.rotation_k, self.rotation_v = rotation_k, rotation_v
+        self.centroids, self.boundaries = centroids, boundaries
+        self.layers = {}
+
+    def _roundtrip(self, x, rotation):
+        idx, norms, _ = mse_quantize(x.float(), rotation, self.boundaries)
+        packed = nibble_pack(idx.to(torch.uint8))
+        back = mse_dequantize(nibble_unpack(packed).long(), norms, rotation, self.centroids)
+        return packed, norms.float(), back.to(x.dtype)
+
+    def update(self, key_states, value_states, layer_idx):
+        kp, kn, kd = self._roundtrip(key_states, self.rotation_k)
+        vp, vn, vd = self._roundtrip(value_states, self.rotation_v)
+        new = [kp, kn, vp, vn, kd, vd]
+        old = self.layers.get(layer_idx)
+        self.layers[layer_idx] = new if old is None else [
+            torch.cat([o, n], dim=2) for o, n in zip(old, new)]
+        return self.layers[layer_idx][4], self.layers[layer_idx][5]
+
+    def get_compressed(self, layer_idx):
+        return tuple(self.layers[layer_idx][:4])
+
+    def get_seq_length(self, layer_idx=0):
+        return 0 if layer_idx not in self.layers else self.layers[layer_idx][0].shape[2]
 
 
 def gather_paged(kv_cache, block_row, seq_len, num_kv_heads, head_dim, block_size,

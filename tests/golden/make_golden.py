@@ -187,6 +187,56 @@ def main() -> None:
         v_packed=vp_.numpy(), v_norms=vn_.numpy(),
         out_causal_bf16=bf16_bits(oc), out_full_bf16=bf16_bits(on),
     )
+    # ---- CompressedDynamicCache on a stand-in for DynamicCache ----------------------------
+    from flashquant.cache.hf_cache import CompressedDynamicCache
+
+    class Layer:
+        def __init__(self):
+            self.keys = self.values = None
+            self.is_initialized = False
+
+        def lazy_initialization(self, _):
+            self.is_initialized = True
+
+    class Cache:
+        def __init__(self):
+            self.layers = []
+            self.layer_class_to_replicate = Layer
+
+        def update(self, k_, v_, layer_idx, cache_kwargs=None):
+            return k_, v_
+
+        def get_seq_length(self, layer_idx=0):
+            return 0
+
+    g = torch.Generator().manual_seed(1004)
+    wrapped = CompressedDynamicCache(Cache(), head_dim=d, bits=4, max_seq_len=64)
+    hc = {"rotation_k": wrapped.rotation_k.numpy(), "rotation_v": wrapped.rotation_v.numpy()}
+    steps = [20, 1, 3, 1]
+    for layer in (0, 1):
+        for i, s_new in enumerate(steps):
+            kx = torch.randn(2, 2, s_new, d, generator=g)
+            kx[..., outl] *= 10.0
+            vx = torch.randn(2, 2, s_new, d, generator=g)
+            kx, vx = kx.to(torch.bfloat16), vx.to(torch.bfloat16)
+            ko, vo = wrapped.cache.update(kx, vx, layer)
+            hc[f"k_in_{layer}_{i}_bf16"] = bf16_bits(kx)
+            hc[f"v_in_{layer}_{i}_bf16"] = bf16_bits(vx)
+        kp, kn_, vp_, vn_ = wrapped.get_compressed(layer)
+        hc[f"k_packed_{layer}"] = kp.contiguous().numpy()
+        hc[f"k_norms_{layer}"] = kn_.contiguous().numpy()
+        hc[f"v_packed_{layer}"] = vp_.contiguous().numpy()
+        hc[f"v_norms_{layer}"] = vn_.contiguous().numpy()
+        hc[f"k_out_{layer}_bf16"] = bf16_bits(ko)
+        hc[f"v_out_{layer}_bf16"] = bf16_bits(vo)
+        hc[f"seq_len_{layer}"] = np.int64(wrapped.cache.get_seq_length(layer))
+    hc["steps"] = np.array(steps, dtype=np.int64)
+    hc["vram_bytes"] = np.int64(wrapped.vram_bytes())
+    hc["compressed_vram_bytes"] = np.int64(wrapped.compressed_vram_bytes())
+    hc["baseline_vram_bytes"] = np.int64(wrapped.baseline_vram_bytes())
+    wrapped.restore()
+    np.savez_compressed(os.path.join(HERE, "hf_cache.npz"), **hc)
+
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
