@@ -60,6 +60,9 @@ SIGNATURES = {
                                    _i, _f, _i, _p, _p, _sz, _p]),
     "fq_workspace_status": (_i, [_p, _p, _p]),
     "fq_tq4_compress_into": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _i64, _i64, _i64, _i64, _i, _p]),
+    "fq_cache_update_workspace_bytes": (_sz, [_i64, _i64, _i]),
+    "fq_cache_update": (_i, [_p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _p,
+                             _i64, _i64, _i64, _i64, _p, _p, _i64, _i64, _i, _p, _sz, _p]),
     "fq_tq4_decompress_original_workspace_bytes": (_sz, [_i64, _i]),
     "fq_tq4_decompress_original": (_i, [_p, _p, _p, _i, _p, _p, _i, _i64, _i, _p, _sz, _p]),
     "fq_fused_tq_attention_kv": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i,

@@ -88,23 +88,26 @@ class CompressedBuffer:
 class _GrowingTensor:
     """``(B, H, length, D)`` tensor that grows along the token axis by doubling its storage."""
 
-    def __init__(self, first: torch.Tensor) -> None:
-        b, h, s, d = first.shape
-        self._cap = max(16, 2 * s)
-        self._buf = torch.empty(b, h, self._cap, d, dtype=first.dtype, device=first.device)
+    def __init__(self, batch: int, heads: int, dim: int, dtype: torch.dtype,
+                 device: torch.device, first: int) -> None:
+        self._cap = max(16, 2 * first)
+        self._buf = torch.empty(batch, heads, self._cap, dim, dtype=dtype, device=device)
         self._len = 0
-        self.append(first)
 
-    def append(self, new: torch.Tensor) -> None:
-        s = new.shape[2]
-        if self._len + s > self._cap:
-            cap = max(2 * self._cap, self._len + s)
+    def reserve(self, new_tokens: int) -> int:
+        """Make room for ``new_tokens`` more rows; return the position of the first one."""
+        if self._len + new_tokens > self._cap:
+            cap = max(2 * self._cap, self._len + new_tokens)
             buf = torch.empty(*self._buf.shape[:2], cap, self._buf.shape[3], dtype=self._buf.dtype,
                               device=self._buf.device)
             buf[:, :, :self._len] = self._buf[:, :, :self._len]
             self._buf, self._cap = buf, cap
-        self._buf[:, :, self._len:self._len + s] = new
-        self._len += s
+        pos = self._len
+        self._len += new_tokens
+        return pos
+
+    def storage(self) -> torch.Tensor:
+        return self._buf
 
     def view(self) -> torch.Tensor:
         return self._buf[:, :, :self._len]
@@ -171,6 +174,7 @@ class CompressedDynamicCache:
         self._decompressed_k: List[Optional[_GrowingTensor]] = []
         self._decompressed_v: List[Optional[_GrowingTensor]] = []
         self._original_dtype: torch.dtype = torch.bfloat16
+        self._workspace: Optional[torch.Tensor] = None
         if getattr(cache, "_flashquant_wrapped", False):
             raise FlashQuantCacheError(
                 "Cache is already wrapped by FlashQuant. "
@@ -192,16 +196,6 @@ class CompressedDynamicCache:
         packed, norms = K.tq4_compress(tensor.reshape(b * h * s, 1, d), rot, bnd,
                                        rotation_T_even=even, rotation_T_odd=odd)
         return packed.reshape(b, h, s, d // 2), norms.reshape(b, h, s, 1)
-
-    def _compress_into(self, compressor: ValueCompressor, tensor: torch.Tensor,
-                       layer: _CompressedLayer) -> int:
-        """Compress ``tensor`` into the layer's buffer in place; return the first row written."""
-        even, odd, bnd, _, rot = compressor.tables(tensor.device)
-        buf = layer.buffer
-        pos = buf.reserve(tensor.shape[2])
-        K.tq4_compress_into(tensor, rot, bnd, buf._indices, buf._norms, pos,
-                            rotation_T_even=even, rotation_T_odd=odd)
-        return pos
 
     def _dequantize_tensor(self, compressor: ValueCompressor, indices: torch.Tensor,
                            norms: torch.Tensor) -> torch.Tensor:
@@ -248,14 +242,22 @@ class CompressedDynamicCache:
                                              key_states.device)
         v_layer = self._get_or_create_buffer(layer_idx, False, batch, heads, half_dim,
                                              torch.uint8, value_states.device)
-        k_pos = self._compress_into(self.key_compressor, key_states, k_layer)
-        v_pos = self._compress_into(self.value_compressor, value_states, v_layer)
+        kb, vb = k_layer.buffer, v_layer.buffer
+        if kb.length + new_seq > kb.max_seq or vb.length + new_seq > vb.max_seq:
+            kb.reserve(new_seq)  # raises the overflow error; nothing has been claimed yet
+            vb.reserve(new_seq)
+        tables_k = self.key_compressor.tables(key_states.device)
+        tables_v = self.value_compressor.tables(key_states.device)
 
         if getattr(self.cache, "layer_class_to_replicate", None) is not None:
             while len(self.cache.layers) <= layer_idx:
                 self.cache.layers.append(self.cache.layer_class_to_replicate())
 
         if self.fused_mode:
+            pos = kb.reserve(new_seq)
+            vb.reserve(new_seq)
+            K.cache_update(key_states, value_states, tables_k, tables_v, kb._indices, kb._norms,
+                           vb._indices, vb._norms, pos)
             layer = self.cache.layers[layer_idx]
             if hasattr(layer, "is_initialized") and not layer.is_initialized:
                 layer.lazy_initialization(key_states)
@@ -263,22 +265,27 @@ class CompressedDynamicCache:
             layer.values = value_states
             return key_states, value_states
 
-        # only the NEW tokens are de-quantised; they are read back from their rows in the buffers
-        kb, vb = k_layer.buffer, v_layer.buffer
-        new_k = self._dequantize_tensor(self.key_compressor,
-                                        kb._indices[:, :, k_pos:k_pos + new_seq],
-                                        kb._norms[:, :, k_pos:k_pos + new_seq])
-        new_v = self._dequantize_tensor(self.value_compressor,
-                                        vb._indices[:, :, v_pos:v_pos + new_seq],
-                                        vb._norms[:, :, v_pos:v_pos + new_seq])
+        # only the NEW tokens are de-quantised, straight into the rows behind the earlier ones
         if self._decompressed_k[layer_idx] is None:
-            self._decompressed_k[layer_idx] = _GrowingTensor(new_k)
-            self._decompressed_v[layer_idx] = _GrowingTensor(new_v)
-        else:
-            self._decompressed_k[layer_idx].append(new_k)
-            self._decompressed_v[layer_idx].append(new_v)
-        decompressed_k = self._decompressed_k[layer_idx].view()
-        decompressed_v = self._decompressed_v[layer_idx].view()
+            self._decompressed_k[layer_idx] = _GrowingTensor(
+                batch, heads, dim, key_states.dtype, key_states.device, new_seq)
+            self._decompressed_v[layer_idx] = _GrowingTensor(
+                batch, heads, dim, key_states.dtype, key_states.device, new_seq)
+        grown_k, grown_v = self._decompressed_k[layer_idx], self._decompressed_v[layer_idx]
+        pos = kb.reserve(new_seq)
+        vb.reserve(new_seq)
+        out_pos = grown_k.reserve(new_seq)
+        grown_v.reserve(new_seq)
+        need = batch * heads * new_seq * dim * 4
+        if self._workspace is None or self._workspace.numel() < need or \
+                self._workspace.device != key_states.device:
+            self._workspace = torch.empty(max(need, 1 << 16), dtype=torch.uint8,
+                                          device=key_states.device)
+        K.cache_update(key_states, value_states, tables_k, tables_v, kb._indices, kb._norms,
+                       vb._indices, vb._norms, pos, grown_k.storage(), grown_v.storage(), out_pos,
+                       self._workspace)
+        decompressed_k = grown_k.view()
+        decompressed_v = grown_v.view()
 
         if hasattr(self.cache, "layers") and layer_idx < len(self.cache.layers):
             layer = self.cache.layers[layer_idx]

@@ -13,14 +13,17 @@ template <typename T>
 __global__ void __launch_bounds__(kDecompressThreads) decompress_kernel(
     const uint8_t* __restrict__ packed, const float* __restrict__ norms,
     const float* __restrict__ centroids, int n_centroids, T* __restrict__ out,
-    int64_t n_words, int words_per_vec) {
+    int64_t n_words, int words_per_vec, RowMap in_map) {
   __shared__ float lut[16];
   if (threadIdx.x < 16) lut[threadIdx.x] = threadIdx.x < n_centroids ? centroids[threadIdx.x] : 0.f;
   __syncthreads();
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t w = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; w < n_words; w += stride) {
-    const uint32_t word = reinterpret_cast<const uint32_t*>(packed)[w];
-    const float n = norms[w / words_per_vec];
+    const int64_t vec = w / words_per_vec;
+    const int64_t row = in_map(vec);
+    const uint32_t word =
+        reinterpret_cast<const uint32_t*>(packed)[row * words_per_vec + (w - vec * words_per_vec)];
+    const float n = norms[row];
     float v[8];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -45,10 +48,11 @@ __global__ void __launch_bounds__(kDecompressThreads) decompress_kernel(
 
 using namespace fq;
 
-extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
-                                 const float* centroids, int n_centroids, void* out,
-                                 fq_dtype out_dtype, int64_t n_vectors, int head_dim,
-                                 fq_stream_t stream) {
+namespace fq {
+
+int decompress_rows(const uint8_t* packed, const float* norms, const float* centroids,
+                    int n_centroids, void* out, int out_dtype, int64_t n_vectors, int head_dim,
+                    RowMap in_map, cudaStream_t s) {
   FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
   if (n_vectors == 0) return FQ_OK;
   FQ_REQUIRE(packed && norms && centroids && out, FQ_ERR_INVALID_ARGUMENT,
@@ -66,25 +70,36 @@ extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t want = (n_words + kDecompressThreads - 1) / kDecompressThreads;
   const int grid = int(want < int64_t(sms) * 8 ? want : int64_t(sms) * 8);
-  cudaStream_t s = stream;
   switch (out_dtype) {
     case FQ_F32:
       decompress_kernel<float><<<grid, kDecompressThreads, 0, s>>>(
-          packed, norms, centroids, n_centroids, static_cast<float*>(out), n_words, words_per_vec);
+          packed, norms, centroids, n_centroids, static_cast<float*>(out), n_words, words_per_vec,
+          in_map);
       break;
     case FQ_F16:
       decompress_kernel<__half><<<grid, kDecompressThreads, 0, s>>>(
-          packed, norms, centroids, n_centroids, static_cast<__half*>(out), n_words, words_per_vec);
+          packed, norms, centroids, n_centroids, static_cast<__half*>(out), n_words, words_per_vec,
+          in_map);
       break;
     case FQ_BF16:
       decompress_kernel<__nv_bfloat16><<<grid, kDecompressThreads, 0, s>>>(
           packed, norms, centroids, n_centroids, static_cast<__nv_bfloat16*>(out), n_words,
-          words_per_vec);
+          words_per_vec, in_map);
       break;
     default:
-      return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", int(out_dtype));
+      return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", out_dtype);
   }
   return check_launch("decompress kernel launch");
+}
+
+}  // namespace fq
+
+extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
+                                 const float* centroids, int n_centroids, void* out,
+                                 fq_dtype out_dtype, int64_t n_vectors, int head_dim,
+                                 fq_stream_t stream) {
+  return decompress_rows(packed, norms, centroids, n_centroids, out, int(out_dtype), n_vectors,
+                         head_dim, RowMap(), stream);
 }
 
 // Decompress to the ORIGINAL space: (c[code] * norm) Pi, rounded to out_dtype.  The codes are

@@ -270,10 +270,28 @@ __device__ __forceinline__ float fast_log2(float x) {
   return r;
 }
 
+// Where row r of a contiguous list of rows lives in a buffer made of segments (the per-head
+// buffers of a contiguous cache): runs of seg_len rows land seg_stride rows apart, starting at
+// row seg_offset of each segment.  seg_len == 0: row r is row r.
+struct RowMap {
+  uint32_t seg_len = 0;
+  int64_t seg_stride = 0;
+  int64_t seg_offset = 0;
+  __host__ __device__ __forceinline__ int64_t operator()(int64_t r) const {
+    if (seg_len == 0) return r;
+    const int64_t seg = r / seg_len;
+    return seg * seg_stride + seg_offset + (r - seg * seg_len);
+  }
+};
+
 // rotate.cu: row rotations around the prefill kernel
 int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* out,
                      int64_t n_rows, int head_dim, cudaStream_t stream);
 int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out, int64_t n_rows,
-                int head_dim, cudaStream_t stream);
+                int head_dim, cudaStream_t stream, RowMap out_map = RowMap());
+// decompress.cu: codes (rows through in_map) -> rotated-space values, contiguous
+int decompress_rows(const uint8_t* packed, const float* norms, const float* centroids,
+                    int n_centroids, void* out, int out_dtype, int64_t n_vectors, int head_dim,
+                    RowMap in_map, cudaStream_t stream);
 
 }  // namespace fq

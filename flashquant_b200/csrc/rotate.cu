@@ -18,7 +18,7 @@ constexpr int kRotTile = 64;
 template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 __global__ void __launch_bounds__(kRotThreads, 1) rotate_rows_kernel(
     const TIn* __restrict__ x, const float* __restrict__ rotation, TOut* __restrict__ out,
-    int64_t n_rows) {
+    int64_t n_rows, RowMap out_map) {
   constexpr int JT = D / 32;
   constexpr int VPW = kRotTile / 8;
   constexpr int LDA = D + 4;
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kRotThreads, 1) rotate_rows_kernel(
 #pragma unroll
     for (int v = 0; v < VPW; ++v) {
       if (r0 + v >= n_rows) continue;
-      TOut* dst = out + (r0 + v) * D + lane * JT;
+      TOut* dst = out + out_map(r0 + v) * D + lane * JT;
       TOut o[JT];
 #pragma unroll
       for (int j = 0; j < JT; ++j) {
@@ -151,7 +151,7 @@ __device__ __forceinline__ void rt_store2<float>(float* p, float a, float b) {
 template <typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 __global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
     const TIn* __restrict__ x, const float* __restrict__ rotation, TOut* __restrict__ out,
-    int64_t n_rows) {
+    int64_t n_rows, RowMap out_map) {
   constexpr int D = 128;
   extern __shared__ __align__(16) unsigned char rt_smem[];
   __half* b_hi = reinterpret_cast<__half*>(rt_smem);  // plane[n][k] = B[k][n]
@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
        mt += int64_t(gridDim.x) * (kRtThreads / 32)) {
     const int64_t r0 = mt * 16 + g, r1 = r0 + 8;
     const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
+    const int64_t o0 = out_map(r0), o1 = out_map(r1);
     const TIn* x0 = x + (ok0 ? r0 : 0) * D + 2 * t;
     const TIn* x1 = x + (ok1 ? r1 : 0) * D + 2 * t;
     uint32_t xh[D / 16][4], xl[D / 16][4];
@@ -232,8 +233,8 @@ __global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
           if constexpr (kRoundViaIn) v[c] = to_f32(from_f32<TIn>(v[c]));  // round to x's type first
         }
         const int col = 8 * (grp * 4 + i) + 2 * t;
-        if (ok0) rt_store2<TOut>(out + r0 * D + col, v[0], v[1]);
-        if (ok1) rt_store2<TOut>(out + r1 * D + col, v[2], v[3]);
+        if (ok0) rt_store2<TOut>(out + o0 * D + col, v[0], v[1]);
+        if (ok1) rt_store2<TOut>(out + o1 * D + col, v[2], v[3]);
       }
     }
   }
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(kRtThreads, 2) rotate_rows_tc_kernel(
 
 template <typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 static int launch_rotate_tc(const void* x, const float* rotation, void* out, int64_t n_rows,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, RowMap out_map = RowMap()) {
   const size_t smem = size_t(2) * 128 * kRtLd * sizeof(__half);
   auto kern = rotate_rows_tc_kernel<TIn, TOut, kTranspose, kRoundViaIn>;
   static thread_local int set_dev = -1;
@@ -260,13 +261,13 @@ static int launch_rotate_tc(const void* x, const float* rotation, void* out, int
   const int64_t ctas_needed = (warp_tiles + kRtThreads / 32 - 1) / (kRtThreads / 32);
   const int grid = int(ctas_needed < 2 * int64_t(sms) ? ctas_needed : 2 * int64_t(sms));
   kern<<<grid, kRtThreads, smem, stream>>>(static_cast<const TIn*>(x), rotation,
-                                          static_cast<TOut*>(out), n_rows);
+                                          static_cast<TOut*>(out), n_rows, out_map);
   return check_launch("rotate kernel launch");
 }
 
 template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 static int launch_rotate_t(const void* x, const float* rotation, void* out, int64_t n_rows,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, RowMap out_map = RowMap()) {
   const size_t smem = (size_t(D) * D + size_t(kRotTile) * (D + 4)) * sizeof(float);
   auto kern = rotate_rows_kernel<D, TIn, TOut, kTranspose, kRoundViaIn>;
   static thread_local int set_dev = -1;
@@ -284,7 +285,7 @@ static int launch_rotate_t(const void* x, const float* rotation, void* out, int6
   if (tiles == 0) return FQ_OK;
   const int grid = int(tiles < 2 * int64_t(sms) ? tiles : 2 * int64_t(sms));
   kern<<<grid, kRotThreads, smem, stream>>>(static_cast<const TIn*>(x), rotation,
-                                           static_cast<TOut*>(out), n_rows);
+                                           static_cast<TOut*>(out), n_rows, out_map);
   return check_launch("rotate kernel launch");
 }
 
@@ -300,20 +301,20 @@ int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* ou
              : launch_rotate_t<64, __half, __half, true, true>(q, rotation, out, n_rows, stream);
 }
 
-// o_rot (fp32) -> round_dtype(o_rot Pi)
+// o_rot (fp32) -> round_dtype(o_rot Pi); row r of the result goes to row out_map(r) of `out`
 int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out, int64_t n_rows,
-                int head_dim, cudaStream_t stream) {
+                int head_dim, cudaStream_t stream, RowMap m) {
   if (dtype == FQ_F32)
     return head_dim == 128
-               ? launch_rotate_tc<float, float, false, false>(o_rot, rotation, out, n_rows, stream)
-               : launch_rotate_t<64, float, float, false, false>(o_rot, rotation, out, n_rows, stream);
+               ? launch_rotate_tc<float, float, false, false>(o_rot, rotation, out, n_rows, stream, m)
+               : launch_rotate_t<64, float, float, false, false>(o_rot, rotation, out, n_rows, stream, m);
   if (head_dim == 128)
     return dtype == FQ_BF16
-               ? launch_rotate_tc<float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)
-               : launch_rotate_tc<float, __half, false, false>(o_rot, rotation, out, n_rows, stream);
+               ? launch_rotate_tc<float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream, m)
+               : launch_rotate_tc<float, __half, false, false>(o_rot, rotation, out, n_rows, stream, m);
   return dtype == FQ_BF16
-             ? launch_rotate_t<64, float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream)
-             : launch_rotate_t<64, float, __half, false, false>(o_rot, rotation, out, n_rows, stream);
+             ? launch_rotate_t<64, float, __nv_bfloat16, false, false>(o_rot, rotation, out, n_rows, stream, m)
+             : launch_rotate_t<64, float, __half, false, false>(o_rot, rotation, out, n_rows, stream, m);
 }
 
 }  // namespace fq

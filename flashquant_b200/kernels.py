@@ -169,6 +169,48 @@ def tq4_decompress_original(
     return out
 
 
+def cache_update(key, value, tables_k, tables_v, k_packed, k_norms, v_packed, v_norms,
+                 position: int, k_out=None, v_out=None, out_position: int = 0,
+                 workspace: Optional[torch.Tensor] = None) -> None:
+    """One cache update in one native call: compress ``key`` / ``value`` ``(B, H, S, D)`` into
+    rows ``position ..`` of the code and norm buffers and, when ``k_out`` / ``v_out``
+    ``(B, H, out_capacity, D)`` are given, write the de-quantised new tokens to their rows
+    ``out_position ..`` (src/flashquant/cache/hf_cache.py:260-365).
+
+    ``tables_*``: (Pi^T even columns, Pi^T odd columns, boundaries, centroids, Pi) on the device.
+    """
+    N.require_cuda(key, value, k_packed, k_norms, v_packed, v_norms, k_out, v_out)
+    b, h, s, d = key.shape
+    if value.shape != key.shape or value.dtype != key.dtype:
+        raise ValueError("key and value must have the same shape and dtype")
+    cap = k_packed.shape[2]
+    for codes, norms in ((k_packed, k_norms), (v_packed, v_norms)):
+        if codes.shape != (b, h, cap, d // 2) or norms.shape[:3] != (b, h, cap):
+            raise ValueError("buffers must be (B, H, capacity, D/2) and (B, H, capacity, 1)")
+        if not (codes.is_contiguous() and norms.is_contiguous()):
+            raise ValueError("the cache buffers must be contiguous")
+    out_cap = 0
+    if k_out is not None:
+        out_cap = k_out.shape[2]
+        for o in (k_out, v_out):
+            if o.shape != (b, h, out_cap, d) or o.dtype != key.dtype or not o.is_contiguous():
+                raise ValueError("outputs must be contiguous (B, H, out_capacity, D) of key's dtype")
+    dev = key.device
+    key, value = _contig(key), _contig(value)
+    ek, ok_, bnd, cent, rk = tables_k
+    ev, ov, _, _, rv = tables_v
+    lib = N.load()
+    need = lib.fq_cache_update_workspace_bytes(b * h, s, d) if k_out is not None else 0
+    if need and (workspace is None or workspace.numel() < need):
+        raise ValueError(f"workspace of {need} bytes needed")
+    N.check(lib.fq_cache_update(
+        N.ptr(key), N.ptr(value), N.dtype_code(key.dtype), N.ptr(ek), N.ptr(ok_), N.ptr(rk),
+        N.ptr(ev), N.ptr(ov), N.ptr(rv), N.ptr(bnd), bnd.numel(), N.ptr(cent), cent.numel(),
+        N.ptr(k_packed), N.ptr(k_norms), N.ptr(v_packed), N.ptr(v_norms), b * h, s, cap,
+        int(position), N.ptr(k_out), N.ptr(v_out), out_cap, int(out_position), d,
+        N.ptr(workspace) if need else None, need, N.stream_ptr(dev)))
+
+
 def tq_prod_quantize(x, rotation, boundaries, centroids, qjl_matrix):
     """Two-stage quantiser on ``(..., D)``: packed codes, norms, packed sign bits, gamma.
 

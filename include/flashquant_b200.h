@@ -111,6 +111,35 @@ int fq_tq4_decompress(const uint8_t* packed, const float* norms, const float* ce
                       int head_dim, fq_stream_t stream);
 
 /*
+ * One update of a contiguous compressed cache in one call.
+ * Replaces the body of CompressedDynamicCache._compressed_update
+ * (src/flashquant/cache/hf_cache.py:260-365): _compress_tensor and CompressedBuffer.append for
+ * keys and values, then _dequantize_tensor of the NEW tokens and their concatenation behind
+ * the de-quantised tokens of earlier updates (torch.cat there, rows out_position .. of a
+ * caller-owned growing tensor here).  Six launches on `stream`, no allocation, no sync.
+ *   key, value          (n_segments, n_new, head_dim) of `dtype`, contiguous
+ *   rot_T_even/odd_k/v  the split transposed rotations of keys / values (fq_tq4_compress)
+ *   rotation_k/v        (head_dim, head_dim) fp32 row-major Pi of keys / values
+ *   k_packed, v_packed  (n_segments, capacity, head_dim/2) bytes; k_norms, v_norms
+ *                       (n_segments, capacity) fp32; rows position .. position+n_new-1 written
+ *   k_out, v_out        (n_segments, out_capacity, head_dim) of `dtype`, rows out_position ..
+ *                       written with round_dtype((c[code] n) Pi); both null = fused mode,
+ *                       nothing is de-quantised and rotation_k/v, centroids, workspace are unused
+ *   workspace           16-byte aligned, fq_cache_update_workspace_bytes(...) bytes
+ * head_dim is 64 or 128.
+ */
+size_t fq_cache_update_workspace_bytes(int64_t n_segments, int64_t n_new, int head_dim);
+int fq_cache_update(const void* key, const void* value, fq_dtype dtype,
+                    const float* rot_T_even_k, const float* rot_T_odd_k, const float* rotation_k,
+                    const float* rot_T_even_v, const float* rot_T_odd_v, const float* rotation_v,
+                    const float* boundaries, int n_boundaries, const float* centroids,
+                    int n_centroids, uint8_t* k_packed, float* k_norms, uint8_t* v_packed,
+                    float* v_norms, int64_t n_segments, int64_t n_new, int64_t capacity,
+                    int64_t position, void* k_out, void* v_out, int64_t out_capacity,
+                    int64_t out_position, int head_dim, void* workspace, size_t workspace_bytes,
+                    fq_stream_t stream);
+
+/*
  * TQ4 decompress to the ORIGINAL space: out[v] = round_dtype((c[code] * n) Pi).
  * Replaces CompressedDynamicCache._dequantize_tensor (src/flashquant/cache/hf_cache.py:196-219:
  * nibble_unpack + ValueCompressor.decompress, src/flashquant/core/compressor.py:252-262, i.e.
