@@ -586,7 +586,7 @@ def run_cache(args):
         "ms_per_step": ms_prompt, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"DynamicCache-style update, one layer: prompt of {b} x {n} bf16 "
                                f"tokens x {HKV} kv heads x {D} compressed into pre-allocated "
-                               "buffers (fused mode); inputs 67 MB per tensor, larger than L2 together "
+                               "buffers (fused mode); inputs 33.5 MB per tensor (K, V), larger than L2 together "
                                "with the outputs"},
         "decode_update_us": ms_step * 1e3, "decode_fused_attention_us": ms_attend * 1e3,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",

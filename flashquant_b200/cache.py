@@ -323,9 +323,9 @@ class CompressedDynamicCache:
                         sm_scale: Optional[float] = None, is_causal: bool = False) -> torch.Tensor:
         """Attention of ``query (B, H_Q, N_Q, D)`` over the compressed layer, read in place."""
         kp, kn, vp, vn = self.get_compressed(layer_idx)
-        return K.fused_tq_attention_kv(query, kp, kn, vp, vn, self.centroids_k, self.centroids_v,
-                                       self.key_compressor.tables(query.device)[4],
-                                       self.value_compressor.tables(query.device)[4],
+        tk = self.key_compressor.tables(query.device)
+        tv = self.value_compressor.tables(query.device)
+        return K.fused_tq_attention_kv(query, kp, kn, vp, vn, tk[3], tv[3], tk[4], tv[4],
                                        sm_scale=sm_scale, is_causal=is_causal)
 
     # ----- properties -----

@@ -126,8 +126,8 @@ extern "C" int fq_tq4_decompress_original(const uint8_t* packed, const float* no
   const size_t need = fq_tq4_decompress_original_workspace_bytes(n_vectors, head_dim);
   FQ_REQUIRE(workspace && aligned(workspace, 16) && workspace_bytes >= need, FQ_ERR_WORKSPACE,
              "fq_tq4_decompress_original: workspace of %zu bytes needed (16-byte aligned)", need);
-  FQ_REQUIRE(aligned(out, 16), FQ_ERR_ALIGNMENT,
-             "fq_tq4_decompress_original: out must be 16-byte aligned");
+  FQ_REQUIRE(aligned(out, 16) && aligned(rotation, 16), FQ_ERR_ALIGNMENT,
+             "fq_tq4_decompress_original: out and rotation must be 16-byte aligned");
   int rc = fq_tq4_decompress(packed, norms, centroids, n_centroids, workspace, FQ_F32, n_vectors,
                              head_dim, stream);
   if (rc != FQ_OK) return rc;

@@ -152,6 +152,13 @@ struct PrefillArgs {
   float scale_log2;
   int causal;
   uint32_t* status;
+  // Split mode (n_splits > 1, one query tile, no mask): blockIdx.x is a slice of split_tokens
+  // (a multiple of the key tile) keys and values; the CTA stores an un-normalised partial row
+  // [o * 2^0 (D) | m | l | - | -] per query row at part[(split * total_rows + row) * (D + 4)].
+  int n_splits;
+  int split_tokens;
+  int64_t total_rows;
+  float* part;
 };
 
 template <int D>
@@ -208,7 +215,9 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   // (0..63 of the output), the second the rest; a warp reaches TMEM lanes 32*(warp%4)..+31
   const int row = tid & (kPfM - 1), half = tid >> 7;
   // heavy (late) query tiles first: the causal work per tile grows with its index
-  const int m_tile = int(gridDim.x) - 1 - int(blockIdx.x);
+  const bool split_mode = p.n_splits > 1;
+  const int m_tile = split_mode ? 0 : int(gridDim.x) - 1 - int(blockIdx.x);
+  const int split = split_mode ? int(blockIdx.x) : 0;
   const int hq = blockIdx.y, b = blockIdx.z;
   const int group = p.hq / p.hkv;
   const int hkv = hq / group;
@@ -217,12 +226,19 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 
   int kv_end = p.nkv;
   if (p.causal && m0 + rows < kv_end) kv_end = m0 + rows;
+  // a slice of the keys: move the bases, the loop below then sees tokens 0 .. kv_end of it
+  const int kv_begin = split * p.split_tokens;
+  if (split_mode) {
+    kv_end = kv_end - kv_begin < p.split_tokens ? kv_end - kv_begin : p.split_tokens;
+    if (kv_end < 0) kv_end = 0;
+  }
   const int n_tiles = (kv_end + kPfN - 1) / kPfN;
 
-  const uint8_t* kc_base = p.k_packed + (int64_t(b) * p.hkv + hkv) * p.kv_stride * (D / 2);
-  const uint8_t* vc_base = p.v_packed + (int64_t(b) * p.hkv + hkv) * p.kv_stride * (D / 2);
-  const float* kn_base = p.k_norms + (int64_t(b) * p.hkv + hkv) * p.kv_stride;
-  const float* vn_base = p.v_norms + (int64_t(b) * p.hkv + hkv) * p.kv_stride;
+  const int64_t kv_row0 = (int64_t(b) * p.hkv + hkv) * p.kv_stride + kv_begin;
+  const uint8_t* kc_base = p.k_packed + kv_row0 * (D / 2);
+  const uint8_t* vc_base = p.v_packed + kv_row0 * (D / 2);
+  const float* kn_base = p.k_norms + kv_row0;
+  const float* vn_base = p.v_norms + kv_row0;
   // norms ride along with the codes when a bulk copy can take them (16-byte granularity)
   const bool norm_bulk = ((reinterpret_cast<uintptr_t>(kn_base) | reinterpret_cast<uintptr_t>(vn_base)) & 15) == 0;
 
@@ -519,8 +535,15 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     xch[tid] = l_run;
     __syncthreads();
     const float l_row = l_run + xch[tid ^ kPfM];  // both halves of the row
-    const float inv = l_row > 0.f ? 1.f / (l_row * 256.f) : 0.f;  // 2^-kPfPScaleLog2
-    float* dst = p.o_rot + ((int64_t(b) * p.hq + hq) * p.nq + q_pos) * D;
+    const int64_t row_global = (int64_t(b) * p.hq + hq) * p.nq + q_pos;
+    // 2^-kPfPScaleLog2, and 1/l unless the rows of the slices are still to be merged
+    const float inv = split_mode ? 1.f / 256.f : (l_row > 0.f ? 1.f / (l_row * 256.f) : 0.f);
+    float* dst = split_mode ? p.part + (int64_t(split) * p.total_rows + row_global) * (D + 4)
+                            : p.o_rot + row_global * D;
+    if (split_mode && half == 0 && row < rows) {
+      dst[D] = m_run;
+      dst[D + 1] = l_row;
+    }
 #pragma unroll
     for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
       float o[32];
@@ -542,6 +565,36 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   if (warp == 0) tmem_dealloc(tmem_base, kPfTmemCols);
 }
 
+// Merge of the slices' partial rows: o = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i with
+// M = max_i m_i (a slice without keys has m = -inf, l = 0).  32 threads per query row.
+template <int D>
+__global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ part,
+                                                           int n_splits, int64_t total_rows,
+                                                           float* __restrict__ o_rot) {
+  static_assert(D == 128, "four columns per thread");
+  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= total_rows) return;
+  float m_max = -INFINITY;
+  for (int s = 0; s < n_splits; ++s)
+    m_max = fmaxf(m_max, part[(int64_t(s) * total_rows + row) * (D + 4) + D]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float* pr = part + (int64_t(s) * total_rows + row) * (D + 4);
+    const float m = pr[D];
+    if (m == -INFINITY) continue;
+    const float w = fast_exp2(m - m_max);
+    const float4 o = *reinterpret_cast<const float4*>(pr + 4 * lane);
+    acc.x = fmaf(w, o.x, acc.x); acc.y = fmaf(w, o.y, acc.y);
+    acc.z = fmaf(w, o.z, acc.z); acc.w = fmaf(w, o.w, acc.w);
+    l = fmaf(w, pr[D + 1], l);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  *reinterpret_cast<float4*>(o_rot + row * D + 4 * lane) =
+      make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
@@ -559,20 +612,28 @@ static int launch_prefill_t(const PrefillArgs& a, cudaStream_t stream) {
                   cudaGetErrorString(e));
     set_dev = dev;
   }
-  dim3 grid((a.nq + kPfM - 1) / kPfM, a.hq, a.batch);
+  dim3 grid(a.n_splits > 1 ? a.n_splits : (a.nq + kPfM - 1) / kPfM, a.hq, a.batch);
   kern<<<grid, kPfThreads, S::kBytes, stream>>>(a);
-  return check_launch("prefill attention kernel launch");
+  int rc = check_launch("prefill attention kernel launch");
+  if (rc != FQ_OK || a.n_splits <= 1 || a.o_rot == nullptr) return rc;
+  prefill_merge_kernel<D><<<unsigned((a.total_rows + 7) / 8), 256, 0, stream>>>(
+      a.part, a.n_splits, a.total_rows, a.o_rot);
+  return check_launch("prefill merge kernel launch");
 }
 
+constexpr int kPfMaxSplits = 64;  // slices of the keys for a single query token
+
 struct PrefillWorkspace {
-  size_t q_rot_off, o_rot_off, total;
+  size_t q_rot_off, o_rot_off, part_off, total;
 };
-static PrefillWorkspace prefill_workspace(int64_t rows, int d) {
+// single_token: room for the partial rows of kPfMaxSplits slices behind the rotated output
+static PrefillWorkspace prefill_workspace(int64_t rows, int d, bool single_token) {
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   PrefillWorkspace w;
   w.q_rot_off = 256;
   w.o_rot_off = up(w.q_rot_off + size_t(rows) * d * 2);
-  w.total = up(w.o_rot_off + size_t(rows) * d * 4);
+  w.part_off = up(w.o_rot_off + size_t(rows) * d * 4);
+  w.total = single_token ? up(w.part_off + size_t(kPfMaxSplits) * rows * (d + 4) * 4) : w.part_off;
   return w;
 }
 
@@ -583,7 +644,7 @@ using namespace fq;
 extern "C" size_t fq_fused_tq_attention_workspace_bytes(int batch, int num_q_heads, int n_q,
                                                         int head_dim) {
   if (batch < 0 || num_q_heads < 0 || n_q < 0 || head_dim < 0) return 0;
-  return prefill_workspace(int64_t(batch) * num_q_heads * n_q, head_dim).total;
+  return prefill_workspace(int64_t(batch) * num_q_heads * n_q, head_dim, n_q == 1).total;
 }
 
 static int attention_common(const void* q, fq_dtype dtype, const uint8_t* k_packed,
@@ -612,12 +673,14 @@ static int attention_common(const void* q, fq_dtype dtype, const uint8_t* k_pack
              FQ_ERR_INVALID_ARGUMENT, "centroid count outside [1, 16]");
   FQ_REQUIRE(!is_causal || n_q == n_kv || n_q == 1, FQ_ERR_UNSUPPORTED,
              "fused attention: the causal mask is aligned at the first token (n_q == n_kv)");
-  FQ_REQUIRE(aligned(q, 16) && aligned(out, 16) && aligned(k_packed, 16) && aligned(v_packed, 16),
-             FQ_ERR_ALIGNMENT, "fused attention: q, out and the packed codes must be 16-byte aligned");
+  FQ_REQUIRE(aligned(q, 16) && aligned(out, 16) && aligned(k_packed, 16) && aligned(v_packed, 16) &&
+                 aligned(rotation, 16) && aligned(rotation_v, 16),
+             FQ_ERR_ALIGNMENT,
+             "fused attention: q, out, the rotations and the packed codes must be 16-byte aligned");
   const int64_t rows = int64_t(batch) * num_q_heads * n_q;
   if (rows == 0) return FQ_OK;
   FQ_REQUIRE(n_kv >= 1, FQ_ERR_INVALID_ARGUMENT, "fused attention: no keys");
-  const PrefillWorkspace w = prefill_workspace(rows, head_dim);
+  const PrefillWorkspace w = prefill_workspace(rows, head_dim, n_q == 1);
   FQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
              "fused attention: workspace of %zu bytes needed (256-byte aligned)", w.total);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
@@ -637,8 +700,34 @@ static int attention_common(const void* q, fq_dtype dtype, const uint8_t* k_pack
   a.scale_log2 = sm_scale * 1.4426950408889634f;
   a.causal = (is_causal && n_q > 1) ? 1 : 0;  // a single query token never needs the mask
   a.status = reinterpret_cast<uint32_t*>(ws);
+  const int group = num_q_heads / num_kv_heads;
+  if (n_q == 1 && group <= kPfM) {
+    // One query token: the query heads of a KV group become the rows of one query tile
+    // ((B, Hq, 1, D) read as (B, Hkv, group, D)), so the group's keys and values are
+    // de-quantised once, and the keys are cut into slices so that the CTAs fill the GPU.
+    a.hq = num_kv_heads; a.nq = group;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = (n_kv + kPfN - 1) / kPfN;
+    const int64_t per_slice = int64_t(batch) * num_kv_heads;
+    int want = int(2 * int64_t(sms) / per_slice);  // two CTAs per SM: one wave
+    want = want < 1 ? 1 : (want > kPfMaxSplits ? kPfMaxSplits : want);
+    const int tiles_per = (tiles + want - 1) / want;
+    const int n_splits = (tiles + tiles_per - 1) / tiles_per;
+    if (n_splits > 1) {
+      a.n_splits = n_splits;
+      a.split_tokens = tiles_per * kPfN;
+      a.total_rows = rows;
+      a.part = reinterpret_cast<float*>(ws + w.part_off);
+      // few rows: the back-rotation merges the slices on its way in, no merge launch
+      if (rotate_is_few_rows(rows)) a.o_rot = nullptr;
+    }
+  }
   rc = launch_prefill_t<128>(a, stream);
   if (rc != FQ_OK) return rc;
+  if (a.n_splits > 1 && a.o_rot == nullptr)
+    return rotate_back_merged(a.part, a.n_splits, dtype, rotation_v, out, rows, head_dim, stream);
   return rotate_back(o_rot, dtype, rotation_v, out, rows, head_dim, stream);
 }
 

@@ -289,9 +289,165 @@ static int launch_rotate_t(const void* x, const float* rotation, void* out, int6
   return check_launch("rotate kernel launch");
 }
 
+// ------------------------------------------------------------------------------------
+// A few rows (the query or the output of one decode step): staging the matrix in shared
+// memory would cost more than the product.  One thread per output column, kFewRows rows per
+// CTA, the matrix read straight through L1/L2 in fp32 FMAs.  With `part` the input row is
+// first merged from the partial rows of n_splits key slices, [o (D) | m | l | - | -] at
+// part[(split * n_rows + row) * (D + 4)]: o = sum 2^(m_i - M) o_i / sum 2^(m_i - M) l_i.
+// ------------------------------------------------------------------------------------
+constexpr int kFewRows = 4;
+constexpr int64_t kFewRowsMax = 1024;  // above this the tensor-core kernel wins
+
+// kFewRows * D threads.  Every thread reads D/16 or D/4 consecutive floats of the matrix as
+// float4, adjacent threads adjacent chunks (coalesced, few loads in a row per thread):
+//   x Pi^T: thread (j, slice of D/4 k) -> partial of column j, summed over 4 adjacent lanes;
+//   x Pi:   thread (4 columns, slice of D/16 k) -> partials summed over 16 slices in shared memory.
+template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
+__global__ void __launch_bounds__(kFewRows * D) rotate_few_rows_kernel(
+    const TIn* __restrict__ x, const float* __restrict__ rotation, TOut* __restrict__ out,
+    int64_t n_rows, RowMap out_map, const float* __restrict__ part, int n_splits) {
+  static_assert(kFewRows == 4, "thread maps below");
+  __shared__ __align__(16) float xs[kFewRows][D];
+  __shared__ __align__(16) float red[kTranspose ? 1 : 16][kFewRows][D];
+  const int t = threadIdx.x;
+  const int64_t r0 = int64_t(blockIdx.x) * kFewRows;
+  {
+    const int r = t / D, j = t % D;
+    float v = 0.f;
+    if (r0 + r < n_rows) {
+      if (part) {
+        float m_max = -INFINITY;
+        for (int s = 0; s < n_splits; ++s)
+          m_max = fmaxf(m_max, part[(int64_t(s) * n_rows + r0 + r) * (D + 4) + D]);
+        float acc = 0.f, l = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+          const float* pr = part + (int64_t(s) * n_rows + r0 + r) * (D + 4);
+          const float m = pr[D];
+          if (m == -INFINITY) continue;
+          const float w = fast_exp2(m - m_max);
+          acc = fmaf(w, pr[j], acc);
+          l = fmaf(w, pr[D + 1], l);
+        }
+        v = l > 0.f ? acc / l : 0.f;
+      } else {
+        v = to_f32(x[(r0 + r) * D + j]);
+      }
+    }
+    xs[r][j] = v;
+  }
+  __syncthreads();
+  auto store = [&](int r, int j, float v) {
+    if (r0 + r >= n_rows) return;
+    if constexpr (kRoundViaIn) v = to_f32(from_f32<TIn>(v));  // round to x's type first
+    out[out_map(r0 + r) * D + j] = from_f32<TOut>(v);
+  };
+  if constexpr (kTranspose) {  // out[r][j] = sum_k x[r][k] Pi[j][k]
+    const int j = t >> 2, sl = t & 3;
+    constexpr int kLen = D / 4;
+    const float4* prow = reinterpret_cast<const float4*>(rotation + j * D + sl * kLen);
+    float4 b[kLen / 4];
+#pragma unroll
+    for (int i = 0; i < kLen / 4; ++i) b[i] = prow[i];
+    float acc[kFewRows];
+#pragma unroll
+    for (int r = 0; r < kFewRows; ++r) {
+      acc[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < kLen / 4; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(&xs[r][sl * kLen + 4 * i]);
+        acc[r] = fmaf(a.x, b[i].x, acc[r]);
+        acc[r] = fmaf(a.y, b[i].y, acc[r]);
+        acc[r] = fmaf(a.z, b[i].z, acc[r]);
+        acc[r] = fmaf(a.w, b[i].w, acc[r]);
+      }
+      acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 1);
+      acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 2);
+    }
+    if (sl == 0) {
+#pragma unroll
+      for (int r = 0; r < kFewRows; ++r) store(r, j, acc[r]);
+    }
+  } else {  // out[r][j] = sum_k x[r][k] Pi[k][j]
+    constexpr int kCols4 = D / 4, kLen = D / 16;
+    const int c4 = t % kCols4, ks = t / kCols4;
+    float4 b[kLen];
+#pragma unroll
+    for (int i = 0; i < kLen; ++i)
+      b[i] = *reinterpret_cast<const float4*>(rotation + (ks * kLen + i) * D + 4 * c4);
+#pragma unroll
+    for (int r = 0; r < kFewRows; ++r) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < kLen; ++i) {
+        const float a = xs[r][ks * kLen + i];
+        acc.x = fmaf(a, b[i].x, acc.x); acc.y = fmaf(a, b[i].y, acc.y);
+        acc.z = fmaf(a, b[i].z, acc.z); acc.w = fmaf(a, b[i].w, acc.w);
+      }
+      *reinterpret_cast<float4*>(&red[ks][r][4 * c4]) = acc;
+    }
+    __syncthreads();
+    const int r = t / D, j = t % D;
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < 16; ++s) v += red[s][r][j];
+    store(r, j, v);
+  }
+}
+
+template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
+static int launch_rotate_few(const void* x, const float* rotation, void* out, int64_t n_rows,
+                             cudaStream_t stream, RowMap out_map, const float* part = nullptr,
+                             int n_splits = 0) {
+  if (n_rows == 0) return FQ_OK;
+  rotate_few_rows_kernel<D, TIn, TOut, kTranspose, kRoundViaIn>
+      <<<unsigned((n_rows + kFewRows - 1) / kFewRows), kFewRows * D, 0, stream>>>(
+          static_cast<const TIn*>(x), rotation, static_cast<TOut*>(out), n_rows, out_map, part,
+          n_splits);
+  return check_launch("rotate kernel launch");
+}
+
+template <int D, bool kTranspose, bool kRoundViaIn, typename TIn>
+static int rotate_few_out(const void* x, int out_dtype, const float* rotation, void* out,
+                          int64_t n_rows, cudaStream_t stream, RowMap m, const float* part,
+                          int n_splits) {
+  switch (out_dtype) {
+    case FQ_F32:
+      return launch_rotate_few<D, TIn, float, kTranspose, kRoundViaIn>(x, rotation, out, n_rows,
+                                                                        stream, m, part, n_splits);
+    case FQ_F16:
+      return launch_rotate_few<D, TIn, __half, kTranspose, kRoundViaIn>(x, rotation, out, n_rows,
+                                                                         stream, m, part, n_splits);
+    case FQ_BF16:
+      return launch_rotate_few<D, TIn, __nv_bfloat16, kTranspose, kRoundViaIn>(
+          x, rotation, out, n_rows, stream, m, part, n_splits);
+  }
+  return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", out_dtype);
+}
+
+// merged partial rows of key slices -> round_dtype(o Pi) in one launch (few rows only)
+int rotate_back_merged(const float* part, int n_splits, int dtype, const float* rotation,
+                       void* out, int64_t n_rows, int head_dim, cudaStream_t stream) {
+  if (head_dim == 128)
+    return rotate_few_out<128, false, false, float>(nullptr, dtype, rotation, out, n_rows, stream,
+                                                    RowMap(), part, n_splits);
+  return rotate_few_out<64, false, false, float>(nullptr, dtype, rotation, out, n_rows, stream,
+                                                 RowMap(), part, n_splits);
+}
+bool rotate_is_few_rows(int64_t n_rows) { return n_rows <= kFewRowsMax; }
+
 // q (dtype) -> fp16 copy of round_dtype(q Pi^T)
 int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* out,
                      int64_t n_rows, int head_dim, cudaStream_t stream) {
+  if (n_rows <= kFewRowsMax) {
+    if (head_dim == 128)
+      return dtype == FQ_BF16
+                 ? launch_rotate_few<128, __nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream, RowMap())
+                 : launch_rotate_few<128, __half, __half, true, true>(q, rotation, out, n_rows, stream, RowMap());
+    return dtype == FQ_BF16
+               ? launch_rotate_few<64, __nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream, RowMap())
+               : launch_rotate_few<64, __half, __half, true, true>(q, rotation, out, n_rows, stream, RowMap());
+  }
   if (head_dim == 128)
     return dtype == FQ_BF16
                ? launch_rotate_tc<__nv_bfloat16, __half, true, true>(q, rotation, out, n_rows, stream)
@@ -304,6 +460,10 @@ int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* ou
 // o_rot (fp32) -> round_dtype(o_rot Pi); row r of the result goes to row out_map(r) of `out`
 int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out, int64_t n_rows,
                 int head_dim, cudaStream_t stream, RowMap m) {
+  if (n_rows <= kFewRowsMax)
+    return head_dim == 128
+               ? rotate_few_out<128, false, false, float>(o_rot, dtype, rotation, out, n_rows, stream, m, nullptr, 0)
+               : rotate_few_out<64, false, false, float>(o_rot, dtype, rotation, out, n_rows, stream, m, nullptr, 0);
   if (dtype == FQ_F32)
     return head_dim == 128
                ? launch_rotate_tc<float, float, false, false>(o_rot, rotation, out, n_rows, stream, m)

@@ -86,6 +86,18 @@ def test_longer_sequence_chunked_oracle(consts):
     attention_close(run_gpu(case, is_causal=True), ref)
 
 
+@pytest.mark.parametrize("b,hq,hkv,nkv", [(2, 32, 8, 4133), (1, 4, 4, 1000), (3, 8, 2, 64),
+                                         (1, 16, 1, 70)])
+def test_single_query_token_over_many_keys(consts, b, hq, hkv, nkv):
+    # one query token per sequence (a decode step over a contiguous cache): the heads of a KV
+    # group share a query tile and the keys are cut into slices that a second kernel merges
+    case = list(make_case(consts, b, hq, hkv, nkv, seed=500 + nkv))
+    case[0] = case[0][:, :, -1:].contiguous()
+    ref = O.fused_tq_attention(*case, is_causal=True)
+    attention_close(run_gpu(tuple(case), is_causal=True), ref)
+    assert K.attention_workspace_status(torch.device(DEV)) == 0
+
+
 def test_argument_errors(consts):
     from flashquant_b200._native import FlashQuantNativeError
     case = make_case(consts, 1, 4, 2, 64, seed=3)
