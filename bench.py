@@ -616,7 +616,7 @@ def main():
                     help="decode is the headline; the others time further rows on one GPU")
     ap.add_argument("--prefill-batch", type=int, default=4)
     ap.add_argument("--prefill-seq", type=int, default=8192)
-    ap.add_argument("--traffic", type=float, default=148.96e6,
+    ap.add_argument("--traffic", type=float, default=148.76e6,
                     help="DRAM bytes per launch of the decode kernel (dram read + write) from "
                          "the ncu capture summarised in profiles/paged_decode_kernel_config1.md")
     args = ap.parse_args()

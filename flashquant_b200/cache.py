@@ -234,6 +234,11 @@ class CompressedDynamicCache:
         if not self.enabled:
             return self._original_update(key_states, value_states, layer_idx, cache_kwargs)
         N.require_cuda(key_states, value_states)
+        if value_states.shape != key_states.shape or value_states.dtype != key_states.dtype:
+            raise ValueError("key_states and value_states must have the same shape and dtype")
+        grown = self._decompressed_k[layer_idx] if layer_idx < len(self._decompressed_k) else None
+        if grown is not None and not self.fused_mode and grown.storage().dtype != key_states.dtype:
+            raise ValueError(f"layer {layer_idx} was filled with {grown.storage().dtype} tensors")
         self._original_dtype = key_states.dtype
         self._ensure_layer(layer_idx)
         batch, heads, new_seq, dim = key_states.shape

@@ -302,3 +302,69 @@ def test_compress_into_equals_compress_then_copy(consts):
         fq.tq4_compress_into(x, rot, b4, packed, norms, 41)  # 41 + 50 > 90
     # nothing to do
     fq.tq4_compress_into(x[:, :, :0], rot, b4, packed, norms, 90)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,n_vec,dtype", [(128, 5000, torch.bfloat16), (128, 33, torch.float32),
+                                             (64, 3000, torch.float16), (64, 7, torch.bfloat16)])
+def test_decompress_to_the_original_space(consts, dim, n_vec, dtype):
+    # both rotation kernels (few rows / many rows) at both head sizes
+    cent, bnd = O.lloyd_max_codebook(dim, 4)
+    rot = O.haar_rotation(dim, 42)
+    x = torch.randn(n_vec, 1, dim, generator=torch.Generator().manual_seed(n_vec)) * 2.0
+    packed, norms = O.compress(x, rot, bnd)
+    ref = O.mse_dequantize(O.nibble_unpack(packed).long(), norms, rot, cent).to(dtype)
+    got = fq.tq4_decompress_original(packed.to(DEV), norms.to(DEV), cent, rot, dtype=dtype)
+    assert got.shape == (n_vec, 1, dim) and got.dtype == dtype
+    ulp_close(got.cpu(), ref, dtype)
+    empty = fq.tq4_decompress_original(packed[:0].to(DEV), norms[:0].to(DEV), cent, rot, dtype=dtype)
+    assert empty.shape == (0, 1, dim)
+
+
+@pytest.mark.gpu
+def test_update_edge_cases(consts):
+    rk, rv = O.haar_rotation(128, 42), O.haar_rotation(128, 43)
+    cache = MockDynamicCache()
+    with wrap_with_rotations(cache, rk, rv, bits=4, max_seq_len=40) as w:
+        k = torch.randn(1, 2, 5, 128, generator=torch.Generator().manual_seed(1)).half().to(DEV)
+        ko, _ = cache.update(k, k, 3)  # layers 0..2 stay empty
+        assert cache.get_seq_length(3) == 5 and cache.get_seq_length(0) == 0
+        assert len(cache.layers) == 4
+        with pytest.raises(FlashQuantCacheError):
+            w.get_compressed(1)
+        # an update without tokens changes nothing
+        ko2, _ = cache.update(k[:, :, :0], k[:, :, :0], 3)
+        assert cache.get_seq_length(3) == 5 and torch.equal(ko2, ko)
+        # the running tensor outgrows its first allocation (16 rows) and keeps its contents
+        for _ in range(3):
+            ko3, _ = cache.update(k, k, 3)
+        assert ko3.shape == (1, 2, 20, 128) and torch.equal(ko3[:, :, :5], ko)
+        assert torch.equal(ko3[:, :, 15:20], ko)  # same tokens in, same values out
+        # a zero vector: norm 0, every coordinate on the middle code, de-quantised to zero
+        z = torch.zeros(1, 2, 1, 128, dtype=torch.float16, device=DEV)
+        kz, _ = cache.update(z, z, 3)
+        kp, kn, _, _ = w.get_compressed(3)
+        assert bool((kn[:, :, -1] == 0).all()) and bool((kp[:, :, -1] == 0x88).all())
+        assert bool((kz[:, :, -1] == 0).all())
+        # mixed dtypes are refused before anything is written
+        with pytest.raises(ValueError):
+            cache.update(k, k.float(), 3)
+        with pytest.raises(ValueError):
+            cache.update(k.float(), k.float(), 3)
+        assert cache.get_seq_length(3) == 21
+    # native argument checks
+    lib = _native.load()
+    assert lib.fq_cache_update_workspace_bytes(6, 5, 128) == 6 * 5 * 128 * 4
+    tk, tv = w.key_compressor.tables(torch.device(DEV)), w.value_compressor.tables(torch.device(DEV))
+    kb, vb = w._compressed_keys[3].buffer, w._compressed_values[3].buffer
+    out = torch.empty(1, 2, 64, 128, dtype=torch.float16, device=DEV)
+    small = torch.empty(16, dtype=torch.uint8, device=DEV)
+    with pytest.raises((_native.FlashQuantNativeError, ValueError)):
+        fq.kernels.cache_update(k, k, tk, tv, kb._indices, kb._norms, vb._indices, vb._norms, 0,
+                                out, out.clone(), 0, small)
+    with pytest.raises(_native.FlashQuantNativeError):  # 38 + 5 > 40
+        fq.kernels.cache_update(k, k, tk, tv, kb._indices, kb._norms, vb._indices, vb._norms, 38)
+    with pytest.raises(ValueError, match="capacity"):
+        fq.fused_tq_attention_kv(k, kb._indices[:, :, :5], kb._norms[:, :, :5],
+                                 vb._indices[:, :, :5].contiguous(), vb._norms[:, :, :5].contiguous(),
+                                 tk[3], tv[3], tk[4], tv[4])
