@@ -128,6 +128,14 @@ extern "C" int fq_tq4_decompress_original(const uint8_t* packed, const float* no
              "fq_tq4_decompress_original: workspace of %zu bytes needed (16-byte aligned)", need);
   FQ_REQUIRE(aligned(out, 16) && aligned(rotation, 16), FQ_ERR_ALIGNMENT,
              "fq_tq4_decompress_original: out and rotation must be 16-byte aligned");
+  if (rotate_is_few_rows(n_vectors)) {
+    FQ_REQUIRE(packed && norms && centroids, FQ_ERR_INVALID_ARGUMENT,
+               "fq_tq4_decompress_original: null pointer");
+    FQ_REQUIRE(n_centroids >= 1 && n_centroids <= 16, FQ_ERR_INVALID_ARGUMENT,
+               "n_centroids %d outside [1, 16]", n_centroids);
+    return rotate_back_from_codes(packed, norms, centroids, n_centroids, RowMap(), int(out_dtype),
+                                  rotation, out, n_vectors, head_dim, stream, RowMap());
+  }
   int rc = fq_tq4_decompress(packed, norms, centroids, n_centroids, workspace, FQ_F32, n_vectors,
                              head_dim, stream);
   if (rc != FQ_OK) return rc;

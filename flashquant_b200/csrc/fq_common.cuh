@@ -293,6 +293,11 @@ int rotate_back(const float* o_rot, int dtype, const float* rotation, void* out,
 int rotate_back_merged(const float* part, int n_splits, int dtype, const float* rotation,
                        void* out, int64_t n_rows, int head_dim, cudaStream_t stream);
 bool rotate_is_few_rows(int64_t n_rows);
+// the same from nibble codes + norms (rows through in_map), expanded on the way in; few rows only
+int rotate_back_from_codes(const uint8_t* codes, const float* norms, const float* centroids,
+                           int n_centroids, RowMap in_map, int dtype, const float* rotation,
+                           void* out, int64_t n_rows, int head_dim, cudaStream_t stream,
+                           RowMap out_map);
 // decompress.cu: codes (rows through in_map) -> rotated-space values, contiguous
 int decompress_rows(const uint8_t* packed, const float* norms, const float* centroids,
                     int n_centroids, void* out, int out_dtype, int64_t n_vectors, int head_dim,

@@ -299,6 +299,16 @@ static int launch_rotate_t(const void* x, const float* rotation, void* out, int6
 constexpr int kFewRows = 4;
 constexpr int64_t kFewRowsMax = 1024;  // above this the tensor-core kernel wins
 
+// Input rows given as nibble codes + norm (row r of the product is row map(r) of the buffers):
+// value j of a row is centroids[code_j] * norm, code_2i the high nibble of byte i.
+struct CodeRows {
+  const uint8_t* codes = nullptr;
+  const float* norms = nullptr;
+  const float* centroids = nullptr;
+  int n_centroids = 0;
+  RowMap map;
+};
+
 // kFewRows * D threads.  Every thread reads D/16 or D/4 consecutive floats of the matrix as
 // float4, adjacent threads adjacent chunks (coalesced, few loads in a row per thread):
 //   x Pi^T: thread (j, slice of D/4 k) -> partial of column j, summed over 4 adjacent lanes;
@@ -306,7 +316,7 @@ constexpr int64_t kFewRowsMax = 1024;  // above this the tensor-core kernel wins
 template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 __global__ void __launch_bounds__(kFewRows * D) rotate_few_rows_kernel(
     const TIn* __restrict__ x, const float* __restrict__ rotation, TOut* __restrict__ out,
-    int64_t n_rows, RowMap out_map, const float* __restrict__ part, int n_splits) {
+    int64_t n_rows, RowMap out_map, const float* __restrict__ part, int n_splits, CodeRows cr) {
   static_assert(kFewRows == 4, "thread maps below");
   __shared__ __align__(16) float xs[kFewRows][D];
   __shared__ __align__(16) float red[kTranspose ? 1 : 16][kFewRows][D];
@@ -330,6 +340,11 @@ __global__ void __launch_bounds__(kFewRows * D) rotate_few_rows_kernel(
           l = fmaf(w, pr[D + 1], l);
         }
         v = l > 0.f ? acc / l : 0.f;
+      } else if (cr.codes) {
+        const int64_t row_in = cr.map(r0 + r);
+        const uint32_t byte = cr.codes[row_in * (D / 2) + (j >> 1)];
+        const int code = (j & 1) ? int(byte & 15u) : int(byte >> 4);
+        v = (code < cr.n_centroids ? cr.centroids[code] : 0.f) * cr.norms[row_in];
       } else {
         v = to_f32(x[(r0 + r) * D + j]);
       }
@@ -398,29 +413,29 @@ __global__ void __launch_bounds__(kFewRows * D) rotate_few_rows_kernel(
 template <int D, typename TIn, typename TOut, bool kTranspose, bool kRoundViaIn>
 static int launch_rotate_few(const void* x, const float* rotation, void* out, int64_t n_rows,
                              cudaStream_t stream, RowMap out_map, const float* part = nullptr,
-                             int n_splits = 0) {
+                             int n_splits = 0, CodeRows cr = CodeRows()) {
   if (n_rows == 0) return FQ_OK;
   rotate_few_rows_kernel<D, TIn, TOut, kTranspose, kRoundViaIn>
       <<<unsigned((n_rows + kFewRows - 1) / kFewRows), kFewRows * D, 0, stream>>>(
           static_cast<const TIn*>(x), rotation, static_cast<TOut*>(out), n_rows, out_map, part,
-          n_splits);
+          n_splits, cr);
   return check_launch("rotate kernel launch");
 }
 
 template <int D, bool kTranspose, bool kRoundViaIn, typename TIn>
 static int rotate_few_out(const void* x, int out_dtype, const float* rotation, void* out,
                           int64_t n_rows, cudaStream_t stream, RowMap m, const float* part,
-                          int n_splits) {
+                          int n_splits, CodeRows cr = CodeRows()) {
   switch (out_dtype) {
     case FQ_F32:
-      return launch_rotate_few<D, TIn, float, kTranspose, kRoundViaIn>(x, rotation, out, n_rows,
-                                                                        stream, m, part, n_splits);
+      return launch_rotate_few<D, TIn, float, kTranspose, kRoundViaIn>(
+          x, rotation, out, n_rows, stream, m, part, n_splits, cr);
     case FQ_F16:
-      return launch_rotate_few<D, TIn, __half, kTranspose, kRoundViaIn>(x, rotation, out, n_rows,
-                                                                         stream, m, part, n_splits);
+      return launch_rotate_few<D, TIn, __half, kTranspose, kRoundViaIn>(
+          x, rotation, out, n_rows, stream, m, part, n_splits, cr);
     case FQ_BF16:
       return launch_rotate_few<D, TIn, __nv_bfloat16, kTranspose, kRoundViaIn>(
-          x, rotation, out, n_rows, stream, m, part, n_splits);
+          x, rotation, out, n_rows, stream, m, part, n_splits, cr);
   }
   return fail(FQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", out_dtype);
 }
@@ -435,6 +450,21 @@ int rotate_back_merged(const float* part, int n_splits, int dtype, const float* 
                                                  RowMap(), part, n_splits);
 }
 bool rotate_is_few_rows(int64_t n_rows) { return n_rows <= kFewRowsMax; }
+
+// codes + norms (rows through in_map) -> round_dtype((c[code] n) Pi) in one launch (few rows only)
+int rotate_back_from_codes(const uint8_t* codes, const float* norms, const float* centroids,
+                           int n_centroids, RowMap in_map, int dtype, const float* rotation,
+                           void* out, int64_t n_rows, int head_dim, cudaStream_t stream,
+                           RowMap out_map) {
+  CodeRows cr;
+  cr.codes = codes; cr.norms = norms; cr.centroids = centroids; cr.n_centroids = n_centroids;
+  cr.map = in_map;
+  if (head_dim == 128)
+    return rotate_few_out<128, false, false, float>(nullptr, dtype, rotation, out, n_rows, stream,
+                                                    out_map, nullptr, 0, cr);
+  return rotate_few_out<64, false, false, float>(nullptr, dtype, rotation, out, n_rows, stream,
+                                                 out_map, nullptr, 0, cr);
+}
 
 // q (dtype) -> fp16 copy of round_dtype(q Pi^T)
 int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* out,

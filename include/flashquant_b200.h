@@ -116,7 +116,9 @@ int fq_tq4_decompress(const uint8_t* packed, const float* norms, const float* ce
  * (src/flashquant/cache/hf_cache.py:260-365): _compress_tensor and CompressedBuffer.append for
  * keys and values, then _dequantize_tensor of the NEW tokens and their concatenation behind
  * the de-quantised tokens of earlier updates (torch.cat there, rows out_position .. of a
- * caller-owned growing tensor here).  Six launches on `stream`, no allocation, no sync.
+ * caller-owned growing tensor here).  Four launches on `stream` for up to 1024 new vectors
+ * (the back-rotation expands the codes itself and the workspace is not used), six above;
+ * no allocation, no sync.
  *   key, value          (n_segments, n_new, head_dim) of `dtype`, contiguous
  *   rot_T_even/odd_k/v  the split transposed rotations of keys / values (fq_tq4_compress)
  *   rotation_k/v        (head_dim, head_dim) fp32 row-major Pi of keys / values

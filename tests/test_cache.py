@@ -207,8 +207,8 @@ def test_update_matches_reference_outputs(consts):
         assert w.baseline_vram_bytes() == int(z["baseline_vram_bytes"])
         assert w.vram_bytes() == int(z["vram_bytes"])
         assert w.compression_stats()["compression_ratio"] == 3.76
-    # per update: two compress launches, two decompress launches, two back-rotations
-    assert _native.load().fq_launch_count() - launches0 == 2 * 4 * 6
+    # per update of a few rows: two compress launches, two back-rotations that expand the codes
+    assert _native.load().fq_launch_count() - launches0 == 2 * 4 * 4
 
 
 @pytest.mark.gpu
