@@ -11,6 +11,7 @@ from .kernels import (  # noqa: F401
     paged_decode_partials,
     split_k_merge,
     split_k_paged_decode,
+    split_k_paged_decode_multi,
     split_k_paged_decode_qjl,
     tq4_compress,
     tq4_compress_append,

@@ -415,6 +415,34 @@ def split_k_paged_decode(
     return out
 
 
+def split_k_paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
+                               rotation, num_kv_heads, head_dim, block_size, sm_scale=None,
+                               num_splits=0):
+    """Decode attention of the LAST ``n_q`` tokens of every sequence (speculative / multi-token
+    steps): ``q (num_seqs, n_q, H_q, D)``; ``seq_lens`` counts the new tokens, which are already
+    in the cache; query ``i`` of a sequence sees keys ``0 .. seq_len - n_q + i``.
+
+    The reference takes its fused decode only for a step of exactly one token
+    (src/flashquant/vllm/impl.py:441) and otherwise de-quantises the whole cache for a causal
+    varlen attention (impl.py:265-336, 477-509).  Here every (sequence, token) pair is a row of
+    the paged decode kernel with its own length and the sequence's block-table row, so the
+    call is one launch of the same kernel and nothing is de-quantised to memory.
+    """
+    N.require_cuda(q, kv_cache, block_table, seq_lens)
+    if q.dim() != 4:
+        raise ValueError("q must be (num_seqs, n_q, H_q, D)")
+    num_seqs, n_q, hq, d = q.shape
+    if n_q == 0 or num_seqs == 0:
+        return torch.empty_like(q)
+    steps = torch.arange(n_q, device=q.device, dtype=seq_lens.dtype)
+    lens = (seq_lens.reshape(-1, 1) - (n_q - 1) + steps).clamp_(min=0).reshape(-1).contiguous()
+    table = block_table.repeat_interleave(n_q, dim=0)
+    out = split_k_paged_decode(q.reshape(num_seqs * n_q, hq, d), kv_cache, table, lens,
+                               centroids_k, centroids_v, rotation, num_kv_heads, head_dim,
+                               block_size, sm_scale=sm_scale, num_splits=num_splits)
+    return out.reshape(num_seqs, n_q, hq, d)
+
+
 def split_k_paged_decode_qjl(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k,
                              centroids_v, rotation, qjl_matrix, num_kv_heads, head_dim, block_size,
                              sm_scale=None, out=None, num_splits=0, workspace=None):

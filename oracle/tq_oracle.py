@@ -513,6 +513,41 @@ def split_k_paged_decode(q, kv_cache, block_table, seq_lens, centroids_k, centro
     return torch.matmul(o_rot.float(), rotation).to(q.dtype)
 
 
+def paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
+                       num_kv_heads, head_dim, block_size, sm_scale=None):
+    """The last n_q tokens of every sequence attend causally over the paged cache.
+
+    q (num_seqs, n_q, Hq, D); seq_lens counts the n_q new tokens.  What the reference's
+    decompress-all path computes for a step of more than one token
+    (src/flashquant/vllm/impl.py:477-509 feeding flash_attn_varlen_func(causal=True), whose
+    mask is aligned at the END of the keys): de-quantise the sequence in rotated space, query
+    i sees keys 0 .. L - n_q + i, softmax in fp32, with the roundings of the single-token path
+    (src/flashquant/kernels/paged_decode.py:112-128).  A query without visible keys gives zeros.
+    """
+    num_seqs, n_q, hq, d = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    g = hq // num_kv_heads
+    q_rot = torch.matmul(q.float(), rotation.T).to(q.dtype)
+    o_rot = torch.zeros_like(q_rot)
+    for i in range(num_seqs):
+        n = int(seq_lens[i])
+        if n == 0:
+            continue
+        k, v = gather_paged(kv_cache, block_table[i], n, num_kv_heads, head_dim, block_size,
+                            centroids_k, centroids_v)          # (Hkv, L, D)
+        k = k.repeat_interleave(g, dim=0)
+        v = v.repeat_interleave(g, dim=0)
+        qs = q_rot[i].float().permute(1, 0, 2)                   # (Hq, n_q, D)
+        s = torch.bmm(qs, k.transpose(-2, -1)) * sm_scale       # (Hq, n_q, L)
+        visible = torch.arange(n).unsqueeze(0) <= (n - n_q + torch.arange(n_q)).unsqueeze(1)
+        s = s.masked_fill(~visible.unsqueeze(0), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        p = torch.where(visible.any(dim=1).reshape(1, n_q, 1), p, torch.zeros_like(p))
+        o_rot[i] = torch.bmm(p, v).permute(1, 0, 2).to(q.dtype)
+    return torch.matmul(o_rot.float(), rotation).to(q.dtype)
+
+
 def split_k_partials(q_rot, k, v, sm_scale, bounds):
     """Per-split (m, l, acc) of one head: the quantities a split-K decode exchanges.
 

@@ -347,3 +347,30 @@ def test_three_launch_form_gives_the_same_answer(consts):
     assert (three[1] == 0).all()
     # both forms round the same rotated query and merge the same partial rows
     assert (one.float() - three.float()).abs().max().item() <= 2.0 ** -6
+
+
+@pytest.mark.parametrize("n_q,lens", [(4, [0, 1, 3, 4, 5, 64, 301, 1000]), (2, [17, 2048]),
+                                      (1, [9, 300])])
+def test_multi_token_steps_vs_oracle(consts, n_q, lens):
+    # the last n_q tokens of every sequence in one call: query i sees keys 0 .. L - n_q + i;
+    # sequences shorter than n_q have queries without any key (zeros)
+    w = W.decode_workload(seq_lens=lens, num_q_heads=32, num_kv_heads=8, cfg=70 + n_q)
+    cache = fill_cache_cpu(w, consts)
+    args = (consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"])
+    g = torch.Generator().manual_seed(900 + n_q)
+    q = torch.randn(w.num_seqs, n_q, 32, 128, generator=g).to(torch.bfloat16)
+    out = fq.split_k_paged_decode_multi(q.to(DEV), cache.to(DEV), w.block_table.to(DEV),
+                                        w.seq_lens.to(DEV), *args, 8, 128, 16)
+    ref = O.paged_decode_multi(q, cache, w.block_table, w.seq_lens, *args, 8, 128, 16)
+    assert out.shape == q.shape
+    attention_close(out.cpu(), ref)
+    # a query without visible keys: exact zeros
+    for i, n in enumerate(lens):
+        for t in range(n_q):
+            if n - n_q + t < 0:
+                assert bool((out[i, t] == 0).all())
+    # the last query of each sequence is the single-token call (another partition of the keys
+    # over the teams, so equal up to the order of the sums)
+    one = fq.split_k_paged_decode(q[:, -1].contiguous().to(DEV), cache.to(DEV),
+                                  w.block_table.to(DEV), w.seq_lens.to(DEV), *args, 8, 128, 16)
+    attention_close(out[:, -1].cpu(), one.cpu())

@@ -188,3 +188,21 @@ def test_compress_and_store_rows(consts):
         assert torch.equal(flat[s, 128:136].view(torch.float32), kn[i].reshape(-1))
     untouched = [s for s in range(32) if s not in (3, 31, 0, 17, 16)]
     assert (flat[untouched] == 0).all()
+
+
+def test_multi_token_decode_equals_single_token_calls(consts):
+    # the last n_q tokens of a sequence, masked at the end of the keys, are n_q single-token
+    # decodes at lengths L - n_q + 1 .. L (pins the mask alignment of the multi-token oracle to
+    # the single-token one, which is pinned to the reference's outputs above)
+    z, a = _decode_case(consts)
+    n_q = 3
+    q = torch.randn(a["seq_lens"].numel(), n_q, int(z["h_q"]), int(z["d"]),
+                    generator=torch.Generator().manual_seed(12)).to(torch.bfloat16)
+    multi = O.paged_decode_multi(q, **a)
+    for t in range(n_q):
+        lens = (a["seq_lens"] - (n_q - 1) + t).clamp(min=0)
+        one = O.split_k_paged_decode(q[:, t].contiguous(), **{**a, "seq_lens": lens})
+        err = (one.float() - multi[:, t].float()).abs()
+        tol = one.float().abs().amax(dim=-1, keepdim=True) * 2.0 ** -7 + 1e-3
+        assert bool((err <= tol).all())
+        assert bool((multi[:, t][lens == 0] == 0).all())
