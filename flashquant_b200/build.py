@@ -28,7 +28,8 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE]
 
 KERNEL_SOURCES = ["capi.cu", "compress.cu", "decompress.cu", "paged_decode.cu", "prefill.cu",
-                  "rotate.cu", "host_step.cu", "cache_update.cu"]
+                  "rotate.cu", "host_step.cu", "cache_update.cu",
+                  "decode_multi.cu"]
 
 
 def _sources():

@@ -425,22 +425,34 @@ def split_k_paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, 
     The reference takes its fused decode only for a step of exactly one token
     (src/flashquant/vllm/impl.py:441) and otherwise de-quantises the whole cache for a causal
     varlen attention (impl.py:265-336, 477-509).  Here every (sequence, token) pair is a row of
-    the paged decode kernel with its own length and the sequence's block-table row, so the
-    call is one launch of the same kernel and nothing is de-quantised to memory.
+    the paged decode kernel with its own length and the sequence's block-table row
+    (``fq_split_k_paged_decode_multi``: a small kernel writes those rows, then the decode
+    launch), so nothing is de-quantised to memory.
     """
     N.require_cuda(q, kv_cache, block_table, seq_lens)
     if q.dim() != 4:
         raise ValueError("q must be (num_seqs, n_q, H_q, D)")
     num_seqs, n_q, hq, d = q.shape
+    out = torch.empty_like(q)
     if n_q == 0 or num_seqs == 0:
-        return torch.empty_like(q)
-    steps = torch.arange(n_q, device=q.device, dtype=seq_lens.dtype)
-    lens = (seq_lens.reshape(-1, 1) - (n_q - 1) + steps).clamp_(min=0).reshape(-1).contiguous()
-    table = block_table.repeat_interleave(n_q, dim=0)
-    out = split_k_paged_decode(q.reshape(num_seqs * n_q, hq, d), kv_cache, table, lens,
-                               centroids_k, centroids_v, rotation, num_kv_heads, head_dim,
-                               block_size, sm_scale=sm_scale, num_splits=num_splits)
-    return out.reshape(num_seqs, n_q, hq, d)
+        return out
+    dev, _, _, _, q3, block_table, seq_lens, ck, cv, rot = _decode_args(
+        q.reshape(num_seqs * n_q, hq, d), kv_cache, block_table, seq_lens, centroids_k,
+        centroids_v, rotation, num_kv_heads, head_dim, block_size)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    lib = N.load()
+    workspace = decode_workspace(dev, num_seqs * n_q, hq, num_kv_heads, d, num_splits)
+    max_blocks = block_table.shape[1]
+    need = lib.fq_split_k_paged_decode_multi_scratch_bytes(num_seqs, n_q, max_blocks)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    N.check(lib.fq_split_k_paged_decode_multi(
+        N.ptr(q3), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
+        block_table.stride(0), max_blocks, N.ptr(seq_lens), N.ptr(ck), ck.numel(), N.ptr(cv),
+        cv.numel(), N.ptr(rot), num_seqs, n_q, hq, num_kv_heads, d, block_size, kv_cache.shape[0],
+        float(sm_scale), N.ptr(out), int(num_splits), N.ptr(workspace), workspace.numel(),
+        N.ptr(scratch), scratch.numel(), N.stream_ptr(dev)))
+    return out
 
 
 def split_k_paged_decode_qjl(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k,

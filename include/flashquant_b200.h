@@ -241,6 +241,33 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
                             void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
 /*
+ * Decode steps of n_q tokens per sequence (speculative or chunked decode).
+ * The reference takes its fused decode only for a step of exactly one token
+ * (src/flashquant/vllm/impl.py:441) and otherwise de-quantises the whole cache for a causal
+ * varlen attention (impl.py:265-336, 477-509).  Here the last n_q tokens of every sequence,
+ * already appended to the cache and counted in seq_lens, attend in one decode launch: query i
+ * of a sequence sees keys 0 .. seq_len - n_q + i (a query without a visible key gives zeros).
+ *   q, out        (num_seqs, n_q, num_q_heads, head_dim)
+ *   block_table   (num_seqs, block_table_stride) int32, max_blocks (<= stride) columns used
+ *   scratch       caller-owned, 16-byte aligned, fq_split_k_paged_decode_multi_scratch_bytes(...)
+ *                 bytes: the per-(sequence, token) lengths and block-table rows a small kernel
+ *                 writes before the decode
+ * num_seqs * n_q <= 2048; workspace as for fq_split_k_paged_decode with num_seqs * n_q rows;
+ * everything else as fq_split_k_paged_decode.
+ */
+size_t fq_split_k_paged_decode_multi_scratch_bytes(int num_seqs, int n_q, int max_blocks);
+int fq_split_k_paged_decode_multi(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                                  const int32_t* block_table, int64_t block_table_stride,
+                                  int max_blocks, const int32_t* seq_lens,
+                                  const float* centroids_k, int n_centroids_k,
+                                  const float* centroids_v, int n_centroids_v,
+                                  const float* rotation, int num_seqs, int n_q, int num_q_heads,
+                                  int num_kv_heads, int head_dim, int block_size,
+                                  int64_t num_blocks, float sm_scale, void* out, int num_splits,
+                                  void* workspace, size_t workspace_bytes, void* scratch,
+                                  size_t scratch_bytes, fq_stream_t stream);
+
+/*
  * fq_split_k_paged_decode normally is one cooperative launch with one CTA per SM.  On a GPU
  * that cannot hold such a launch (shared with other contexts, partitioned) the call falls
  * back by itself to three ordinary launches (q rotation, streaming, merge) with the same
