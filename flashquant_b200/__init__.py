@@ -8,6 +8,7 @@ from .kernels import (  # noqa: F401
     HostDecodeStep,
     fused_tq_attention,
     fused_tq_attention_kv,
+    pack_2bit,
     paged_decode_partials,
     split_k_merge,
     split_k_paged_decode,
@@ -20,6 +21,7 @@ from .kernels import (  # noqa: F401
     tq4_decompress,
     tq4_decompress_original,
     tq_prod_quantize,
+    unpack_2bit,
 )
 from .cache import (  # noqa: F401
     CompressedBuffer,

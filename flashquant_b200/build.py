@@ -29,7 +29,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE
 
 KERNEL_SOURCES = ["capi.cu", "compress.cu", "decompress.cu", "paged_decode.cu", "prefill.cu",
                   "rotate.cu", "host_step.cu", "cache_update.cu",
-                  "decode_multi.cu"]
+                  "decode_multi.cu", "packing.cu"]
 
 
 def _sources():

@@ -211,6 +211,45 @@ def cache_update(key, value, tables_k, tables_v, k_packed, k_norms, v_packed, v_
         N.ptr(workspace) if need else None, need, N.stream_ptr(dev)))
 
 
+def pack_2bit(indices: torch.Tensor) -> torch.Tensor:
+    """``(..., D)`` codes 0..3 -> ``(..., D/4)`` uint8, four per byte, first code in the top bits
+    (csrc/core/packing.cpp:48-66 of the reference).  Raises on a code above 3, as it does."""
+    N.require_cuda(indices)
+    d = indices.shape[-1]
+    if d % 4 != 0:
+        raise ValueError(f"Last dimension must be divisible by 4 for 2-bit packing, got {d}")
+    if indices.dtype != torch.uint8 and bool(((indices < 0) | (indices > 3)).any()):
+        raise ValueError("indices out of range for 2-bit packing (0..3)")
+    codes = _contig(indices.to(torch.uint8))
+    n = codes.numel()
+    pad = (-n) % 16
+    flat = codes.reshape(-1)
+    if pad:
+        flat = torch.cat([flat, flat.new_zeros(pad)])
+    packed = torch.empty((n + pad) // 4, dtype=torch.uint8, device=codes.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=codes.device)
+    N.check(N.load().fq_pack_2bit(N.ptr(flat), N.ptr(packed), n + pad, N.ptr(bad),
+                                  N.stream_ptr(codes.device)))
+    if int(bad.item()):
+        raise ValueError("indices out of range for 2-bit packing (0..3)")
+    return packed[: n // 4].reshape(*indices.shape[:-1], d // 4)
+
+
+def unpack_2bit(packed: torch.Tensor, dim: int) -> torch.Tensor:
+    """``(..., dim/4)`` uint8 -> ``(..., dim)`` int64 codes (csrc/core/packing.cpp:68-79)."""
+    N.require_cuda(packed)
+    if packed.shape[-1] * 4 != dim:
+        raise ValueError("dim must be four times the packed last dimension")
+    p = _contig(packed).reshape(-1)
+    n = p.numel() * 4
+    pad = (-n) % 16
+    if pad:
+        p = torch.cat([p, p.new_zeros(pad // 4)])
+    codes = torch.empty(n + pad, dtype=torch.uint8, device=p.device)
+    N.check(N.load().fq_unpack_2bit(N.ptr(p), N.ptr(codes), n + pad, N.stream_ptr(p.device)))
+    return codes[:n].reshape(*packed.shape[:-1], dim).long()
+
+
 def tq_prod_quantize(x, rotation, boundaries, centroids, qjl_matrix):
     """Two-stage quantiser on ``(..., D)``: packed codes, norms, packed sign bits, gamma.
 

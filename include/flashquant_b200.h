@@ -100,6 +100,20 @@ int fq_tq_prod_quantize(const void* x, fq_dtype dtype, const float* rotation,
                         float* gamma, int64_t n_vectors, int head_dim, fq_stream_t stream);
 
 /*
+ * 2-bit code packing, four codes per byte: byte = c0<<6 | c1<<4 | c2<<2 | c3.
+ * Replaces pack_2bit / unpack_2bit of the reference's C++ core (csrc/core/packing.cpp:48-79;
+ * the Python-side restatement its tests use is tests/conftest.py:245-265).
+ *   codes          n_codes bytes, one code (0..3) per byte, 16-byte aligned
+ *   packed         n_codes/4 bytes, 4-byte aligned
+ *   out_of_range   optional device word: bit 0 is OR-ed in when a code above 3 was seen (the
+ *                  reference validates before packing; its low two bits are packed here)
+ * n_codes must be a multiple of 16.
+ */
+int fq_pack_2bit(const uint8_t* codes, uint8_t* packed, int64_t n_codes, uint32_t* out_of_range,
+                 fq_stream_t stream);
+int fq_unpack_2bit(const uint8_t* packed, uint8_t* codes, int64_t n_codes, fq_stream_t stream);
+
+/*
  * TQ4 decompress (rotated space): out[v][2j] = c[byte>>4]*n, out[v][2j+1] = c[byte&15]*n.
  * Replaces tq4_decompress_cuda (csrc/cuda/decompress.cuh:40-48) as reached from
  * flashquant.kernels.decompress.tq4_decompress (src/flashquant/kernels/decompress.py:75-77);

@@ -128,6 +128,25 @@ def nibble_unpack(packed: torch.Tensor) -> torch.Tensor:
     return torch.stack([hi, lo], dim=-1).flatten(-2)
 
 
+def pack_2bit(idx: torch.Tensor) -> torch.Tensor:
+    """Four 2-bit codes per byte, first code in the top two bits.
+
+    csrc/core/packing.cpp:48-66 (v0<<6 | v1<<4 | v2<<2 | v3), as restated by the reference's
+    tests (tests/conftest.py:245-257)."""
+    d = idx.shape[-1]
+    if d % 4 != 0:
+        raise ValueError(f"Last dim must be divisible by 4, got {d}")
+    f = idx.reshape(-1, d).to(torch.uint8)
+    packed = (f[:, 0::4] << 6) | (f[:, 1::4] << 4) | (f[:, 2::4] << 2) | f[:, 3::4]
+    return packed.reshape(*idx.shape[:-1], d // 4)
+
+
+def unpack_2bit(packed: torch.Tensor, dim: int) -> torch.Tensor:
+    """csrc/core/packing.cpp:68-79; tests/conftest.py:259-265."""
+    parts = [((packed >> s) & 0x03).long() for s in (6, 4, 2, 0)]
+    return torch.stack(parts, dim=-1).flatten(-2)
+
+
 def sign_bits_pack(signs: torch.Tensor) -> torch.Tensor:
     """QJL signs (+-1 floats, (..., m)) -> (..., m/8) uint8.
 

@@ -316,3 +316,26 @@ def test_prod_quantize_bulk_head_dim_64(C):
     check_norms(g2, gamma, rtol=2e-6)
     bad = O.sign_bits_unpack(bits.cpu()) != signs
     assert bad.float().mean().item() <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(32, 128), (8, 256), (3, 20), (1, 4), (5, 7, 64)])
+def test_two_bit_packing_equals_oracle(shape):
+    idx = torch.randint(0, 4, shape, generator=torch.Generator().manual_seed(sum(shape)))
+    packed = fq.pack_2bit(idx.to(DEV))
+    assert packed.dtype == torch.uint8 and packed.shape == (*shape[:-1], shape[-1] // 4)
+    assert torch.equal(packed.cpu(), O.pack_2bit(idx))
+    back = fq.unpack_2bit(packed, shape[-1])
+    assert back.dtype == torch.int64 and torch.equal(back.cpu(), idx)
+    assert torch.equal(fq.unpack_2bit(O.pack_2bit(idx).to(DEV), shape[-1]).cpu(), idx)
+
+
+def test_two_bit_packing_errors():
+    with pytest.raises(ValueError, match="divisible by 4"):
+        fq.pack_2bit(torch.zeros(2, 6, dtype=torch.long, device=DEV))
+    with pytest.raises(ValueError, match="out of range"):
+        fq.pack_2bit(torch.tensor([[4, 0, 0, 0]], device=DEV))
+    with pytest.raises(ValueError, match="out of range"):
+        fq.pack_2bit(torch.tensor([[0, 0, 7, 0]], dtype=torch.uint8, device=DEV))
+    with pytest.raises(ValueError, match="out of range"):
+        fq.pack_2bit(torch.tensor([[-1, 0, 0, 0]], device=DEV))
+    assert fq.pack_2bit(torch.zeros(0, 8, dtype=torch.long, device=DEV)).shape == (0, 2)

@@ -206,3 +206,18 @@ def test_multi_token_decode_equals_single_token_calls(consts):
         tol = one.float().abs().amax(dim=-1, keepdim=True) * 2.0 ** -7 + 1e-3
         assert bool((err <= tol).all())
         assert bool((multi[:, t][lens == 0] == 0).all())
+
+
+def test_two_bit_packing_known_answers():
+    # byte = c0<<6 | c1<<4 | c2<<2 | c3 (the reference's C++ core and the restatement in its tests)
+    assert O.pack_2bit(torch.tensor([[0, 1, 2, 3]])).item() == 0x1B
+    assert O.pack_2bit(torch.tensor([[3, 3, 3, 3]])).item() == 0xFF
+    assert O.pack_2bit(torch.tensor([[1, 0, 0, 0, 0, 0, 0, 2]])).tolist() == [[0x40, 0x02]]
+    idx = torch.randint(0, 4, (32, 128), generator=torch.Generator().manual_seed(4))
+    packed = O.pack_2bit(idx)
+    assert packed.shape == (32, 32) and packed.dtype == torch.uint8
+    assert torch.equal(O.unpack_2bit(packed, 128), idx)
+    assert O.pack_2bit(torch.zeros(8, 256, dtype=torch.long)).shape[-1] == 64
+    import pytest
+    with pytest.raises(ValueError):
+        O.pack_2bit(torch.zeros(2, 6, dtype=torch.long))
