@@ -68,6 +68,7 @@ struct DecodeArgs {
   const uint8_t* kv_cache;
   const int32_t* block_table;
   int64_t bt_stride;
+  int max_pages;  // columns of a block-table row that may be read
   const int32_t* seq_lens;
   const float* cent_k;
   int nck;
@@ -99,8 +100,12 @@ struct DecodeArgs {
 // ------------------------------------------------------------------------------------
 // page-count prefix of the batch, built by one warp into shared memory
 // ------------------------------------------------------------------------------------
+// A sequence never owns more pages than its block-table row has columns: a length beyond
+// max_pages * block_size is cut there (the reference's CPU path would raise an IndexError on the
+// table) and, where `status` is given, reported as FQ_DEV_BAD_BLOCK_INDEX.
 __device__ __forceinline__ void build_page_prefix(const int32_t* __restrict__ seq_lens, int n,
-                                                  int block_size, int* prefix, int lane) {
+                                                  int block_size, int max_pages, uint32_t* status,
+                                                  int* prefix, int lane) {
   int carry = 0;
   if (lane == 0) prefix[0] = 0;
   for (int base = 0; base < n; base += 32) {
@@ -108,6 +113,10 @@ __device__ __forceinline__ void build_page_prefix(const int32_t* __restrict__ se
     int len = i < n ? seq_lens[i] : 0;
     if (len < 0) len = 0;
     int v = (len + block_size - 1) / block_size;
+    if (v > max_pages) {
+      v = max_pages;
+      if (status) atomicOr(status, FQ_DEV_BAD_BLOCK_INDEX);
+    }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int up = __shfl_up_sync(0xffffffffu, v, o);
@@ -606,7 +615,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     if (tid == 66) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rot_w));
   }
   if (warp == 1) reinterpret_cast<__half*>(smem + p.off_cent)[lane] = __float2half_rn(cent_val);
-  if (warp == 0) build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
+  if (warp == 0)
+    build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, p.max_pages,
+                      blockIdx.x == 0 ? p.status : nullptr, prefix, lane);
   __syncthreads();
 
   // ---- phase a: one rotated query tile per warp of the grid (before the warps change their
@@ -692,7 +703,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
         phys = 0;
       }
-      int n_valid = p.seq_lens[seq] - pg * p.block_size;
+      int n_valid = p.seq_lens[seq] - pg * p.block_size;  // pg < max_pages: see the prefix
       if (n_valid > p.block_size) n_valid = p.block_size;
       const int flags =
           (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
@@ -1147,6 +1158,7 @@ struct MergeArgs {
   int num_workers; // kFromSlots: teams of the streaming kernel (grid size x teams per CTA)
   const int32_t* seq_lens;
   int block_size;
+  int max_pages;   // kFromSlots: the same cut of over-long sequences as the streaming kernel
   const float* rotation;
   void* out;
   float* row_out;
@@ -1183,7 +1195,7 @@ __global__ void __launch_bounds__(kMergeHeads* D) merge_rotate_kernel(MergeArgs 
   // ---- which rows belong to this sequence ----------------------------------------------
   if constexpr (kFromSlots) {
     if (warp == 0) {
-      build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, prefix, lane);
+      build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, p.max_pages, nullptr, prefix, lane);
       if (lane == 0) {
         const int64_t total = prefix[p.num_seqs];
         const int64_t active = total < p.num_workers ? total : int64_t(p.num_workers);
@@ -1567,6 +1579,7 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.kv_cache = kv_cache;
   a.block_table = block_table;
   a.bt_stride = block_table_stride;
+  a.max_pages = int(block_table_stride < 0 ? 0 : (block_table_stride > (1 << 30) ? (1 << 30) : block_table_stride));
   a.seq_lens = seq_lens;
   a.cent_k = centroids_k; a.nck = nck;
   a.cent_v = centroids_v; a.ncv = ncv;
@@ -1599,7 +1612,7 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
 
 static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int hkv, int head_dim,
                                  int num_splits, int ctas, const int32_t* seq_lens,
-                                 int block_size) {
+                                 int block_size, int64_t block_table_stride) {
   const int workers = ctas * (kCW / hkv);
   const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, workers);
   MergeArgs m{};
@@ -1608,6 +1621,7 @@ static MergeArgs slot_merge_args(void* workspace, int num_seqs, int hq, int hkv,
   m.num_workers = workers;
   m.seq_lens = seq_lens;
   m.block_size = block_size;
+  m.max_pages = int(block_table_stride < 0 ? 0 : (block_table_stride > (1 << 30) ? (1 << 30) : block_table_stride));
   m.num_seqs = num_seqs;
   m.hq = hq;
   return m;
@@ -1658,7 +1672,7 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
                     workspace, workspace_bytes, ctas, stream);
   if (rc != FQ_OK) return rc;
   MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                num_splits, ctas, seq_lens, block_size);
+                                num_splits, ctas, seq_lens, block_size, block_table_stride);
   m.rotation = rotation;
   m.out = out;
   return launch_merge<true, true>(m, head_dim, dtype, stream);
@@ -1713,7 +1727,7 @@ static int partials_common(const void* q, fq_dtype dtype, const uint8_t* kv_cach
                         sm_scale, num_splits, workspace, workspace_bytes, ctas, stream);
   if (rc != FQ_OK) return rc;
   MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                num_splits, ctas, seq_lens, block_size);
+                                num_splits, ctas, seq_lens, block_size, block_table_stride);
   m.row_out = partials;
   return launch_merge<true, false>(m, head_dim, FQ_F16, stream);
 }
