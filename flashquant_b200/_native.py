@@ -73,6 +73,11 @@ SIGNATURES = {
     "fq_fused_tq_attention_kv": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i,
                                       _i, _i, _i64, _i, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_set_single_launch": (None, [_i]),
+    "fq_paged_decode_set_fast_path": (None, [_i]),
+    "fq_paged_decode_set_weight_split": (None, [_i]),
+    "fq_paged_decode_test_expect_extra_segments": (None, [_i]),
+    "fq_set_device_wait_limit_ns": (None, [C.c_uint64]),
+    "fq_get_device_wait_limit_ns": (C.c_uint64, []),
     "fq_split_k_paged_decode_qjl": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _p, _i,
                                          _i, _i, _i, _i, _i64, _f, _p, _i, _p, _sz, _p]),
     "fq_decode_step_host_staging_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),

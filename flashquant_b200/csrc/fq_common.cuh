@@ -115,10 +115,21 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ------------------------------------------------------------------------------------
-// Shared-memory barriers and bulk copies (PTX).  Every wait is bounded: after
-// `kSpinLimit` failed polls the caller gets `false` and must record an error and leave.
+// Shared-memory barriers and bulk copies (PTX).  Every wait is bounded IN TIME: when the
+// limit (nanoseconds of %globaltimer) has passed since the first failed poll, the caller gets
+// `false` and must record an error and leave.  The limit is a kernel argument set from
+// fq_set_device_wait_limit_ns(); waits that take no argument use the default.
 // ------------------------------------------------------------------------------------
-constexpr uint32_t kSpinLimit = 1u << 24;  // try_wait itself blocks for a while per poll
+constexpr uint64_t kDefaultWaitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
+
+// Limit the launchers pass to their kernels (capi.cu; fq_set_device_wait_limit_ns).
+uint64_t device_wait_limit_ns();
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -166,13 +177,52 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Returns false when the limit ran out.  One poll that succeeds costs no timer read.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          uint64_t limit_ns = kDefaultWaitNs) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
-  return false;
+}
+// The same for a whole warp (all 32 lanes call it): every lane gets the same answer, so the
+// warp can leave a loop together.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  while (true) {
+    const bool ok = mbar_try_wait(bar, parity);
+    const bool late = global_timer_ns() - t0 > limit_ns;
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (__any_sync(0xffffffffu, late)) return false;
+  }
+}
+// Waits until *counter >= target (a counter other CTAs of the launch bump with
+// red_release_add).  Lane 0 polls, every lane gets the same answer.
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p);
+__device__ __forceinline__ bool counter_wait_warp(const uint32_t* counter, uint32_t target,
+                                                  uint64_t limit_ns, int lane) {
+  int state = 0;  // 1 = reached, 2 = gave up
+  uint64_t t0 = 0;
+#pragma unroll 1
+  while (true) {
+    if (lane == 0) {
+      if (ld_acquire_u32(counter) >= target) {
+        state = 1;
+      } else {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > limit_ns) state = 2;
+      }
+    }
+    state = __shfl_sync(0xffffffffu, state, 0);
+    if (state) return state == 1;
+    __nanosleep(64);
+  }
 }
 
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.

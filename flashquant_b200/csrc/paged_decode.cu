@@ -79,6 +79,9 @@ struct DecodeArgs {
   float scale_log2;
   int num_splits;
   int stages;
+  int n_q;             // query tokens per sequence (fast path; hq counts all of their heads)
+  uint64_t wait_ns;    // limit of every wait on another CTA or on a copy
+  uint32_t seg_extra;  // test hook: the merge expects this many segment arrivals too many
   float* slots;  // (num_seqs * S + workers, Hq, D+4), workers = gridDim.x * teams
   uint32_t* status;
   uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent;
@@ -368,11 +371,13 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       if (n > kMaxParts) n = kMaxParts;
       if (tid == 0) {
         *n_parts_s = n;
-        const uint32_t expected = uint32_t(n) * uint32_t(p.hkv);
-        uint32_t spins = 0;
+        const uint32_t expected = uint32_t(n) * uint32_t(p.hkv) + p.seg_extra;
+        uint64_t t0 = 0;
         while (ld_acquire_u32(p.seg_count + seq) < expected) {
           __nanosleep(32);
-          if (++spins > (kSpinLimit >> 2)) {
+          const uint64_t now = global_timer_ns();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > p.wait_ns) {
             atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
             break;
           }
@@ -447,7 +452,7 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
     }
     compute_sync();
     if (!pi_ready) {
-      if (!mbar_wait(pi_bar, 0)) {  // only if the copy were lost
+      if (!mbar_wait(pi_bar, 0, p.wait_ns)) {  // only if the copy were lost
         if (tid == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
         return;
       }
@@ -711,7 +716,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
           make_int4(int(phys), n_valid | (flags << 8), seq, seq * p.num_splits + s + int(wk));
     };
     bool first_round = true;
-    uint32_t idle = 0;
+    uint64_t idle_since = 0;
 #pragma unroll 1
     while (true) {
       // ---- descriptors of run pages [base, base + 32) of team T: x = physical page, y = valid
@@ -789,10 +794,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       const bool done = issue_idx >= my_run && q_owed < 0;
       if (__all_sync(0xffffffffu, done)) break;
       if (__any_sync(0xffffffffu, progress)) {
-        idle = 0;
+        idle_since = 0;
       } else {
         __nanosleep(32);
-        if (++idle > kSpinLimit) {
+        // lane 0 keeps the time, every lane leaves with it
+        bool late = false;
+        if (lane == 0) {
+          const uint64_t now = global_timer_ns();
+          if (idle_since == 0) idle_since = now;
+          late = now - idle_since > p.wait_ns;
+        }
+        if (__shfl_sync(0xffffffffu, int(late), 0)) {
           if (lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
           break;
         }
@@ -858,7 +870,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 #pragma unroll 1
   for (int it = 0; it < n_run; ++it) {
     // ---- wait for the page ----------------------------------------------------------------
-    if (!page_ready && !mbar_wait(full_bar + stage, fphase)) {
+    if (!page_ready && !mbar_wait(full_bar + stage, fphase, p.wait_ns)) {
       timed_out = true;
       break;
     }
@@ -880,7 +892,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 #pragma unroll
         for (int c = 0; c < 4; ++c) oacc[j][c] = 0.f;
       if (flags & kQNew) {
-        if (!mbar_wait(qfull_bar, qcnt & 1)) {
+        if (!mbar_wait(qfull_bar, qcnt & 1, p.wait_ns)) {
           timed_out = true;
           break;
         }
@@ -1140,6 +1152,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
 
   if constexpr (FUSE != 0) fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
 }
+
+}  // namespace fq
+#include "paged_decode_fast.cuh"
+namespace fq {
 
 // ------------------------------------------------------------------------------------
 // 3. merge of partial rows + rounding + out = o_rot Pi
@@ -1436,6 +1452,101 @@ static int launch_stream_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStre
   return check_launch("paged decode kernel launch");
 }
 
+// ---- fast path (head_dim 128, 8 KV heads, pages of 16 tokens): padded rows, one producer warp
+// per team ---------------------------------------------------------------------------------
+static std::atomic<int> g_fast_path{1};      // 0: always the generic kernel
+// test hook: the merge phase of the single launch expects this many segment arrivals more than
+// will ever come, so that its bounded wait can be seen to give up
+static std::atomic<int> g_test_extra_segments{0};
+static std::atomic<int> g_weight_split{0};   // 1: two fp16 terms per softmax weight
+
+static bool fast_path_fits(int hq_rows, int n_q, int hkv, int head_dim, int block_size,
+                           bool two_stage) {
+  if (!g_fast_path.load(std::memory_order_relaxed) || two_stage) return false;
+  if (head_dim != kFD || hkv != kFH || block_size != kFBS || n_q < 1 || hq_rows % n_q) return false;
+  const int hq = hq_rows / n_q;
+  return hq % hkv == 0 && (hq / hkv) * n_q <= 8;
+}
+
+static SmemPlan plan_smem_fast(int num_seqs, int hq_rows) {
+  SmemPlan s{};
+  auto up16 = [](uint32_t v) { return (v + 15u) & ~15u; };
+  const uint32_t q_all = kFTeams * up16(uint32_t(hq_rows) * kFD * 2);
+  const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
+  const uint32_t fixed = kLutBytes + q_all + prefix + kFTeams * 16 + 96 + 64;
+  const uint32_t budget = 227 * 1024 - 512;
+  int stages = 0;
+  if (budget > fixed) stages = int((budget - fixed) / (kFTeams * (kFStage + 16)));
+  if (stages > kMaxStages) stages = kMaxStages;
+  s.stages = stages;
+  s.off_ring = kLutBytes;
+  s.off_q = s.off_ring + kFTeams * uint32_t(stages < 0 ? 0 : stages) * kFStage;
+  s.off_prefix = s.off_q + q_all;
+  s.off_desc = s.off_prefix + prefix;  // no descriptor ring: headers travel with the stages
+  s.off_bar = s.off_desc;
+  s.off_cent = up16(s.off_bar + kFTeams * (2 * uint32_t(stages) + 2) * 8 + 8);  // + merge barrier
+  s.total = s.off_cent + 64;
+  return s;
+}
+
+template <bool KPRMT, int FUSE, bool PSPLIT>
+static int launch_fast_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
+  auto kern = paged_decode_fast_kernel<KPRMT, FUSE, PSPLIT>;
+  static thread_local int set_dev = -1;
+  static thread_local size_t set_bytes = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (set_dev != dev || set_bytes < sp.total) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sp.total));
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "paged decode: shared memory opt-in of %u bytes refused: %s",
+                  sp.total, cudaGetErrorString(e));
+    set_dev = dev;
+    set_bytes = sp.total;
+  }
+  a.stages = sp.stages;
+  a.off_ring = sp.off_ring; a.off_q = sp.off_q;
+  a.off_prefix = sp.off_prefix; a.off_desc = sp.off_desc; a.off_bar = sp.off_bar;
+  a.off_cent = sp.off_cent;
+  if constexpr (FUSE == 0) {
+    kern<<<ctas, kDecodeThreads, sp.total, stream>>>(a);
+  } else {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = sp.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorLaunchOutOfResources) {
+      cudaGetLastError();
+      fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs refused: %s", ctas,
+           cudaGetErrorString(e));
+      return kCoopRefused;
+    }
+    if (e != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "paged decode: cooperative launch of %d CTAs failed: %s", ctas,
+                  cudaGetErrorString(e));
+  }
+  return check_launch("paged decode kernel launch");
+}
+
+template <int FUSE>
+static int launch_fast(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
+  const bool kprmt = a.nck <= 8;
+  const bool split = g_weight_split.load(std::memory_order_relaxed) != 0;
+  if (kprmt)
+    return split ? launch_fast_t<true, FUSE, true>(a, sp, ctas, stream)
+                 : launch_fast_t<true, FUSE, false>(a, sp, ctas, stream);
+  return split ? launch_fast_t<false, FUSE, true>(a, sp, ctas, stream)
+               : launch_fast_t<false, FUSE, false>(a, sp, ctas, stream);
+}
+
 template <int FUSE>
 static int launch_stream(DecodeArgs& a, const SmemPlan& sp, int ctas, int head_dim,
                          cudaStream_t stream) {
@@ -1550,13 +1661,20 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                         int hq, int hkv, int head_dim, int block_size, int64_t num_blocks,
                         float sm_scale, int num_splits, void* workspace, size_t workspace_bytes,
                         int ctas, cudaStream_t stream, void* fused_out = nullptr,
-                        const uint8_t* kq_cache = nullptr, const float* qjl = nullptr) {
+                        const uint8_t* kq_cache = nullptr, const float* qjl = nullptr,
+                        int n_q = 1) {
+  // `hq` counts the query rows of a sequence: n_q tokens x heads (n_q > 1: fast path only)
   FQ_REQUIRE(workspace && aligned(workspace, 256), FQ_ERR_WORKSPACE,
              "paged decode: workspace is null or not 256-byte aligned");
   const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv));
   FQ_REQUIRE(workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
              "paged decode: workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
-  const SmemPlan sp = plan_smem(num_seqs, hq, hkv, head_dim, block_size, kq_cache != nullptr);
+  const bool fast = fast_path_fits(hq, n_q, hkv, head_dim, block_size, kq_cache != nullptr);
+  FQ_REQUIRE(fast || n_q == 1, FQ_ERR_UNSUPPORTED,
+             "paged decode: %d tokens per sequence in one pass need head_dim 128, 8 KV heads, "
+             "pages of 16 tokens and at most 8 (token, head) pairs per KV head", n_q);
+  const SmemPlan sp = fast ? plan_smem_fast(num_seqs, hq)
+                           : plan_smem(num_seqs, hq, hkv, head_dim, block_size, kq_cache != nullptr);
   FQ_REQUIRE(sp.stages >= 2, FQ_ERR_UNSUPPORTED,
              "paged decode: a page of %d tokens x %d heads does not fit the shared-memory ring",
              block_size, hkv);
@@ -1589,7 +1707,11 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.num_splits = num_splits;
   a.slots = reinterpret_cast<float*>(ws + w.slots_off);
   a.status = reinterpret_cast<uint32_t*>(ws);
-  if (!fused_out) return launch_stream<0>(a, sp, ctas, head_dim, stream);
+  a.n_q = n_q;
+  a.wait_ns = device_wait_limit_ns();
+  a.seg_extra = uint32_t(g_test_extra_segments.load(std::memory_order_relaxed));
+  if (!fused_out)
+    return fast ? launch_fast<0>(a, sp, ctas, stream) : launch_stream<0>(a, sp, ctas, head_dim, stream);
   a.q_src = q;
   a.rotation = rotation;
   a.out = fused_out;
@@ -1606,6 +1728,8 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
     return dtype == FQ_BF16 ? launch_stream<3>(a, sp, ctas, head_dim, stream)
                             : launch_stream<4>(a, sp, ctas, head_dim, stream);
   }
+  if (fast)
+    return dtype == FQ_BF16 ? launch_fast<1>(a, sp, ctas, stream) : launch_fast<2>(a, sp, ctas, stream);
   return dtype == FQ_BF16 ? launch_stream<1>(a, sp, ctas, head_dim, stream)
                           : launch_stream<2>(a, sp, ctas, head_dim, stream);
 }
@@ -1680,6 +1804,18 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
 
 extern "C" void fq_paged_decode_set_single_launch(int enabled) {
   g_single_launch.store(enabled ? 1 : 0, std::memory_order_relaxed);
+}
+
+extern "C" void fq_paged_decode_set_fast_path(int enabled) {
+  g_fast_path.store(enabled ? 1 : 0, std::memory_order_relaxed);
+}
+
+extern "C" void fq_paged_decode_set_weight_split(int enabled) {
+  g_weight_split.store(enabled ? 1 : 0, std::memory_order_relaxed);
+}
+
+extern "C" void fq_paged_decode_test_expect_extra_segments(int n) {
+  g_test_extra_segments.store(n < 0 ? 0 : n, std::memory_order_relaxed);
 }
 
 extern "C" int fq_split_k_paged_decode_qjl(
@@ -1904,3 +2040,11 @@ extern "C" int fq_split_k_paged_decode_static(
                       num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
                       scratch, kStaticScratchBytes, ctas, stream, out);
 }
+
+#ifdef FQ_PROF
+extern "C" void* fq_fast_prof_ptr() {
+  void* p = nullptr;
+  cudaGetSymbolAddress(&p, fq::g_fast_prof);
+  return p;
+}
+#endif

@@ -291,6 +291,37 @@ int fq_split_k_paged_decode_multi(const void* q, fq_dtype dtype, const uint8_t* 
 void fq_paged_decode_set_single_launch(int enabled);
 
 /*
+ * Process-wide switches of the paged decode.  (No counterpart in the reference.)
+ *
+ * fq_paged_decode_set_fast_path(0) routes every call through the generic streaming kernel;
+ * by default a cache of head_dim 128, 8 KV heads and pages of 16 tokens takes a kernel
+ * specialised for that layout (same results up to the order of the fp32 sums).
+ *
+ * fq_paged_decode_set_weight_split(1) makes the specialised kernel carry every softmax
+ * weight as two fp16 terms into the value product (twice the tensor-core work of that
+ * product, weights exact to ~2^-22 instead of 2^-12); off by default.
+ */
+void fq_paged_decode_set_fast_path(int enabled);
+void fq_paged_decode_set_weight_split(int enabled);
+
+/*
+ * Every wait inside a kernel - on a shared-memory barrier, on a counter another CTA of the
+ * launch bumps - gives up after this many nanoseconds of the GPU's global timer, ORs
+ * FQ_DEV_WAIT_TIMEOUT into the status word and lets the kernel return; nothing spins for
+ * ever.  Default 200 ms; the value is read when a call is launched.  (No counterpart in the
+ * reference, whose kernels have no such waits.)
+ */
+void fq_set_device_wait_limit_ns(uint64_t nanoseconds);
+uint64_t fq_get_device_wait_limit_ns(void);
+
+/*
+ * Test hook: the merge phase of the single-launch decode waits for `n` more segment arrivals
+ * than its sequence will ever produce, so that a test can watch the bounded wait give up
+ * (status FQ_DEV_WAIT_TIMEOUT, the call still returns).  0 restores normal operation.
+ */
+void fq_paged_decode_test_expect_extra_segments(int n);
+
+/*
  * fq_split_k_paged_decode with the two-stage estimator in the logits:
  *   logit = sm_scale * ( |k| <q_rot, c[code]> + gamma * sqrt(pi/2)/m * <S q, signs> )
  * i.e. TurboQuantProd.estimate_inner_product (src/flashquant/core/quantizer.py:349-370,
