@@ -1472,8 +1472,9 @@ static SmemPlan plan_smem_fast(int num_seqs, int hq_rows) {
   SmemPlan s{};
   auto up16 = [](uint32_t v) { return (v + 15u) & ~15u; };
   const uint32_t q_all = kFTeams * up16(uint32_t(hq_rows) * kFD * 2);
-  const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
-  const uint32_t fixed = kLutBytes + q_all + prefix + kFTeams * 16 + 96 + 64;
+  const uint32_t prefix = up16(uint32_t(2 * num_seqs + 1) * 4);  // page prefix, then ranks
+  const uint32_t desc = kFTeams * kFDescRing * 16;
+  const uint32_t fixed = kLutBytes + q_all + prefix + desc + kFTeams * 16 + 96 + 64;
   const uint32_t budget = 227 * 1024 - 512;
   int stages = 0;
   if (budget > fixed) stages = int((budget - fixed) / (kFTeams * (kFStage + 16)));
@@ -1482,8 +1483,8 @@ static SmemPlan plan_smem_fast(int num_seqs, int hq_rows) {
   s.off_ring = kLutBytes;
   s.off_q = s.off_ring + kFTeams * uint32_t(stages < 0 ? 0 : stages) * kFStage;
   s.off_prefix = s.off_q + q_all;
-  s.off_desc = s.off_prefix + prefix;  // no descriptor ring: headers travel with the stages
-  s.off_bar = s.off_desc;
+  s.off_desc = s.off_prefix + prefix;
+  s.off_bar = s.off_desc + desc;
   s.off_cent = up16(s.off_bar + kFTeams * (2 * uint32_t(stages) + 2) * 8 + 8);  // + merge barrier
   s.total = s.off_cent + 64;
   return s;

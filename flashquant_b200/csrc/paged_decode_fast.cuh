@@ -15,9 +15,11 @@
 //   * Every stride is a compile-time constant, loads take 32-bit shared addresses with
 //     immediate offsets, a full page takes a path without length masks, and the running
 //     maximum is a large negative number instead of -inf, so no select guards the exponent.
-//   * One producer warp per team (its lanes 0-7 copy two rows each) blocks on the stage
-//     barriers instead of polling; the page descriptor (valid tokens, segment flags, partial
-//     row) travels in a 16-byte header of the stage.
+//   * Two producer warps per team (even / odd pages; eight lanes copy two rows each) block on
+//     the stage barriers instead of polling; page descriptors (valid tokens, segment flags,
+//     partial row, physical page) are produced 32 at a time, one lane per page.
+//   * The tile loop is software-pipelined by one page: the raw codes of the next tile travel
+//     from shared memory to registers under the softmax and value product of this one.
 //   * The eight columns of the 16x8 products are (token, head) pairs: with 4 query heads per
 //     KV head a step of two tokens per sequence reads every page once.
 #pragma once
@@ -29,8 +31,8 @@ constexpr int kFH = 8;                         // KV heads
 constexpr int kFBS = 16;                       // tokens per page
 constexpr int kFRowG = kFH * (kFD + 8);        // 1088: token row in the cache
 constexpr int kFPair = 2 * kFRowG + 48;        // 2224: pitch of a pair of rows in shared memory
-constexpr int kFHdr = 16;                      // descriptor in front of the rows
-constexpr int kFStage = kFHdr + kFBS / 2 * kFPair;  // 17 808
+constexpr int kFStage = kFBS / 2 * kFPair;     // 17 792: a page in shared memory
+constexpr int kFDescRing = 128;                // page descriptors per team (16 bytes each)
 // shared-memory offset of token row r of a page: pairs (2k, 2k+1) keep the cache's pitch
 __host__ __device__ constexpr int fast_row(int r) { return (r >> 1) * kFPair + (r & 1) * kFRowG; }
 constexpr int kFTeams = kCW / kFH;             // 2
@@ -318,7 +320,7 @@ __device__ __forceinline__ int seq_of_page(const int* prefix, int num_seqs, int6
 
 // FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out
 #ifdef FQ_PROF
-__device__ unsigned long long g_fast_prof[192 * 20 * 8];
+__device__ unsigned long long g_fast_prof[192 * 20 * 8 + 192 * 16 * 8];
 #define FQ_T(v) const long long v = clock64()
 #define FQ_ACC(a, t1, t0) a += (t1) - (t0)
 #else
@@ -331,6 +333,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
 #ifdef FQ_PROF
   long long pf_wait = 0, pf_tile = 0, pf_q = 0, pf_end = 0;
   const long long pf_start = clock64();
+  const unsigned long long pf_g0 = global_timer_ns();
+  unsigned long long pf_g1 = 0, pf_g2 = 0, pf_g3 = 0;
 #endif
   using TQ = typename std::conditional<FUSE == 2, __half, __nv_bfloat16>::type;
   constexpr int D = kFD;
@@ -349,6 +353,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
   const int stages = p.stages;
 
   int* prefix = reinterpret_cast<int*>(smem + p.off_prefix);
+  int* rank = prefix + (p.num_seqs + 1);  // rank[s]: sequences before s that own pages
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
   const uint32_t sbase = smem_u32(smem);
 
@@ -389,9 +394,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     if (tid == 66) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rot_w));
   }
   if (warp == 1) reinterpret_cast<__half*>(smem + p.off_cent)[lane] = __float2half_rn(cent_val);
-  if (warp == 0)
+  if (warp == 0) {
     build_page_prefix(p.seq_lens, p.num_seqs, kFBS, p.max_pages,
                       blockIdx.x == 0 ? p.status : nullptr, prefix, lane);
+    int carry = 0;
+    for (int base = 0; base < p.num_seqs; base += 32) {
+      const int i = base + lane;
+      const unsigned owns = __ballot_sync(0xffffffffu, i < p.num_seqs && prefix[i + 1] > prefix[i]);
+      if (i < p.num_seqs) rank[i] = carry + __popc(owns & ((1u << lane) - 1u));
+      carry += __popc(owns);
+    }
+  }
   __syncthreads();
 
   // ---- phase a: one rotated query tile per warp of the grid --------------------------------------
@@ -411,20 +424,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       }
   }
 
+#ifdef FQ_PROF
+  pf_g1 = global_timer_ns();  // set-up and this warp's rotation tiles done
+#endif
   // ---- the flat page list and its cut into runs -----------------------------------------------------
   const int64_t total = prefix[p.num_seqs];
   const int64_t workers = int64_t(gridDim.x) * kFTeams;
   const int64_t active = total < workers ? total : workers;
 
   // ---------------------------------------------------------------------------------------------
-  // Producer warps: warp kCW + T feeds team T.  Per page: wait for the stage, write the
-  // descriptor, then lanes 0-7 copy two token rows each.  Block-table entries are fetched 32
-  // pages at a time (one per lane) and handed round by shuffles.
+  // Producer warps.  Issuing a page costs a warp about a thousand cycles of barrier and copy
+  // instructions one after the other, so every team has two: warp kCW + T takes the even pages
+  // of the team's run, warp kCW + 2 + T the odd ones.  The even warp also describes the pages,
+  // 32 at a time with one lane per page (sequence, valid tokens, segment flags, partial-row
+  // slot, physical page, which query to load), into a ring of descriptors that the compute
+  // warps read, and issues every query copy, in order.  Per page: wait for the stage, arm its
+  // barrier, eight lanes copy two token rows each.
   // ---------------------------------------------------------------------------------------------
   if (warp >= kCW) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
-    const int T = warp - kCW;
-    if (T >= kFTeams) return;
+    const int T = (warp - kCW) & 1;
+    const bool describer = warp < kCW + kFTeams;
     const int64_t wk = int64_t(blockIdx.x) * kFTeams + T;
     if (wk >= active) return;
     const int f0 = int(total * wk / active);
@@ -433,104 +453,126 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     const uint32_t full = sbase + p.off_bar + uint32_t(T) * (2 * stages + 2) * 8;
     const uint32_t empty = full + stages * 8, qfull = empty + stages * 8, qempty = qfull + 8;
     const uint32_t ring = sbase + p.off_ring + uint32_t(T) * stages * kFStage;
-    const uint32_t qbuf = sbase + p.off_q + uint32_t(T) * q_bytes;
+    const uint32_t desc = sbase + p.off_desc + uint32_t(T) * kFDescRing * 16;
     const uint64_t stream_policy = l2_evict_first_policy();  // pages are read once
-    // position of the run's first page; everything about a sequence is fetched when the run
-    // enters it, so that a page costs no global load and no division
-    int seq = seq_of_page(prefix, p.num_seqs, f0);
-    int pg = f0 - prefix[seq];
-    int n_pages = prefix[seq + 1] - prefix[seq];
-    int left = p.seq_lens[seq] - pg * kFBS;  // tokens of the sequence from this page on
-    int pps = (n_pages + p.num_splits - 1) / p.num_splits;
-    int sp = pg / pps;                        // split of the current page
-    int split_end = min((sp + 1) * pps, n_pages);
-    int stage = 0, phase = 1, q_issued = 0;
-    int32_t entry = 0;
-    bool bad = false, first = true;
+    int q_issued = 0;
+    int stage = describer ? 0 : 1 % stages;  // stage of run page i = i % stages ...
+    uint32_t parity = (describer || stages > 1) ? 1u : 0u;  // ... used for the (i / stages)-th time
+    int32_t entry = 0;   // physical page of run page (chunk base + own stride * lane)
+    bool bad = false;
+    const int first_seq = seq_of_page(prefix, p.num_seqs, f0);
 #pragma unroll 1
-    for (int i = 0; i < n_run; ++i) {
-      if ((i & 31) == 0) {  // block-table entries of run pages i .. i+31, one per lane
+    for (int i = describer ? 0 : 1; i < n_run; i += 2) {
+      FQ_T(pa);
+      if (describer) {
+        if ((i & 31) == 0) {
+          // ---- run pages i .. i+31: x = valid tokens | flags << 8 | query number << 12,
+          // y = sequence, z = partial-row slot, w = physical page ---------------------------------
+          const int r = i + lane;
+          int4 dsc = make_int4(0, 0, 0, 0);
+          if (r < n_run) {
+            const int f = f0 + r;
+            const int seq = seq_of_page(prefix, p.num_seqs, f);
+            const int pg = f - prefix[seq], n_pages = prefix[seq + 1] - prefix[seq];
+            const int pps = (n_pages + p.num_splits - 1) / p.num_splits;
+            const int sp = pg / pps;
+            const int split_end = min((sp + 1) * pps, n_pages);
+            const bool q_new = r == 0 || pg == 0;
+            const bool seg_first = r == 0 || pg == sp * pps;
+            const bool seg_last = pg + 1 == split_end || r + 1 == n_run;
+            // tokens from this page on, capped (not at 16: a step of several tokens masks up to
+            // n_q - 1 tokens before the end, which may reach into the page before the last)
+            const int left = min(p.seq_lens[seq] - pg * kFBS, 127);
+            // the n-th query this run loads: sequences that own pages, counted from the first
+            const int qn = rank[seq] - rank[first_seq];
+            int phys = p.block_table[int64_t(seq) * p.bt_stride + pg];
+            if (phys < 0 || phys >= p.num_blocks) {
+              phys = 0;
+              bad = true;
+            }
+            const int flags =
+                (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
+            dsc = make_int4(left | (flags << 8) | (qn << 12), seq,
+                            seq * p.num_splits + sp + int(wk), phys);
+          }
+          sts128(desc + uint32_t(r & (kFDescRing - 1)) * 16, dsc.x, dsc.y, dsc.z, dsc.w);
+          __syncwarp();
+        }
+      } else if (((i - 1) & 63) == 0) {
+        // physical pages of this warp's next 32 pages (run pages i, i+2, ...), one per lane
+        const int r = i + 2 * lane;
         entry = 0;
-        if (i + lane < n_run) {
-          const int f = f0 + i + lane;
-          const int s2 = seq_of_page(prefix, p.num_seqs, f);
-          entry = p.block_table[int64_t(s2) * p.bt_stride + (f - prefix[s2])];
+        if (r < n_run) {
+          const int f = f0 + r;
+          const int seq = seq_of_page(prefix, p.num_seqs, f);
+          entry = p.block_table[int64_t(seq) * p.bt_stride + (f - prefix[seq])];
           if (entry < 0 || entry >= p.num_blocks) {
             entry = 0;
             bad = true;
           }
         }
       }
-      const int phys = __shfl_sync(0xffffffffu, entry, i & 31);
-      // descriptor: x = valid tokens | flags << 8, y = sequence, z = partial-row slot
-      const bool q_new = first || pg == 0;
-      const bool seg_first = first || pg == sp * pps;
-      const bool seg_last = (pg + 1 == split_end) || (i + 1 == n_run);
-      const int flags =
-          (seg_first ? kSegStart : 0) | (seg_last ? kSegEnd : 0) | (q_new ? kQNew : 0);
-      first = false;
-      FQ_T(pa);
-      if (i >= stages && !mbar_wait_warp_s(empty + stage * 8, phase, p.wait_ns)) {
+      int phys;
+      uint4 d0 = make_uint4(0u, 0u, 0u, 0u);
+      if (describer) {
+        d0 = lds128<0>(desc + uint32_t(i & (kFDescRing - 1)) * 16);
+        phys = int(d0.w);
+      } else {
+        phys = __shfl_sync(0xffffffffu, entry, ((i - 1) >> 1) & 31);
+      }
+      FQ_T(pb);
+      FQ_ACC(pf_end, pb, pa);
+      if (i >= stages && !mbar_wait_warp_s(empty + stage * 8, parity, p.wait_ns)) {
         if (lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
         break;
       }
-      FQ_T(pb);
-      FQ_ACC(pf_wait, pb, pa);
-      if (q_new) {
-        // the query buffer is single: the team must have taken the previous query into
-        // registers, and (single launch) the rotated rows of this one must be stored
-        bool ok = q_issued == 0 || mbar_wait_warp_s(qempty, (q_issued - 1) & 1, p.wait_ns);
-        if constexpr (FUSE != 0) {
-          if (ok) {
-            ok = counter_wait_warp(p.q_count + seq, uint32_t(q_tiles), p.wait_ns, lane);
-            fence_proxy_async();  // lane 0 acquired the rows and issues the copy
+      FQ_T(pc);
+      FQ_ACC(pf_wait, pc, pb);
+      const uint32_t st = ring + uint32_t(stage) * kFStage;
+      if (lane == 0) mbar_expect_tx_s(full + stage * 8, kFBS * kFRowG);
+      __syncwarp();
+      if (lane < kFBS / 2)
+        bulk_g2s_hint_s(st + lane * kFPair,
+                        p.kv_cache + int64_t(phys) * (kFBS * kFRowG) + lane * (2 * kFRowG),
+                        2 * kFRowG, full + stage * 8, stream_policy);
+      FQ_T(pd);
+      FQ_ACC(pf_tile, pd, pc);
+      if (describer) {
+        // queries of this page and of the other warp's next page, in run order.  The buffer is
+        // single: the team must have taken the previous query into registers, and (single
+        // launch) the rotated rows of this one must be stored
+        bool ok = true;
+#pragma unroll 1
+        for (int k = 0; k < 2 && ok; ++k) {
+          const uint4 dq = k == 0 ? d0
+                                  : (i + 1 < n_run ? lds128<0>(desc + uint32_t((i + 1) & (kFDescRing - 1)) * 16)
+                                                   : make_uint4(0u, 0u, 0u, 0u));
+          if (!((dq.x >> 8) & kQNew)) continue;
+          const int seq = int(dq.y);
+          ok = q_issued == 0 || mbar_wait_warp_s(qempty, (q_issued - 1) & 1, p.wait_ns);
+          if constexpr (FUSE != 0) {
+            if (ok) {
+              ok = counter_wait_warp(p.q_count + seq, uint32_t(q_tiles), p.wait_ns, lane);
+              fence_proxy_async();  // lane 0 acquired the rows and issues the copy
+            }
           }
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_expect_tx_s(qfull, q_bytes);
+            bulk_g2s_s(sbase + p.off_q + uint32_t(T) * q_bytes,
+                       p.q_rot + int64_t(seq) * p.hq * D, q_bytes, qfull);
+          }
+          ++q_issued;
         }
         if (!ok) {
           if (lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
           break;
         }
-        if (lane == 0) {
-          mbar_expect_tx_s(qfull, q_bytes);
-          bulk_g2s_s(qbuf, p.q_rot + int64_t(seq) * p.hq * D, q_bytes, qfull);
-        }
-        ++q_issued;
       }
-      FQ_T(pc);
-      FQ_ACC(pf_q, pc, pb);
-      const uint32_t st = ring + uint32_t(stage) * kFStage;
-      if (lane == 0) {
-        // tokens from this page on, capped (not at 16: a step of several tokens masks up to
-        // n_q - 1 tokens before the end, which may reach into the page before the last)
-        sts128(st, (left > 127 ? 127 : left) | (flags << 8), seq,
-               seq * p.num_splits + sp + int(wk), 0);
-        mbar_expect_tx_s(full + stage * 8, kFBS * kFRowG);
-      }
-      __syncwarp();
-      FQ_T(pd);
-      FQ_ACC(pf_tile, pd, pc);
-      if (lane < kFBS / 2)
-        bulk_g2s_hint_s(st + kFHdr + lane * kFPair,
-                        p.kv_cache + int64_t(phys) * (kFBS * kFRowG) + lane * (2 * kFRowG),
-                        2 * kFRowG, full + stage * 8, stream_policy);
       FQ_T(pe);
-      FQ_ACC(pf_end, pe, pd);
-      if (++stage == stages) { stage = 0; phase ^= 1; }
-      // next page of the flat list
-      left -= kFBS;
-      if (++pg == n_pages) {
-        if (i + 1 < n_run) {
-          do { ++seq; n_pages = prefix[seq + 1] - prefix[seq]; } while (n_pages == 0);
-          pg = 0;
-          left = p.seq_lens[seq];
-          pps = (n_pages + p.num_splits - 1) / p.num_splits;
-          sp = 0;
-          split_end = min(pps, n_pages);
-        }
-      } else if (pg == split_end) {
-        ++sp;
-        split_end = min(split_end + pps, n_pages);
-      }
+      FQ_ACC(pf_q, pe, pd);
+      stage += 2;
+      while (stage >= stages) { stage -= stages; parity ^= 1u; }
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
 #ifdef FQ_PROF
@@ -581,6 +623,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     const uint32_t full = sbase + p.off_bar + uint32_t(team) * (2 * stages + 2) * 8;
     const uint32_t empty = full + stages * 8, qfull = empty + stages * 8, qempty = qfull + 8;
     const uint32_t ring = sbase + p.off_ring + uint32_t(team) * stages * kFStage;
+    const uint32_t desc = sbase + p.off_desc + uint32_t(team) * kFDescRing * 16;
     const uint32_t qbuf = p.off_q + uint32_t(team) * q_bytes;
     // column g of the B operand is (token g / group, head g % group); the partial row of
     // column c belongs to query row col_row(c)
@@ -615,16 +658,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       if (!mbar_wait_warp_s(full, 0, p.wait_ns)) {
         timed_out = true;
       } else {
-        d = lds128<0>(ring);
-        fast_load(w, ring + kFHdr, raw);
+        d = lds128<0>(desc);
+        fast_load(w, ring, raw);
       }
       FQ_T(cb);
       FQ_ACC(pf_wait, cb, ca);
+#ifdef FQ_PROF
+      pf_g2 = global_timer_ns();  // first page in shared memory
+#endif
     }
 #pragma unroll 1
     for (int it = 0; it < n_run && !timed_out; ++it) {
       FQ_T(cb);
-      const int n_valid = d.x & 0xff, flags = d.x >> 8;
+      const int n_valid = d.x & 0xff, flags = (d.x >> 8) & 0xf;
       const int seg_seq = d.y, seg_slot = d.z;
       if (flags & kSegStart) {
         m_run[0] = m_run[1] = kNegBig;
@@ -668,9 +714,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
         if (!mbar_wait_warp_s(full + stage * 8, fphase, p.wait_ns)) {
           timed_out = true;  // this tile is still finished below
         } else {
-          const uint32_t st = ring + uint32_t(stage) * kFStage;
-          d = lds128<0>(st);
-          fast_load(w, st + kFHdr, raw);
+          d = lds128<0>(desc + uint32_t((it + 1) & (kFDescRing - 1)) * 16);
+          fast_load(w, ring + uint32_t(stage) * kFStage, raw);
         }
         FQ_T(cx);
         FQ_ACC(pf_wait, cx, ca);
@@ -724,10 +769,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       o[0] = pf_wait; o[1] = pf_q; o[2] = pf_tile; o[3] = pf_end; o[4] = n_run;
       o[5] = clock64() - pf_start;
     }
+    pf_g3 = global_timer_ns();  // streaming done
 #endif
   }  // phase b
 
   if constexpr (FUSE != 0) fused_merge<D, TQ>(p, smem, prefix, total, active, kFTeams, stages);
+#ifdef FQ_PROF
+  if (lane == 0 && warp < kCW) {
+    unsigned long long* o = g_fast_prof + (192 * 20 + blockIdx.x * 16 + warp) * 8;
+    o[0] = pf_g0; o[1] = pf_g1; o[2] = pf_g2; o[3] = pf_g3; o[4] = global_timer_ns();
+  }
+#endif
 }
 
 }  // namespace fq

@@ -457,15 +457,17 @@ def gather_paged(kv_cache, block_row, seq_len, num_kv_heads, head_dim, block_siz
 
 
 def paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
-                         num_kv_heads, head_dim, block_size, sm_scale=None):
+                         num_kv_heads, head_dim, block_size, sm_scale=None, keep_fp32=False):
     """Rotated-space paged decode (vectorised per sequence).
 
     src/flashquant/kernels/cpu_reference.py:230-368.  A sequence of length 0 yields zeros.
+    ``keep_fp32`` returns the fp32 rows the reference holds just before it casts them to the
+    query's dtype (cpu_reference.py:365-366), for checks of what precedes that rounding.
     """
     num_seqs, hq, d = q_rot.shape
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(head_dim)
-    out = torch.zeros_like(q_rot)
+    out = torch.zeros(q_rot.shape, dtype=torch.float32) if keep_fp32 else torch.zeros_like(q_rot)
     g = hq // num_kv_heads
     for i in range(num_seqs):
         n = int(seq_lens[i])
@@ -478,7 +480,7 @@ def paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, ce
             v = v.repeat_interleave(g, dim=0)
         s = torch.bmm(q_rot[i].float().unsqueeze(1), k.transpose(-2, -1)) * sm_scale
         p = torch.softmax(s, dim=-1)
-        out[i] = torch.bmm(p, v).squeeze(1).to(q_rot.dtype)
+        out[i] = torch.bmm(p, v).squeeze(1).to(out.dtype)
     return out
 
 
@@ -526,10 +528,20 @@ def split_k_paged_decode(q, kv_cache, block_table, seq_lens, centroids_k, centro
     src/flashquant/kernels/paged_decode.py:112-128: q_rot rounded to q.dtype, rotated
     output rounded to q.dtype by the attention, final product rounded to q.dtype.
     """
+    return split_k_paged_decode_stages(q, kv_cache, block_table, seq_lens, centroids_k,
+                                       centroids_v, rotation, num_kv_heads, head_dim,
+                                       block_size, sm_scale)[1]
+
+
+def split_k_paged_decode_stages(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
+                                rotation, num_kv_heads, head_dim, block_size, sm_scale=None):
+    """``split_k_paged_decode`` together with the value it rounds: returns
+    ``(o_rot_fp32, out)`` where ``o_rot_fp32`` is the rotated-space attention output before
+    its cast to the query's dtype and ``out = ((o_rot_fp32.to(dtype)).float() @ Pi).to(dtype)``."""
     q_rot = torch.matmul(q.float(), rotation.T).to(q.dtype)
-    o_rot = paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k,
-                                 centroids_v, num_kv_heads, head_dim, block_size, sm_scale)
-    return torch.matmul(o_rot.float(), rotation).to(q.dtype)
+    o32 = paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
+                               num_kv_heads, head_dim, block_size, sm_scale, keep_fp32=True)
+    return o32, torch.matmul(o32.to(q.dtype).float(), rotation).to(q.dtype)
 
 
 def paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, rotation,
@@ -543,12 +555,19 @@ def paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, centroid
     i sees keys 0 .. L - n_q + i, softmax in fp32, with the roundings of the single-token path
     (src/flashquant/kernels/paged_decode.py:112-128).  A query without visible keys gives zeros.
     """
+    return paged_decode_multi_stages(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
+                                     rotation, num_kv_heads, head_dim, block_size, sm_scale)[1]
+
+
+def paged_decode_multi_stages(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
+                              rotation, num_kv_heads, head_dim, block_size, sm_scale=None):
+    """``paged_decode_multi`` with the fp32 rotated-space rows it rounds: ``(o_rot_fp32, out)``."""
     num_seqs, n_q, hq, d = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(head_dim)
     g = hq // num_kv_heads
     q_rot = torch.matmul(q.float(), rotation.T).to(q.dtype)
-    o_rot = torch.zeros_like(q_rot)
+    o_rot = torch.zeros(q_rot.shape, dtype=torch.float32)
     for i in range(num_seqs):
         n = int(seq_lens[i])
         if n == 0:
@@ -563,8 +582,8 @@ def paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, centroid
         s = s.masked_fill(~visible.unsqueeze(0), float("-inf"))
         p = torch.softmax(s, dim=-1)
         p = torch.where(visible.any(dim=1).reshape(1, n_q, 1), p, torch.zeros_like(p))
-        o_rot[i] = torch.bmm(p, v).permute(1, 0, 2).to(q.dtype)
-    return torch.matmul(o_rot.float(), rotation).to(q.dtype)
+        o_rot[i] = torch.bmm(p, v).permute(1, 0, 2)
+    return o_rot, torch.matmul(o_rot.to(q.dtype).float(), rotation).to(q.dtype)
 
 
 def split_k_partials(q_rot, k, v, sm_scale, bounds):
@@ -611,6 +630,15 @@ def qjl_paged_decode(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k, 
     as <q_rot, c[idx]> * norm, values as in ``paged_decode_rotated``.  ``kq_cache`` is the
     sign/gamma side plane (num_blocks, block_size, H*(m/8+4)).
     """
+    return qjl_paged_decode_stages(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k,
+                                   centroids_v, rotation, qjl, num_kv_heads, head_dim, block_size,
+                                   sm_scale)[1]
+
+
+def qjl_paged_decode_stages(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k,
+                            centroids_v, rotation, qjl, num_kv_heads, head_dim, block_size,
+                            sm_scale=None):
+    """``qjl_paged_decode`` with the fp32 rotated-space rows it rounds: ``(o_rot_fp32, out)``."""
     num_seqs, hq, d = q.shape
     m = qjl.shape[0]
     if sm_scale is None:
@@ -618,7 +646,7 @@ def qjl_paged_decode(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k, 
     g = hq // num_kv_heads
     q_rot = torch.matmul(q.float(), rotation.T).to(q.dtype)
     sq = torch.matmul(q.float(), qjl.T)  # (num_seqs, hq, m)
-    out_rot = torch.zeros_like(q_rot)
+    out_rot = torch.zeros(q_rot.shape, dtype=torch.float32)
     for i in range(num_seqs):
         n = int(seq_lens[i])
         if n == 0:
@@ -640,5 +668,5 @@ def qjl_paged_decode(q, kv_cache, kq_cache, block_table, seq_lens, centroids_k, 
         corr = torch.bmm(sq[i].unsqueeze(1), signs.transpose(-2, -1)).squeeze(1)
         s = (mse + gam * math.sqrt(math.pi / 2.0) / m * corr) * sm_scale
         p = torch.softmax(s, dim=-1)
-        out_rot[i] = torch.bmm(p.unsqueeze(1), v).squeeze(1).to(q.dtype)
-    return torch.matmul(out_rot.float(), rotation).to(q.dtype)
+        out_rot[i] = torch.bmm(p.unsqueeze(1), v).squeeze(1)
+    return out_rot, torch.matmul(out_rot.to(q.dtype).float(), rotation).to(q.dtype)
