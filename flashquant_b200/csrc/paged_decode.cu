@@ -82,6 +82,7 @@ struct DecodeArgs {
   int n_q;             // query tokens per sequence (fast path; hq counts all of their heads)
   uint64_t wait_ns;    // limit of every wait on another CTA or on a copy
   uint32_t seg_extra;  // test hook: the merge expects this many segment arrivals too many
+  uint32_t xflags;     // experiment switches
   float* slots;  // (num_seqs * S + workers, Hq, D+4), workers = gridDim.x * teams
   uint32_t* status;
   uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent;
@@ -141,6 +142,136 @@ __device__ __forceinline__ void compute_sync() {
 // (run c starts at floor(total * c / active)).
 __host__ __device__ __forceinline__ int cta_of_page(int64_t f, int64_t total, int64_t active) {
   return int(((f + 1) * active + total - 1) / total - 1);
+}
+
+// ------------------------------------------------------------------------------------
+// Centroid tables in fp16 with a common scale.
+//
+// The products run on fp16 operands, and fp16(c) is off by up to 2^-12 of c.  The error is
+// the same for every token that carries the code, so it does not average out: with a few
+// dominant key channels it moves the logits by 2^-9 of their size.  But any table beta *
+// fp16(c / beta) is as cheap as fp16(c) - beta folds into the logit scale (keys) and into
+// the output scale (values) - and for a table of 8 or 16 levels some beta in [1, 2) makes
+// every level land several times closer to an fp16 number (the key table of 8 levels:
+// typically 2^-15 instead of 2^-12).  All compute threads of the CTA try kScaleCandidates
+// values of beta for each table, keep the one with the smallest worst relative error (ties:
+// the smaller beta, so every CTA picks the same), and write the scaled fp16 tables.
+//
+// Shared-memory block at `cent` (kCentBytes): [0,64) fp16 tables (K 16, V 16) as read by the
+// table builders; [64,192) the fp32 centroids (written before the call, K then V);
+// [192,200) beta_k, beta_v; [256,512) scratch of the reduction; [512,640) 1/|c| (0 for a level
+// of exactly zero), written with the centroids.
+// ------------------------------------------------------------------------------------
+constexpr int kCentBytes = 640;
+constexpr int kScaleCandidates = 4096;
+// The search costs a few microseconds, so its result is kept in the workspace (bytes 64..255
+// of the status block: the 32 centroids it was made for, beta_k, beta_v, a magic word and the
+// table sizes) and reused by later calls as long as the centroids are bit-identical.
+constexpr uint32_t kScaleMagic = 0x5ca1ab1eu;
+constexpr int kScaleCacheOffset = 64;  // bytes into the workspace
+
+__device__ __forceinline__ unsigned long long shfl_xor_u64(unsigned long long v, int o) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, uint32_t(v), o);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), o);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+
+// Set-up half, by ONE warp before the CTA-wide barrier: lane i brings centroid i (K 0-15,
+// V 16-31; 0 beyond the table) and learns whether the workspace holds the scales of exactly
+// these tables.  Writes the fp32 centroids, their reciprocals, and the hit flag / scales.
+__device__ __forceinline__ void stage_centroids(unsigned char* cent, float cent_val, int nck,
+                                                int ncv, const uint32_t* cache, int lane) {
+  reinterpret_cast<float*>(cent + 64)[lane] = cent_val;
+  reinterpret_cast<float*>(cent + 512)[lane] = cent_val != 0.f ? 1.f / fabsf(cent_val) : 0.f;
+  const uint32_t kept = __ldcg(cache + lane);
+  const uint32_t extra = lane < 5 ? __ldcg(cache + 32 + lane) : 0u;  // beta_k, beta_v, magic, nck, ncv
+  const bool same = kept == __float_as_uint(cent_val);
+  const float as_beta = __uint_as_float(extra);
+  const bool head_ok = lane < 2 ? (as_beta >= 1.f && as_beta < 2.f)
+                     : lane == 2 ? extra == kScaleMagic
+                     : lane == 3 ? extra == uint32_t(nck)
+                     : lane == 4 ? extra == uint32_t(ncv) : true;
+  const bool hit = __all_sync(0xffffffffu, same && head_ok);
+  if (lane < 2) reinterpret_cast<float*>(cent + 192)[lane] = hit ? __uint_as_float(extra) : 0.f;
+  if (lane == 0) reinterpret_cast<uint32_t*>(cent + 200)[0] = hit ? 1u : 0u;
+}
+
+// Called by the kComputeThreads compute threads (tid 0 .. kComputeThreads-1) after the barrier
+// that follows stage_centroids; ends with a barrier of those threads.  `cache` non-null: this
+// CTA records a fresh result in the workspace.
+__device__ __forceinline__ void scale_centroid_tables(unsigned char* cent, int nck, int ncv,
+                                                      int tid, uint32_t* cache) {
+  const float* c32 = reinterpret_cast<const float*>(cent + 64);
+  const float* inv = reinterpret_cast<const float*>(cent + 512);
+  const bool hit = reinterpret_cast<const uint32_t*>(cent + 200)[0] != 0u;
+  unsigned long long* red = reinterpret_cast<unsigned long long*>(cent + 256);  // [2][16]
+  if (!hit) {
+    unsigned long long best[2] = {~0ull, ~0ull};
+    for (int cand = tid; cand < kScaleCandidates; cand += kComputeThreads) {
+      const float beta = 1.f + float(cand) * (1.f / kScaleCandidates);
+      const float rb = 1.f / beta;
+#pragma unroll
+      for (int tbl = 0; tbl < 2; ++tbl) {
+        const int n = tbl ? ncv : nck;
+        float worst = 0.f;
+        for (int i = 0; i < n; ++i) {
+          const float c = c32[16 * tbl + i];
+          const float h = __half2float(__float2half_rn(c * rb));
+          // relative error; a level of exactly zero is exact whatever beta is (its 1/|c| is 0)
+          worst = fmaxf(worst, fabsf(fmaf(h, beta, -c)) * inv[16 * tbl + i]);
+        }
+        const unsigned long long key =
+            (static_cast<unsigned long long>(__float_as_uint(worst)) << 32) | uint32_t(cand);
+        best[tbl] = key < best[tbl] ? key : best[tbl];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int tbl = 0; tbl < 2; ++tbl) {
+        const unsigned long long other = shfl_xor_u64(best[tbl], o);
+        best[tbl] = other < best[tbl] ? other : best[tbl];
+      }
+    }
+    if ((tid & 31) == 0) {
+      red[tid >> 5] = best[0];
+      red[16 + (tid >> 5)] = best[1];
+    }
+  }
+  compute_sync();
+  if (tid < 32) {
+    // lanes 0-15 finish the key table, 16-31 the value table
+    const int tbl = tid >> 4, i = tid & 15;
+    float beta;
+    if (hit) {
+      beta = reinterpret_cast<const float*>(cent + 192)[tbl];
+    } else {
+      unsigned long long b = red[16 * tbl + i];
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        const unsigned long long other = shfl_xor_u64(b, o);
+        b = other < b ? other : b;
+      }
+      beta = 1.f + float(uint32_t(b)) * (1.f / kScaleCandidates);
+    }
+    __syncwarp();
+    const int n = tbl ? ncv : nck;
+    const float c = i < n ? c32[16 * tbl + i] : 0.f;
+    reinterpret_cast<__half*>(cent)[16 * tbl + i] = __float2half_rn(c * (1.f / beta));
+    if (i == 0) reinterpret_cast<float*>(cent + 192)[tbl] = beta;
+    if (!hit && cache) {
+      // the magic word goes last: whoever sees it sees a whole record (a CTA of this launch
+      // that starts late must not take half of one)
+      cache[tid] = __float_as_uint(c32[tid]);
+      if (i == 0) cache[32 + tbl] = __float_as_uint(beta);
+      if (tid == 3) cache[35] = uint32_t(nck);
+      if (tid == 4) cache[36] = uint32_t(ncv);
+      __threadfence();
+      __syncwarp();
+      if (tid == 2) cache[34] = kScaleMagic;
+    }
+  }
+  compute_sync();
 }
 
 // ------------------------------------------------------------------------------------
@@ -619,7 +750,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
     if (tid == 65) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_count));
     if (tid == 66) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rot_w));
   }
-  if (warp == 1) reinterpret_cast<__half*>(smem + p.off_cent)[lane] = __float2half_rn(cent_val);
+  if (warp == 1)
+    stage_centroids(smem + p.off_cent, cent_val, p.nck, p.ncv,
+                    p.status + kScaleCacheOffset / 4, lane);
   if (warp == 0)
     build_page_prefix(p.seq_lens, p.num_seqs, p.block_size, p.max_pages,
                       blockIdx.x == 0 ? p.status : nullptr, prefix, lane);
@@ -818,7 +951,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   const int64_t wk = int64_t(blockIdx.x) * teams + team;
   const int n_run = wk < active ? int(total * (wk + 1) / active - total * wk / active) : 0;
 
-  // ---- look-up table -------------------------------------------------------------------------
+  // ---- scaled fp16 centroid tables, then the look-up table -------------------------------------
+  scale_centroid_tables(smem + p.off_cent, p.nck, p.ncv, tid,
+                        blockIdx.x == 0 ? p.status + kScaleCacheOffset / 4 : nullptr);
+  const float beta_k = reinterpret_cast<const float*>(smem + p.off_cent + 192)[0];
+  const float beta_v = reinterpret_cast<const float*>(smem + p.off_cent + 192)[1];
+  const float k_scale_log2 = p.scale_log2 * beta_k;  // the key table is c / beta_k
   for (int i = tid; i < 256 * 32; i += kComputeThreads) {
     const int e = i >> 5, l = i & 31;
     const uint32_t hi = e >> 4, lo = e & 15;
@@ -1013,7 +1151,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       // cannot overflow
       const float lg_lo = fast_log2(nv_lo), lg_hi = fast_log2(nv_hi);
       const float lv_lo = fmaxf(lg_lo, -40.f), lv_hi = fmaxf(lg_hi, -40.f);
-      const float ks_lo = nk_lo * p.scale_log2, ks_hi = nk_hi * p.scale_log2;
+      const float ks_lo = nk_lo * k_scale_log2, ks_hi = nk_hi * k_scale_log2;
       float s_lo[2], s_hi[2], mx[2];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -1123,7 +1261,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
       }
-      const float unscale = 1.f / float(1 << int(kPScaleLog2));
+      const float unscale = beta_v / float(1 << int(kPScaleLog2));  // the value table is c / beta_v
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int col = 2 * t + c;
@@ -1150,7 +1288,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   if (timed_out && lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
   }  // phase b
 
-  if constexpr (FUSE != 0) fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
+  if constexpr (FUSE != 0) {
+    if (!(p.xflags & 2u)) fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
+  }
 }
 
 }  // namespace fq
@@ -1385,7 +1525,7 @@ static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size, 
   const uint32_t q_all = teams * up16(uint32_t(hq) * d * 2) * (qs ? 2u : 1u);
   const uint32_t prefix = up16(uint32_t(num_seqs + 1) * 4);
   const uint32_t desc = teams * kDescRing * 16;
-  const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16 + 96;
+  const uint32_t fixed = kLutBytes + q_all + prefix + desc + teams * 16 + 96 + kCentBytes;
   const uint32_t budget = 227 * 1024 - 512;
   int stages = 0;
   if (budget > fixed) stages = int((budget - fixed) / (teams * (page_bytes + 16)));
@@ -1397,7 +1537,7 @@ static SmemPlan plan_smem(int num_seqs, int hq, int hkv, int d, int block_size, 
   s.off_desc = s.off_prefix + prefix;
   s.off_bar = s.off_desc + desc;
   s.off_cent = up16(s.off_bar + teams * (2 * uint32_t(stages) + 2) * 8 + 8);  // + merge barrier
-  s.total = s.off_cent + 64;  // 32 fp16 centroids
+  s.total = s.off_cent + kCentBytes;
   return s;
 }
 
@@ -1474,7 +1614,7 @@ static SmemPlan plan_smem_fast(int num_seqs, int hq_rows) {
   const uint32_t q_all = kFTeams * up16(uint32_t(hq_rows) * kFD * 2);
   const uint32_t prefix = up16(uint32_t(2 * num_seqs + 1) * 4);  // page prefix, then ranks
   const uint32_t desc = kFTeams * kFDescRing * 16;
-  const uint32_t fixed = kLutBytes + q_all + prefix + desc + kFTeams * 16 + 96 + 64;
+  const uint32_t fixed = kLutBytes + q_all + prefix + desc + kFTeams * 16 + 96 + kCentBytes;
   const uint32_t budget = 227 * 1024 - 512;
   int stages = 0;
   if (budget > fixed) stages = int((budget - fixed) / (kFTeams * (kFStage + 16)));
@@ -1486,7 +1626,7 @@ static SmemPlan plan_smem_fast(int num_seqs, int hq_rows) {
   s.off_desc = s.off_prefix + prefix;
   s.off_bar = s.off_desc + desc;
   s.off_cent = up16(s.off_bar + kFTeams * (2 * uint32_t(stages) + 2) * 8 + 8);  // + merge barrier
-  s.total = s.off_cent + 64;
+  s.total = s.off_cent + kCentBytes;
   return s;
 }
 
@@ -1540,7 +1680,9 @@ static int launch_fast_t(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream
 template <int FUSE>
 static int launch_fast(DecodeArgs& a, const SmemPlan& sp, int ctas, cudaStream_t stream) {
   const bool kprmt = a.nck <= 8;
-  const bool split = g_weight_split.load(std::memory_order_relaxed) != 0;
+  // two-term weights ride in the spare columns of the products: at most 4 columns in use
+  const bool split = g_weight_split.load(std::memory_order_relaxed) != 0 &&
+                     (a.hq / a.hkv) <= 4;
   if (kprmt)
     return split ? launch_fast_t<true, FUSE, true>(a, sp, ctas, stream)
                  : launch_fast_t<true, FUSE, false>(a, sp, ctas, stream);
@@ -1711,6 +1853,7 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.n_q = n_q;
   a.wait_ns = device_wait_limit_ns();
   a.seg_extra = uint32_t(g_test_extra_segments.load(std::memory_order_relaxed));
+  { const char* e = getenv("FQ_XFLAGS"); a.xflags = e ? uint32_t(atoi(e)) : 0u; }
   if (!fused_out)
     return fast ? launch_fast<0>(a, sp, ctas, stream) : launch_stream<0>(a, sp, ctas, head_dim, stream);
   a.q_src = q;
@@ -2032,8 +2175,11 @@ extern "C" int fq_split_k_paged_decode_static(
   if (rc != FQ_OK) return rc;
   // the array keeps what the previous call left: the status word and the counters the CTAs
   // signal each other through must start at zero
+  // (bytes 64..255 keep the scaled-table record of earlier calls)
   const size_t head_bytes = workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, 0).q_rot_off;
-  cudaError_t e = cudaMemsetAsync(scratch, 0, head_bytes, stream);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, kScaleCacheOffset, stream);
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + 256, 0, head_bytes - 256, stream);
   if (e != cudaSuccess)
     return fail(FQ_ERR_CUDA, "clearing the scratch status word: %s", cudaGetErrorString(e));
   return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,

@@ -130,27 +130,19 @@ struct FastWarp {
   uint32_t tab[4];  // 8-entry key table for byte permutes: low bytes (2 words), high bytes
 };
 
-// What a lane reads from a stage for one 16-token tile of its KV head: raw codes and norms.
+// The part of a tile's raw data that is fetched one page ahead: the key codes of rows g and
+// g+8, bytes 16t..16t+15 of the head.  (The value codes and the norms are loaded when the tile
+// starts - the key product that comes first hides their latency - so that only eight
+// registers are live across the loop edge.)
 struct FastRaw {
-  uint4 ka, kb;                   // key codes of rows g and g+8, bytes 16t..16t+15 of the head
-  float nk_lo, nk_hi, nv_lo, nv_hi;  // key / value norms of rows g and g+8
-  uint2 x0, x1, x2, x3;           // value codes of tokens 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7
+  uint4 ka, kb;
 };
 
-// All shared-memory reads of a tile, issued together (ten loads, no bank conflicts).
 __device__ __forceinline__ void fast_load(const FastWarp& w, uint32_t rows, FastRaw& r) {
   constexpr int HI = fast_row(8);  // rows g+8, tokens 2t+8: four pairs further
-  const uint32_t kaddr = rows + w.laneK, naddr = rows + w.laneN, vaddr = rows + w.laneV;
+  const uint32_t kaddr = rows + w.laneK;
   r.ka = lds128<0>(kaddr);
   r.kb = lds128<HI>(kaddr);
-  r.nk_lo = ldsf<0>(naddr);
-  r.nk_hi = ldsf<HI>(naddr);
-  r.nv_lo = ldsf<544>(naddr);
-  r.nv_hi = ldsf<544 + HI>(naddr);
-  r.x0 = lds64<0>(vaddr);
-  r.x1 = lds64<kFRowG>(vaddr);
-  r.x2 = lds64<HI>(vaddr);
-  r.x3 = lds64<HI + kFRowG>(vaddr);
 }
 
 // What the first half of a tile hands to the second.
@@ -164,8 +156,18 @@ struct FastMid {
 // group) and the pairing of the value codes.  After it every register of `r` has been used,
 // so the stage can be given back and `r` refilled for the next tile.
 template <bool KPRMT>
-__device__ __forceinline__ void fast_front(const FastWarp& w, const FastRaw& r,
+__device__ __forceinline__ void fast_front(const FastWarp& w, const FastRaw& r, uint32_t rows,
                                            const uint32_t (&qf)[8][2], FastMid& m) {
+  constexpr int HI = fast_row(8);
+  // value codes of tokens 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7 of the head, and the norms of
+  // rows g and g+8: on their way while the key product runs
+  const uint32_t naddr = rows + w.laneN, vaddr = rows + w.laneV;
+  const uint2 x0 = lds64<0>(vaddr), x1 = lds64<kFRowG>(vaddr);
+  const uint2 x2 = lds64<HI>(vaddr), x3 = lds64<HI + kFRowG>(vaddr);
+  m.nk_lo = ldsf<0>(naddr);
+  m.nk_hi = ldsf<HI>(naddr);
+  m.nv_lo = ldsf<544>(naddr);
+  m.nv_hi = ldsf<544 + HI>(naddr);
   const uint32_t ka[4] = {r.ka.x, r.ka.y, r.ka.z, r.ka.w};
   const uint32_t kb[4] = {r.kb.x, r.kb.y, r.kb.z, r.kb.w};
 #pragma unroll
@@ -202,21 +204,21 @@ __device__ __forceinline__ void fast_front(const FastWarp& w, const FastRaw& r,
   // two tokens are paired into one table index
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const uint32_t c0 = h ? r.x0.y : r.x0.x, c1 = h ? r.x1.y : r.x1.x;
-    const uint32_t c2 = h ? r.x2.y : r.x2.x, c3 = h ? r.x3.y : r.x3.x;
+    const uint32_t c0 = h ? x0.y : x0.x, c1 = h ? x1.y : x1.x;
+    const uint32_t c2 = h ? x2.y : x2.x, c3 = h ? x3.y : x3.x;
     m.ev01[h] = ((c0 >> 4) & 0x0f0f0f0fu) | (c1 & 0xf0f0f0f0u);
     m.od01[h] = (c0 & 0x0f0f0f0fu) | ((c1 << 4) & 0xf0f0f0f0u);
     m.ev23[h] = ((c2 >> 4) & 0x0f0f0f0fu) | (c3 & 0xf0f0f0f0u);
     m.od23[h] = (c2 & 0x0f0f0f0fu) | ((c3 << 4) & 0xf0f0f0f0u);
   }
-  m.nk_lo = r.nk_lo; m.nk_hi = r.nk_hi; m.nv_lo = r.nv_lo; m.nv_hi = r.nv_hi;
 }
 
 // Second half of a tile: online softmax in the accumulator layout, then O^T += V^T P^T.
 // `lim0/lim1`: tokens of the tile that columns 2t / 2t+1 may see (MASKED only).
 template <bool MASKED, bool PSPLIT>
-__device__ __forceinline__ void fast_back(const FastWarp& w, const FastMid& m, int g, int lim0,
-                                          int lim1, float scale_log2, float (&oacc)[8][4],
+__device__ __forceinline__ void fast_back(const FastWarp& w, const FastMid& m, int g,
+                                          bool second_term, int lim0, int lim1,
+                                          float scale_log2, float (&oacc)[8][4],
                                           float (&m_run)[2], float (&l_run)[2]) {
   // log2 of the value norm is folded into the exponent so that the fp16 weights stay in range
   // whatever the norms are (clamped below so that l cannot overflow)
@@ -278,15 +280,21 @@ __device__ __forceinline__ void fast_back(const FastWarp& w, const FastMid& m, i
     l_run[c] += p_lo + p_hi;
   }
   // weights as the B operand of the PV product: transpose (token, column) -> (column, token)
-  const uint32_t h_lo = pack_half2(w_lo[0], w_lo[1]), h_hi = pack_half2(w_hi[0], w_hi[1]);
-  const uint32_t pb0 = movmatrix_trans(h_lo), pb1 = movmatrix_trans(h_hi);
-  [[maybe_unused]] uint32_t pc0 = 0u, pc1 = 0u;
+  uint32_t h_lo = pack_half2(w_lo[0], w_lo[1]), h_hi = pack_half2(w_hi[0], w_hi[1]);
   if constexpr (PSPLIT) {
-    // second fp16 term of every weight: what the rounding to fp16 dropped
+    // Two fp16 terms per weight at no extra product: with at most four (token, head) columns
+    // in use, columns 4-7 carry the same queries as columns 0-3, so lanes t >= 2 hold the
+    // same scores and weights as lanes t - 2; they hand the product what the rounding to fp16
+    // dropped, and their accumulators are added to the others' when the segment ends.
     const float2 f_lo = unpack_half2(h_lo), f_hi = unpack_half2(h_hi);
-    pc0 = movmatrix_trans(pack_half2(w_lo[0] - f_lo.x, w_lo[1] - f_lo.y));
-    pc1 = movmatrix_trans(pack_half2(w_hi[0] - f_hi.x, w_hi[1] - f_hi.y));
+    const uint32_t r_lo = pack_half2(w_lo[0] - f_lo.x, w_lo[1] - f_lo.y);
+    const uint32_t r_hi = pack_half2(w_hi[0] - f_hi.x, w_hi[1] - f_hi.y);
+    if (second_term) {
+      h_lo = r_lo;
+      h_hi = r_hi;
+    }
   }
+  const uint32_t pb0 = movmatrix_trans(h_lo), pb1 = movmatrix_trans(h_hi);
   // ---------- O^T += V^T P^T: rows = value coordinates, columns as above -----------------------
   const uint32_t lutv = w.lut + 128;
 #pragma unroll
@@ -298,7 +306,6 @@ __device__ __forceinline__ void fast_back(const FastWarp& w, const FastMid& m, i
     const uint32_t a2 = lds32<0>(lutv + prmt(m.ev23[h], w.lane4, SEL));     \
     const uint32_t a3 = lds32<0>(lutv + prmt(m.od23[h], w.lane4, SEL));     \
     mma_f16(oacc[4 * h + I], a0, a1, a2, a3, pb0, pb1);                     \
-    if constexpr (PSPLIT) mma_f16(oacc[4 * h + I], a0, a1, a2, a3, pc0, pc1); \
   }
     FQ_FAST_PV(0, 0x5504)
     FQ_FAST_PV(1, 0x5514)
@@ -321,6 +328,8 @@ __device__ __forceinline__ int seq_of_page(const int* prefix, int num_seqs, int6
 // FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out
 #ifdef FQ_PROF
 __device__ unsigned long long g_fast_prof[192 * 20 * 8 + 192 * 16 * 8];
+#endif
+#if defined(FQ_PROF) && FQ_PROF >= 2
 #define FQ_T(v) const long long v = clock64()
 #define FQ_ACC(a, t1, t0) a += (t1) - (t0)
 #else
@@ -341,7 +350,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
   constexpr int ROWF = D + kPartPad;
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x;
-  const int warp = tid >> 5, lane = tid & 31;
+  // the warp index through a shuffle: the compiler then knows that it - and every address,
+  // counter and flag derived from it - is the same in all lanes and keeps those in uniform
+  // registers, which the tile loop needs for its accumulators
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_q = p.n_q;
   const int hq_real = p.hq / n_q;
@@ -393,7 +405,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     if (tid == 65) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_count));
     if (tid == 66) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rot_w));
   }
-  if (warp == 1) reinterpret_cast<__half*>(smem + p.off_cent)[lane] = __float2half_rn(cent_val);
+  if (warp == 1)
+    stage_centroids(smem + p.off_cent, cent_val, p.nck, p.ncv,
+                    p.status + kScaleCacheOffset / 4, lane);
   if (warp == 0) {
     build_page_prefix(p.seq_lens, p.num_seqs, kFBS, p.max_pages,
                       blockIdx.x == 0 ? p.status : nullptr, prefix, lane);
@@ -406,6 +420,28 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     }
   }
   __syncthreads();
+
+  // ---- tables, by the compute warps, while the operands of their rotation tiles and the
+  // first pages (producer warps, further down) are on their way ------------------------------------
+  if (warp < kCW) {
+    // scaled fp16 centroid tables (see scale_centroid_tables), then the look-up table: entry e (a
+    // cache byte) holds, once per lane, the fp16 pair of its two codes
+    scale_centroid_tables(smem + p.off_cent, p.nck, p.ncv, tid,
+                          blockIdx.x == 0 ? p.status + kScaleCacheOffset / 4 : nullptr);
+    for (int i = tid; i < 256 * 32; i += kComputeThreads) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t hi = e >> 4, lo = e & 15;
+      // K entry: byte of one token -> (even coordinate, odd coordinate); the byte-permute path
+      // delivers (odd, even), so with it the table does too
+      // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
+      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
+          KPRMT ? uint32_t(cs[lo]) | (uint32_t(cs[hi]) << 16)
+                : uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
+      *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
+          uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
+    }
+    compute_sync();  // the table is complete
+  }
 
   // ---- phase a: one rotated query tile per warp of the grid --------------------------------------
   if constexpr (FUSE != 0) {
@@ -589,20 +625,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
   const int64_t wk = int64_t(blockIdx.x) * kFTeams + team;
   const int n_run = wk < active ? int(total * (wk + 1) / active - total * wk / active) : 0;
 
-  // look-up table: entry e (a cache byte) holds, once per lane, the fp16 pair of its two codes
-  for (int i = tid; i < 256 * 32; i += kComputeThreads) {
-    const int e = i >> 5, l = i & 31;
-    const uint32_t hi = e >> 4, lo = e & 15;
-    // K entry: byte of one token -> (even coordinate, odd coordinate); the byte-permute path
-    // delivers (odd, even), so with it the table does too
-    // V entry: (code of token 2t+1) << 4 | (code of token 2t) -> (token 2t, token 2t+1)
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + l * 4) =
-        KPRMT ? uint32_t(cs[lo]) | (uint32_t(cs[hi]) << 16)
-              : uint32_t(cs[hi]) | (uint32_t(cs[lo]) << 16);
-    *reinterpret_cast<uint32_t*>(smem + e * kLutStride + 128 + l * 4) =
-        uint32_t(cs[16 + lo]) | (uint32_t(cs[16 + hi]) << 16);
-  }
-  compute_sync();  // the table is complete
+  const float beta_k = reinterpret_cast<const float*>(smem + p.off_cent + 192)[0];
+  const float beta_v = reinterpret_cast<const float*>(smem + p.off_cent + 192)[1];
+  const float k_scale_log2 = p.scale_log2 * beta_k;  // the key table is c / beta_k
 
   if (n_run > 0) {  // ---- phase b ----------------------------------------------------------------
     FastWarp w;
@@ -627,14 +652,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     const uint32_t qbuf = p.off_q + uint32_t(team) * q_bytes;
     // column g of the B operand is (token g / group, head g % group); the partial row of
     // column c belongs to query row col_row(c)
-    const int my_tok = g / group, my_head = g - my_tok * group;
-    const bool col_ok = g < ncols;
+    // (with two-term weights columns 4-7 repeat columns 0-3: see fast_back)
+    const int my_col = PSPLIT ? (g & 3) : g;
+    const int my_tok = my_col / group, my_head = my_col - my_tok * group;
+    const bool col_ok = my_col < ncols;
     const uint32_t q_lane =
         qbuf + uint32_t(col_ok ? my_tok * hq_real + head * group + my_head : 0) * D * 2 + (D / 8) * t * 4;
     // tokens that this lane's two accumulator columns (2t, 2t+1) cannot see at the end of a
     // sequence: query token i of n_q sees keys up to L - n_q + i
-    const int back0 = 2 * t < ncols ? n_q - 1 - (2 * t) / group : 0;
-    const int back1 = 2 * t + 1 < ncols ? n_q - 1 - (2 * t + 1) / group : 0;
+    const int col0 = PSPLIT ? (2 * t) & 3 : 2 * t;  // real column behind accumulator column 2t
+    const int back0 = col0 < ncols ? n_q - 1 - col0 / group : 0;
+    const int back1 = col0 + 1 < ncols ? n_q - 1 - (col0 + 1) / group : 0;
 
     float m_run[2] = {kNegBig, kNegBig};
     float l_run[2] = {0.f, 0.f};
@@ -703,7 +731,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       FQ_T(cc);
       FQ_ACC(pf_q, cc, cb);
       FastMid mid;
-      fast_front<KPRMT>(w, raw, qf, mid);
+      fast_front<KPRMT>(w, raw, ring + uint32_t(stage) * kFStage, qf, mid);
       // every value read from the stage has been used in an instruction above: release it
       __syncwarp();
       if (lane == 0) mbar_arrive_s(empty + stage * 8);
@@ -725,9 +753,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       // even the first query token of the step sees all 16 tokens of the page
       const int lim0 = n_valid - back0, lim1 = n_valid - back1;
       if (n_valid - (n_q - 1) >= kFBS)
-        fast_back<false, PSPLIT>(w, mid, g, 16, 16, p.scale_log2, oacc, m_run, l_run);
+        fast_back<false, PSPLIT>(w, mid, g, t >= 2, 16, 16, k_scale_log2, oacc, m_run, l_run);
       else
-        fast_back<true, PSPLIT>(w, mid, g, lim0, lim1, p.scale_log2, oacc, m_run, l_run);
+        fast_back<true, PSPLIT>(w, mid, g, t >= 2, lim0, lim1, k_scale_log2, oacc, m_run, l_run);
       FQ_T(cd);
       FQ_ACC(pf_tile, cd, cy);
       if (flags & kSegEnd) {
@@ -737,11 +765,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
           l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
           l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
         }
-        const float unscale = 1.f / float(1 << int(kPScaleLog2));
+        const float unscale = beta_v / float(1 << int(kPScaleLog2));  // the value table is c / beta_v
+        if constexpr (PSPLIT) {  // second-term accumulators of lanes t+2 join those of lanes t
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) oacc[j][c] += __shfl_xor_sync(0xffffffffu, oacc[j][c], 2);
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int col = 2 * t + c;
-          if (col >= ncols) continue;
+          if (col >= ncols || (PSPLIT && t >= 2)) continue;
           const int ct = col / group;
           float* row = p.slots + (int64_t(seg_slot) * p.hq + ct * hq_real + head * group + (col - ct * group)) * ROWF;
 #pragma unroll
@@ -762,6 +796,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       FQ_T(ce);
       FQ_ACC(pf_end, ce, cd);
     }
+
     if (timed_out && lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
 #ifdef FQ_PROF
     if (lane == 0) {
@@ -773,7 +808,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
 #endif
   }  // phase b
 
-  if constexpr (FUSE != 0) fused_merge<D, TQ>(p, smem, prefix, total, active, kFTeams, stages);
+  if constexpr (FUSE != 0) {
+    if (!(p.xflags & 2u)) fused_merge<D, TQ>(p, smem, prefix, total, active, kFTeams, stages);
+  }
 #ifdef FQ_PROF
   if (lane == 0 && warp < kCW) {
     unsigned long long* o = g_fast_prof + (192 * 20 + blockIdx.x * 16 + warp) * 8;

@@ -40,26 +40,88 @@ def check_norms(got, ref, rtol=NORM_RTOL):
         f"norm relative error {(err / ref.abs().clamp_min(1e-300)).max().item():.3e}"
 
 
-def attention_close(got, ref, atol=2e-3):
-    """Attention outputs: max-abs 2e-3, or one bf16 unit in the last place of the largest
-    entry of the same output row (|row|max * 2^-7) where that is larger.
+ATTN_ATOL = 2e-3           # north-star bound on attention outputs (max-abs)
+PRE_RTOL = 2.0 ** -10      # agreement of the un-rounded rows, relative to the entry
 
-    The reference rounds twice to bf16 (rotated output, then the product with Pi), so an
-    entry of the final row inherits rounding steps of the row's largest entries.  At the
-    benchmark shapes (thousands of tokens per sequence) every |output| is below 0.25 and
-    the plain 2e-3 bound is the one that applies; short test sequences have outputs of
-    order 1, where the bf16 grid itself is coarser than 2e-3.
+
+def ulp(x, dtype):
+    """Spacing of ``dtype`` (bf16 / fp16) numbers at |x|, element-wise, as fp32."""
+    mant = {torch.bfloat16: 7, torch.float16: 10}[dtype]
+    tiny = {torch.bfloat16: -126, torch.float16: -14}[dtype]
+    e = torch.floor(torch.log2(x.abs().float().clamp_min(2.0 ** tiny)))
+    return torch.pow(2.0, e.clamp_min(tiny) - mant)
+
+
+def pre_rounding_bound(ref32, atol=ATTN_ATOL, rtol=PRE_RTOL):
+    """How far an un-rounded rotated-space row may be from the reference's: max-abs ``atol``
+    and ``rtol`` of the entry's own magnitude.  An entry far below the typical size of its
+    row is a sum that cancels, so its magnitude is floored at the row's rms."""
+    rms = ref32.pow(2).mean(dim=-1, keepdim=True).sqrt()
+    return torch.minimum(torch.full_like(ref32, atol), rtol * torch.maximum(ref32.abs(), rms))
+
+
+def attention_close(got, ref, ref_rot32, rotation, got_rot32=None, atol=ATTN_ATOL,
+                    rtol=PRE_RTOL):
+    """Attention outputs against the reference, following its two roundings.
+
+    The reference computes the rotated-space row in fp32 (``ref_rot32``), rounds it to the
+    model dtype, multiplies by Pi and rounds again.  An implementation that is not
+    bit-identical before the first rounding cannot meet a flat 2e-3 after the second one: a
+    coordinate that sits next to a rounding boundary lands on the other neighbour (one unit
+    in the last place, 0.0156 at |x| = 2 in bf16) and the product with Pi spreads that step
+    over the whole row.  So the check has two parts.
+
+    1. Before the first rounding (``got_rot32``, when the caller has it): every entry within
+       ``pre_rounding_bound`` of the reference's fp32 value: max-abs 2e-3 and 2^-10 of the
+       entry.  This is the accuracy statement proper; no rounding is involved.
+    2. After both roundings, entry k may differ by one unit in the last place OF THAT ENTRY
+       (the last rounding may fall either way) plus sum_j ulp(o_rot_j) |Pi_jk| over exactly
+       those coordinates j whose fp32 value lies within the part-1 bound of a rounding
+       boundary - the only ones a conforming implementation can round the other way.
+
+    Returns a dict of measured figures (max errors, share of entries beyond 2e-3, share of
+    identical entries, share of coordinates that could flip).
     """
+    dtype = ref.dtype
     got, ref = got.float().cpu(), ref.float().cpu()
-    rowmax = ref.abs().amax(dim=-1, keepdim=True)
-    tol = torch.maximum(torch.full_like(ref, atol), rowmax * 2.0 ** -7)
+    ref_rot32, rot = ref_rot32.float().cpu(), rotation.float().cpu()
+    margin = pre_rounding_bound(ref_rot32, atol, rtol)
+    stats = {}
+    if got_rot32 is not None:
+        e1 = (got_rot32.float().cpu() - ref_rot32).abs()
+        bad = e1 > margin
+        stats["pre_max_abs"] = e1.max().item()
+        if bool(bad.any()):
+            i = int(torch.argmax((e1 - margin).flatten()))
+            raise AssertionError(
+                f"un-rounded rows: {int(bad.sum())} of {bad.numel()} entries beyond "
+                f"min({atol}, {rtol:.2e} |entry|); worst error {e1.flatten()[i].item():.3e} at value "
+                f"{ref_rot32.flatten()[i].item():.4f} (bound {margin.flatten()[i].item():.3e})")
+    # coordinates of the rotated row that may round to the other neighbour
+    u = ulp(ref_rot32, dtype)
+    lo = ref_rot32.to(dtype).float()
+    dist_to_midpoint = (u / 2 - (ref_rot32 - lo).abs()).abs()
+    may_flip = (dist_to_midpoint <= margin).float()
+    spread = torch.matmul(may_flip * u, rot.abs())
+    tol = ulp(ref, dtype) + spread + 1e-6 * ref.abs()
     err = (got - ref).abs()
     bad = err > tol
+    stats.update(max_abs=err.max().item(), beyond_atol=(err > atol).float().mean().item(),
+                 identical=(err == 0).float().mean().item(), may_flip=may_flip.mean().item())
     if bool(bad.any()):
         i = int(torch.argmax((err - tol).flatten()))
         idx = [int(v) for v in torch.unravel_index(torch.tensor(i), err.shape)]
         raise AssertionError(
-            f"attention mismatch: {int(bad.sum())} of {bad.numel()} entries beyond tolerance; "
-            f"worst at {idx}: got {got.flatten()[i].item():.6f} ref {ref.flatten()[i].item():.6f} "
+            f"attention mismatch: {int(bad.sum())} of {bad.numel()} entries beyond one unit in "
+            f"the last place plus the rounding flips the reference's own values allow; worst at "
+            f"{idx}: got {got.flatten()[i].item():.6f} ref {ref.flatten()[i].item():.6f} "
             f"tol {tol.flatten()[i].item():.2e}; max-abs err {err.max().item():.3e}")
-    return err.max().item()
+    return stats
+
+
+def rows_from_partials(parts):
+    """Normalised fp32 rows (acc / l) from (…, D+4) partial rows; empty rows give zeros."""
+    parts = parts.float().cpu()
+    d = parts.shape[-1] - 4
+    l = parts[..., d + 1:d + 2]
+    return torch.where(l > 0, parts[..., :d] / l.clamp_min(1e-30), torch.zeros_like(parts[..., :d]))
