@@ -1598,7 +1598,7 @@ static std::atomic<int> g_fast_path{1};      // 0: always the generic kernel
 // test hook: the merge phase of the single launch expects this many segment arrivals more than
 // will ever come, so that its bounded wait can be seen to give up
 static std::atomic<int> g_test_extra_segments{0};
-static std::atomic<int> g_weight_split{0};   // 1: two fp16 terms per softmax weight
+static std::atomic<int> g_weight_split{1};   // 1: two fp16 terms per softmax weight (default)
 
 static bool fast_path_fits(int hq_rows, int n_q, int hkv, int head_dim, int block_size,
                            bool two_stage) {

@@ -297,9 +297,11 @@ void fq_paged_decode_set_single_launch(int enabled);
  * by default a cache of head_dim 128, 8 KV heads and pages of 16 tokens takes a kernel
  * specialised for that layout (same results up to the order of the fp32 sums).
  *
- * fq_paged_decode_set_weight_split(1) makes the specialised kernel carry every softmax
- * weight as two fp16 terms into the value product (twice the tensor-core work of that
- * product, weights exact to ~2^-22 instead of 2^-12); off by default.
+ * fq_paged_decode_set_weight_split(0) makes the specialised kernel carry every softmax
+ * weight into the value product as one fp16 number (2^-12 relative) instead of two (2^-22).
+ * The second term rides in product columns that are otherwise idle when a KV head serves at
+ * most four (token, head) columns, so it costs a dozen instructions per 16-token tile (about
+ * 3 % of the streaming phase); on by default.
  */
 void fq_paged_decode_set_fast_path(int enabled);
 void fq_paged_decode_set_weight_split(int enabled);

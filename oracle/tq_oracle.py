@@ -363,6 +363,16 @@ def fused_tq_attention(q, k_packed, k_norms, v_packed, v_norms, centroids_k, cen
     group at a time so that the full score tensor never has to exist; results are
     identical because rows of the softmax are independent.
     """
+    return fused_tq_attention_stages(q, k_packed, k_norms, v_packed, v_norms, centroids_k,
+                                     centroids_v, rotation, sm_scale, is_causal, q_chunk,
+                                     rotation_v)[1]
+
+
+def fused_tq_attention_stages(q, k_packed, k_norms, v_packed, v_norms, centroids_k, centroids_v,
+                              rotation, sm_scale=None, is_causal=False, q_chunk: int = 0,
+                              rotation_v=None):
+    """``fused_tq_attention`` with the fp32 rotated-space rows behind it: ``(o_rot_fp32, out)``
+    (the reference never rounds those rows: its attention runs on ``q_rot.float()``)."""
     b, hq, nq, d = q.shape
     hkv, nkv = k_packed.shape[1], k_packed.shape[2]
     if sm_scale is None:
@@ -394,7 +404,8 @@ def fused_tq_attention(q, k_packed, k_norms, v_packed, v_norms, centroids_k, cen
                         torch.softmax(s, dim=-1), vd[bi, h, :kv_hi])
     # flash_attention_reference casts to its q dtype, which is fp32 here
     # (cpu_reference.py:195 passes q_rot.float()), so no rounding before the rotation.
-    return torch.matmul(out_rot.float(), rotation if rotation_v is None else rotation_v).to(q.dtype)
+    out_rot = out_rot.float()
+    return out_rot, torch.matmul(out_rot, rotation if rotation_v is None else rotation_v).to(q.dtype)
 
 
 class CompressedCacheOracle:

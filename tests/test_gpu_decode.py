@@ -1,7 +1,8 @@
 """GPU parity of the split-K paged decode against the CPU oracle and the golden fixture.
 
-Bar: attention outputs within 2e-3 max-abs of the reference's decompress-then-attend path
-(bf16/fp16 outputs; see parity.attention_close for entries of magnitude >= 0.5).
+Bar (parity.attention_close): before the reference's first rounding the rotated-space rows
+agree within 2e-3 max-abs and 2^-10 of the entry; after both roundings an entry may differ by
+one unit in its last place plus the rounding flips the reference's own values allow.
 """
 
 import numpy as np
@@ -13,7 +14,7 @@ from conftest import bf16_from_bits, load_golden
 from flashquant_b200 import kernels as K
 from flashquant_b200 import workloads as W
 from oracle import tq_oracle as O
-from parity import attention_close
+from parity import attention_close, rows_from_partials
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -45,26 +46,49 @@ def run_gpu(w, cache, consts, k_bits=3, v_bits=4, num_splits=0, q=None, sm_scale
 
 
 def run_oracle(w, cache, consts, k_bits=3, v_bits=4, q=None, sm_scale=None):
+    """(fp32 rotated-space rows before the first rounding, final output) of the reference."""
     d = w.head_dim
     q = w.q if q is None else q
-    return O.split_k_paged_decode(
+    return O.split_k_paged_decode_stages(
         q, cache, w.block_table, w.seq_lens, consts[f"centroids_{d}_{k_bits}"],
         consts[f"centroids_{d}_{v_bits}"], consts[f"rotation_{d}_0"], w.num_kv_heads, d,
         w.block_size, sm_scale)
 
 
+def close(out, stages, consts, d=128, **kw):
+    ref32, ref = stages
+    return attention_close(out, ref, ref32, consts[f"rotation_{d}_0"], **kw)
+
+
+def gpu_rows(w, cache, consts, k_bits=3, v_bits=4, num_splits=0, sm_scale=None):
+    """The GPU's rotated-space rows before any rounding (merged partial rows, normalised)."""
+    d = w.head_dim
+    parts = K.paged_decode_partials(
+        w.q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+        consts[f"centroids_{d}_{k_bits}"], consts[f"centroids_{d}_{v_bits}"],
+        consts[f"rotation_{d}_0"], w.num_kv_heads, d, w.block_size, num_splits=num_splits,
+        sm_scale=sm_scale)
+    return rows_from_partials(parts)
+
+
 def test_golden_fixture(consts):
     z = load_golden("paged_decode.npz")
-    args = (T(z["kv_cache"]).to(DEV), T(z["block_table"]).to(DEV), T(z["seq_lens"]).to(DEV),
-            consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"],
-            int(z["h_kv"]), int(z["d"]), int(z["block_size"]))
+    cache, bt, sl = T(z["kv_cache"]), T(z["block_table"]), T(z["seq_lens"])
+    ck, cv, rot = consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"]
+    geo = (int(z["h_kv"]), int(z["d"]), int(z["block_size"]))
+    args = (cache.to(DEV), bt.to(DEV), sl.to(DEV), ck, cv, rot) + geo
+    q = bf16_from_bits(z["q_bf16"])
+    ref32, ref = O.split_k_paged_decode_stages(q, cache, bt, sl, ck, cv, rot, *geo)
+    assert torch.equal(ref.view(torch.int16), bf16_from_bits(z["out_bf16"]).view(torch.int16))
     for splits in (0, 1, 3, 8):
-        out = K.split_k_paged_decode(bf16_from_bits(z["q_bf16"]).to(DEV), *args, num_splits=splits)
-        attention_close(out, bf16_from_bits(z["out_bf16"]))
+        out = K.split_k_paged_decode(q.to(DEV), *args, num_splits=splits)
+        attention_close(out, ref, ref32, rot)
         assert (out[0] == 0).all()  # empty sequence
-    out = K.split_k_paged_decode(T(z["q_f16"]).to(DEV), *args, sm_scale=float(z["sm_scale_f16"]),
-                                 num_splits=2)
-    attention_close(out, T(z["out_f16"]))
+    q16, scale = T(z["q_f16"]), float(z["sm_scale_f16"])
+    ref32, ref = O.split_k_paged_decode_stages(q16, cache, bt, sl, ck, cv, rot, *geo, sm_scale=scale)
+    assert torch.equal(ref.view(torch.int16), T(z["out_f16"]).view(torch.int16))
+    out = K.split_k_paged_decode(q16.to(DEV), *args, sm_scale=scale, num_splits=2)
+    attention_close(out, ref, ref32, rot)
     ws = K.decode_workspace(torch.device(DEV), 6, 8, 2, 128, 0)
     assert K.workspace_status(ws) == 0
 
@@ -77,14 +101,17 @@ def test_ragged_lengths_vs_oracle(consts, hkv, hq):
     ref = run_oracle(w, cache, consts)
     for splits in (1, 4, 8):
         out = run_gpu(w, cache, consts, num_splits=splits)
-        attention_close(out, ref)
+        close(out, ref, consts, got_rot32=gpu_rows(w, cache, consts, num_splits=splits))
 
 
 def test_head_dim_64_and_shared_4bit_tables(consts):
     w = W.decode_workload(seq_lens=[5, 64, 333], num_q_heads=8, num_kv_heads=2, head_dim=64, cfg=12)
     cache = fill_cache_cpu(w, consts, k_bits=4, v_bits=4)
     ref = run_oracle(w, cache, consts, k_bits=4, v_bits=4)
-    attention_close(run_gpu(w, cache, consts, k_bits=4, v_bits=4, num_splits=2), ref)
+    # head_dim 64 takes the generic kernel (one fp16 term per weight) and a 16-level key table
+    # gains less from the common scale than an 8-level one: 2^-9 before the rounding
+    close(run_gpu(w, cache, consts, k_bits=4, v_bits=4, num_splits=2), ref, consts, d=64,
+          got_rot32=gpu_rows(w, cache, consts, k_bits=4, v_bits=4, num_splits=2), rtol=2.0 ** -9)
 
 
 def test_block_size_32_and_fp16_queries(consts):
@@ -92,7 +119,8 @@ def test_block_size_32_and_fp16_queries(consts):
                           cfg=13, dtype=torch.float16)
     cache = fill_cache_cpu(w, consts, dtype=torch.float16)
     ref = run_oracle(w, cache, consts, sm_scale=0.11)
-    attention_close(run_gpu(w, cache, consts, num_splits=3, sm_scale=0.11), ref)
+    close(run_gpu(w, cache, consts, num_splits=3, sm_scale=0.11), ref, consts,
+          got_rot32=gpu_rows(w, cache, consts, num_splits=3, sm_scale=0.11))
 
 
 def test_split_count_and_page_permutation_invariance(consts):
@@ -100,9 +128,13 @@ def test_split_count_and_page_permutation_invariance(consts):
     rounding, nor on where the pages physically live."""
     w = W.decode_workload(num_seqs=4, context=2048, cfg=14)
     cache = fill_cache_cpu(w, consts)
-    base = run_gpu(w, cache, consts, num_splits=1)
-    for splits in (2, 8, 32):
-        attention_close(run_gpu(w, cache, consts, num_splits=splits), base)
+    ref = run_oracle(w, cache, consts)
+    base = gpu_rows(w, cache, consts, num_splits=1)
+    for splits in (1, 2, 8, 32):
+        close(run_gpu(w, cache, consts, num_splits=splits), ref, consts)
+        # another partition of the keys only changes the order of the fp32 sums
+        rows = gpu_rows(w, cache, consts, num_splits=splits)
+        assert (rows - base).abs().max().item() <= 1e-4 * base.abs().max().item()
     # move every page: new table, same logical content
     perm = torch.randperm(w.num_blocks, generator=torch.Generator().manual_seed(77))
     cache2 = torch.empty_like(cache)
@@ -123,7 +155,9 @@ def test_partials_then_merge_equals_fused_call(consts):
     parts = K.paged_decode_partials(*args, num_splits=4)
     assert parts.shape == (4, 32, 132)
     merged = K.split_k_merge(parts, rot, torch.bfloat16)
-    attention_close(merged, fused)
+    ref = run_oracle(w, cache, consts)
+    close(merged, ref, consts, got_rot32=rows_from_partials(parts))
+    close(fused, ref, consts)
     # empty sequence: (0.., -inf, 0)
     tail = parts[3].cpu()
     assert torch.isinf(tail[:, 128]).all() and (tail[:, 129] == 0).all() and (tail[:, :128] == 0).all()
@@ -150,7 +184,9 @@ def test_token_ranges_on_two_groups_merge_like_one(consts):
     second = K.paged_decode_partials(q, cache, rest_table.to(DEV), (w.seq_lens - cut).to(DEV), ck,
                                      cv, rot, 8, 128, 16, num_splits=2)
     merged = K.split_k_merge(torch.stack([first, second]), rot, torch.bfloat16)
-    attention_close(merged, full)
+    ref = run_oracle(w, cache.cpu(), consts)
+    close(merged, ref, consts)
+    close(full, ref, consts)
 
 
 def test_partials_match_oracle_formulas(consts):
@@ -177,7 +213,7 @@ def test_many_short_sequences_and_more_sequences_than_sms(consts):
     cache = fill_cache_cpu(w, consts)
     ref = run_oracle(w, cache, consts)
     for splits in (0, 3):
-        attention_close(run_gpu(w, cache, consts, num_splits=splits), ref)
+        close(run_gpu(w, cache, consts, num_splits=splits), ref, consts)
 
 
 def test_full_size_config1_vs_oracle(consts):
@@ -187,13 +223,14 @@ def test_full_size_config1_vs_oracle(consts):
     cache = fill_cache_cpu(w, consts)
     out = run_gpu(w, cache, consts, num_splits=8)
     ref = run_oracle(w, cache, consts)
-    attention_close(out, ref)
-    # with the outlier channels some heads put nearly all weight on one token, so outputs
-    # reach |3.5| where one bf16 step is 0.0156: entries beyond 2e-3 exist, are all covered
-    # by the one-step-of-the-row-maximum bound checked above, and must stay rare
-    err = (out.float().cpu() - ref.float()).abs()
-    assert (err > 2e-3).float().mean().item() < 5e-3
-    assert (err == 0).float().mean().item() > 0.5
+    stats = close(out, ref, consts, got_rot32=gpu_rows(w, cache, consts, num_splits=8))
+    # with the outlier channels some heads put nearly all weight on one token, so outputs reach
+    # |3.5| where one bf16 step is 0.0156: entries beyond a flat 2e-3 exist (every one of them
+    # within the per-entry bound checked above) and must stay rare
+    print("configs[1] decode parity:", stats)
+    assert stats["pre_max_abs"] < 5e-4
+    assert stats["beyond_atol"] < 1e-3
+    assert stats["identical"] > 0.8
     ws = K.decode_workspace(torch.device(DEV), 32, 32, 8, 128, 8)
     assert K.workspace_status(ws) == 0
 
@@ -234,7 +271,8 @@ def test_long_sequence_spread_over_every_team(consts):
     cache = fill_cache_cpu(w, consts)
     ref = run_oracle(w, cache, consts)
     for splits in (0, 5):
-        attention_close(run_gpu(w, cache, consts, num_splits=splits), ref)
+        close(run_gpu(w, cache, consts, num_splits=splits), ref, consts,
+              got_rot32=gpu_rows(w, cache, consts, num_splits=splits))
 
 
 @pytest.mark.parametrize("with_qjl,pinned", [(False, True), (True, True), (True, False)])
@@ -292,8 +330,9 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
     assert K.workspace_status(step.workspace) == 0
     hout.copy_(ref.cpu())
     # and against the oracle end to end
-    attention_close(hout, O.split_k_paged_decode(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot, hkv,
-                                                 d, bs, None))
+    ref32, ref_out = O.split_k_paged_decode_stages(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot,
+                                                   hkv, d, bs, None)
+    attention_close(hout, ref_out, ref32, rot)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -311,13 +350,14 @@ def test_two_stage_scoring_vs_oracle(consts, dtype):
     plane = torch.zeros(w.num_blocks, bs, hkv * (d // 8 + 4), dtype=torch.uint8, device=DEV)
     K.tq4_compress_append_qjl(k.to(DEV), v.to(DEV), cache, plane, w.slot_mapping.to(DEV), rot, bk,
                               ck, bv, S)
-    ref = O.qjl_paged_decode(w.q, cache.cpu(), plane.cpu(), w.block_table, w.seq_lens, ck, cv, rot,
-                             S, hkv, d, bs)
+    ref32, ref = O.qjl_paged_decode_stages(w.q, cache.cpu(), plane.cpu(), w.block_table,
+                                           w.seq_lens, ck, cv, rot, S, hkv, d, bs)
     for splits in (0, 4):
         out = K.split_k_paged_decode_qjl(w.q.to(DEV), cache, plane, w.block_table.to(DEV),
                                          w.seq_lens.to(DEV), ck, cv, rot, S, hkv, d, bs,
                                          num_splits=splits)
-        attention_close(out, ref)
+        # the generic kernel's sign-bit product runs on fp16(q S^T): 2^-9 before the rounding
+        attention_close(out, ref, ref32, rot, rtol=2.0 ** -9)
         assert (out[1] == 0).all()  # empty sequence
     # the correction matters: the one-stage logits give another answer on the same cache
     plain = K.split_k_paged_decode(w.q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV),
@@ -342,8 +382,8 @@ def test_three_launch_form_gives_the_same_answer(consts):
         assert K.N.load().fq_launch_count() - n0 == 3
     finally:
         K.set_single_launch(True)
-    attention_close(three, ref)
-    attention_close(one, ref)
+    close(three, ref, consts)
+    close(one, ref, consts)
     assert (three[1] == 0).all()
     # both forms round the same rotated query and merge the same partial rows
     assert (one.float() - three.float()).abs().max().item() <= 2.0 ** -6
@@ -361,9 +401,9 @@ def test_multi_token_steps_vs_oracle(consts, n_q, lens):
     q = torch.randn(w.num_seqs, n_q, 32, 128, generator=g).to(torch.bfloat16)
     out = fq.split_k_paged_decode_multi(q.to(DEV), cache.to(DEV), w.block_table.to(DEV),
                                         w.seq_lens.to(DEV), *args, 8, 128, 16)
-    ref = O.paged_decode_multi(q, cache, w.block_table, w.seq_lens, *args, 8, 128, 16)
+    ref32, ref = O.paged_decode_multi_stages(q, cache, w.block_table, w.seq_lens, *args, 8, 128, 16)
     assert out.shape == q.shape
-    attention_close(out.cpu(), ref)
+    attention_close(out.cpu(), ref, ref32, args[2])
     # a query without visible keys: exact zeros
     for i, n in enumerate(lens):
         for t in range(n_q):
@@ -373,4 +413,4 @@ def test_multi_token_steps_vs_oracle(consts, n_q, lens):
     # over the teams, so equal up to the order of the sums)
     one = fq.split_k_paged_decode(q[:, -1].contiguous().to(DEV), cache.to(DEV),
                                   w.block_table.to(DEV), w.seq_lens.to(DEV), *args, 8, 128, 16)
-    attention_close(out[:, -1].cpu(), one.cpu())
+    attention_close(out[:, -1].cpu(), one.cpu(), ref32[:, -1], args[2], slack=2.0)
