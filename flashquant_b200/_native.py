@@ -48,6 +48,7 @@ SIGNATURES = {
     "fq_split_k_paged_decode_static_max_bytes": (_sz, []),
     "fq_split_k_paged_decode_static": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i,
                                             _i, _i, _i, _i64, _f, _p, _i, _p]),
+    "fq_split_k_paged_decode_static_status": (_i, [_p, _p]),
     "fq_paged_decode_partials": (_i, [_p, _i, _p, _p, _i64, _p, _p, _i, _p, _i, _p, _i, _i, _i,
                                       _i, _i, _i64, _f, _i, _p, _p, _sz, _p]),
     "fq_paged_decode_partials_rotated": (_i, [_p, _p, _p, _i64, _p, _p, _i, _p, _i, _i, _i, _i,

@@ -1719,12 +1719,18 @@ static int rotate_q(const void* q, int dtype, const float* rotation, __half* out
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(rotate_q_kernel<D, __half>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(rotate_q_kernel<D, float>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess)
       return fail(FQ_ERR_CUDA, "rotate_q: shared memory opt-in refused: %s",
                   cudaGetErrorString(e));
     set_dev = dev;
   }
-  if (dtype == FQ_BF16)
+  if (dtype == FQ_F32)
+    rotate_q_kernel<D, float><<<grid, 256, smem, stream>>>(static_cast<const float*>(q), rotation,
+                                                           out, rows);
+  else if (dtype == FQ_BF16)
     rotate_q_kernel<D, __nv_bfloat16><<<grid, 256, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(q), rotation, out, rows);
   else
@@ -1759,6 +1765,9 @@ static int launch_merge_t(const MergeArgs& m, cudaStream_t stream) {
 
 template <bool kFromSlots, bool kFinal>
 static int launch_merge(const MergeArgs& m, int head_dim, int dtype, cudaStream_t stream) {
+  if (dtype == FQ_F32)
+    return head_dim == 128 ? launch_merge_t<128, float, kFromSlots, kFinal>(m, stream)
+                           : launch_merge_t<64, float, kFromSlots, kFinal>(m, stream);
   if (head_dim == 128)
     return dtype == FQ_BF16 ? launch_merge_t<128, __nv_bfloat16, kFromSlots, kFinal>(m, stream)
                             : launch_merge_t<128, __half, kFromSlots, kFinal>(m, stream);
@@ -1775,8 +1784,8 @@ static int validate_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cach
              FQ_ERR_INVALID_ARGUMENT, "paged decode: negative size");
   FQ_REQUIRE(q && kv_cache && block_table && seq_lens && centroids_k && centroids_v && rotation,
              FQ_ERR_INVALID_ARGUMENT, "paged decode: null pointer");
-  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
-             "paged decode: q must be fp16 or bf16");
+  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16 || dtype == FQ_F32, FQ_ERR_INVALID_ARGUMENT,
+             "paged decode: unknown dtype");
   FQ_REQUIRE(nck >= 1 && nck <= 16 && ncv >= 1 && ncv <= 16, FQ_ERR_INVALID_ARGUMENT,
              "centroid count outside [1, 16]");
   FQ_REQUIRE(head_dim == 128 || head_dim == 64, FQ_ERR_UNSUPPORTED,
@@ -1909,6 +1918,15 @@ extern "C" size_t fq_paged_decode_workspace_bytes(int num_seqs, int num_q_heads,
       .total;
 }
 
+static int decode_call(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                       const int32_t* block_table, int64_t block_table_stride,
+                       const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
+                       const float* centroids_v, int n_centroids_v, const float* rotation,
+                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                       int block_size, int64_t num_blocks, float sm_scale, void* out,
+                       int num_splits, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
+
 extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                                        const int32_t* block_table, int64_t block_table_stride,
                                        const int32_t* seq_lens, const float* centroids_k,
@@ -1918,6 +1936,23 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
                                        int block_size, int64_t num_blocks, float sm_scale,
                                        void* out, int num_splits, void* workspace,
                                        size_t workspace_bytes, fq_stream_t stream) {
+  return decode_call(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                     n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                     num_kv_heads, head_dim, block_size, num_blocks, sm_scale, out, num_splits,
+                     workspace, workspace_bytes, stream);
+}
+
+// The whole call: one cooperative launch, or three ordinary ones when that is switched off,
+// refused by the driver, or the query is fp32.  Shared by the entry points that differ only
+// in where the workspace comes from.
+static int decode_call(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                       const int32_t* block_table, int64_t block_table_stride,
+                       const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
+                       const float* centroids_v, int n_centroids_v, const float* rotation,
+                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                       int block_size, int64_t num_blocks, float sm_scale, void* out,
+                       int num_splits, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
   int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
                            centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                            num_kv_heads, head_dim, block_size, num_blocks, num_splits);
@@ -1926,7 +1961,9 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
   if (num_seqs == 0) return FQ_OK;
   const int ctas = device_sm_count();
   if (num_splits == 0) num_splits = auto_splits();
-  if (g_single_launch.load(std::memory_order_relaxed)) {
+  // an fp32 query (the reference's CPU-sized cases) takes the three-launch form: its rotated
+  // query is not rounded (it meets the keys as fp16), its output is not rounded either
+  if (g_single_launch.load(std::memory_order_relaxed) && dtype != FQ_F32) {
     rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
                       n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                       num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
@@ -1975,6 +2012,8 @@ extern "C" int fq_split_k_paged_decode_qjl(
   if (rc != FQ_OK) return rc;
   FQ_REQUIRE(out && kq_cache && qjl, FQ_ERR_INVALID_ARGUMENT,
              "paged decode (two-stage): null pointer");
+  FQ_REQUIRE(dtype != FQ_F32, FQ_ERR_UNSUPPORTED,
+             "paged decode (two-stage): q must be fp16 or bf16");
   FQ_REQUIRE(head_dim == 128, FQ_ERR_UNSUPPORTED,
              "paged decode (two-stage): head_dim %d (built for 128)", head_dim);
   FQ_REQUIRE(aligned(kq_cache, 16) && aligned(qjl, 16), FQ_ERR_ALIGNMENT,
@@ -1982,10 +2021,17 @@ extern "C" int fq_split_k_paged_decode_qjl(
   if (num_seqs == 0) return FQ_OK;
   const int ctas = device_sm_count();
   if (num_splits == 0) num_splits = auto_splits();
-  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
-                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
-                      workspace, workspace_bytes, ctas, stream, out, kq_cache, qjl);
+  rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                    num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
+                    workspace, workspace_bytes, ctas, stream, out, kq_cache, qjl);
+  // this entry has no three-launch form: a GPU that cannot hold the cooperative launch
+  // (shared with other contexts, partitioned) cannot run it
+  if (rc == kCoopRefused)
+    return fail(FQ_ERR_UNSUPPORTED,
+                "paged decode (two-stage): the single cooperative launch was refused by the "
+                "driver and this entry point has no other form");
+  return rc;
 }
 
 static int partials_common(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
@@ -2162,9 +2208,9 @@ extern "C" int fq_split_k_paged_decode_static(
   FQ_REQUIRE(out, FQ_ERR_INVALID_ARGUMENT, "paged decode: out is null");
   if (num_seqs == 0) return FQ_OK;
   const int ctas = device_sm_count();
-  if (num_splits == 0) num_splits = auto_splits();
   const size_t need =
-      workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, ctas * (kCW / num_kv_heads))
+      workspace_layout(num_seqs, num_q_heads, head_dim, num_splits == 0 ? auto_splits() : num_splits,
+                       ctas * (kCW / num_kv_heads))
           .total;
   FQ_REQUIRE(need <= kStaticScratchBytes, FQ_ERR_WORKSPACE,
              "fq_split_k_paged_decode_static: this shape needs %zu bytes of scratch, the built-in "
@@ -2174,18 +2220,34 @@ extern "C" int fq_split_k_paged_decode_static(
   rc = static_scratch(&scratch);
   if (rc != FQ_OK) return rc;
   // the array keeps what the previous call left: the status word and the counters the CTAs
-  // signal each other through must start at zero
-  // (bytes 64..255 keep the scaled-table record of earlier calls)
+  // signal each other through must start at zero (bytes 64..255 keep the scaled-table record
+  // of earlier calls)
   const size_t head_bytes = workspace_layout(num_seqs, num_q_heads, head_dim, num_splits, 0).q_rot_off;
   cudaError_t e = cudaMemsetAsync(scratch, 0, kScaleCacheOffset, stream);
   if (e == cudaSuccess)
     e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + 256, 0, head_bytes - 256, stream);
   if (e != cudaSuccess)
     return fail(FQ_ERR_CUDA, "clearing the scratch status word: %s", cudaGetErrorString(e));
-  return decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
-                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
-                      scratch, kStaticScratchBytes, ctas, stream, out);
+  // same call as fq_split_k_paged_decode from here on: single launch, or three launches when
+  // that is switched off or refused
+  return decode_call(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                     n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                     num_kv_heads, head_dim, block_size, num_blocks, sm_scale, out, num_splits,
+                     scratch, kStaticScratchBytes, stream);
+}
+
+// Device status word of the built-in scratch array (FQ_DEV_* bits of the last static call on
+// the current device); synchronises the stream.
+extern "C" int fq_split_k_paged_decode_static_status(uint32_t* status, fq_stream_t stream) {
+  FQ_REQUIRE(status, FQ_ERR_INVALID_ARGUMENT, "static status: null pointer");
+  void* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc != FQ_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(status, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "fq_split_k_paged_decode_static_status: %s", cudaGetErrorString(e));
+  return FQ_OK;
 }
 
 #ifdef FQ_PROF

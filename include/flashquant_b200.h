@@ -222,9 +222,14 @@ int fq_tq4_compress_append_qjl(const void* key, const void* value, fq_dtype dtyp
  * (paged_decode.py:112-128 + src/flashquant/kernels/cpu_reference.py:230-368):
  * q_rot = round(q Pi^T), softmax(sm_scale q_rot K^T) V in rotated space with
  * K = c_k[code] n_k and V = c_v[code] n_v, rounded, then out = round(o_rot Pi).
- *   q, out         (num_seqs, num_q_heads, head_dim), FQ_F16 or FQ_BF16
+ *   q, out         (num_seqs, num_q_heads, head_dim), FQ_F16, FQ_BF16 or FQ_F32 (an fp32
+ *                  query, as in the reference's CPU-sized cases, is not rounded after its
+ *                  rotation and neither is its output; it always takes the three-launch form)
  *   kv_cache       (num_blocks, block_size, num_kv_heads*(head_dim+8)) bytes, 16-byte aligned
- *   block_table    (num_seqs, block_table_stride) int32
+ *   block_table    (num_seqs, block_table_stride) int32; a sequence never reads more than
+ *                  block_table_stride entries of its row: a seq_len beyond
+ *                  block_table_stride * block_size is cut there and FQ_DEV_BAD_BLOCK_INDEX is
+ *                  set (the reference's CPU path would raise an IndexError)
  *   seq_lens       (num_seqs) int32; a length of 0 gives a zero output row
  *   num_splits     partitions of each sequence (1..64); every partition boundary is a
  *                  boundary between partial rows.  The pages of the whole batch are spread
@@ -334,7 +339,9 @@ void fq_paged_decode_test_expect_extra_segments(int n);
  * fq_split_k_paged_decode.
  *   kq_cache   (num_blocks, block_size, num_kv_heads*(head_dim/8+4)) side plane, 16-byte aligned
  *   qjl        (head_dim, head_dim) fp32 row-major S; q S^T is computed in the same launch
- * head_dim 128 only.  Traffic per (token, KV head): 156 bytes instead of 136.
+ * head_dim 128 only, q FQ_F16 or FQ_BF16.  Traffic per (token, KV head): 156 bytes instead of
+ * 136.  This entry exists only as the single cooperative launch: where the driver refuses
+ * that launch it returns FQ_ERR_UNSUPPORTED.
  */
 int fq_split_k_paged_decode_qjl(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                                 const uint8_t* kq_cache, const int32_t* block_table,
@@ -356,7 +363,13 @@ int fq_split_k_paged_decode_qjl(const void* q, fq_dtype dtype, const uint8_t* kv
  *     with FQ_ERR_WORKSPACE (the message names the size needed);
  *   - the first call on each device looks up the array's device address; make that first
  *     call outside any stream capture;
- *   - all calls on a device share the array: calls that overlap on the GPU race on it.
+ *   - all calls on a device share the array: calls that overlap on the GPU race on it;
+ *   - like fq_split_k_paged_decode it is one cooperative launch, or three ordinary launches
+ *     when fq_paged_decode_set_single_launch(0) is in force or the driver refuses the
+ *     cooperative launch;
+ *   - the caller has no pointer to the array, so the device status word (FQ_DEV_* bits) of
+ *     the last call is read with fq_split_k_paged_decode_static_status, which synchronises
+ *     the stream; the next static call clears the word.
  */
 size_t fq_split_k_paged_decode_static_max_bytes(void);
 int fq_split_k_paged_decode_static(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
@@ -367,6 +380,7 @@ int fq_split_k_paged_decode_static(const void* q, fq_dtype dtype, const uint8_t*
                                    int num_q_heads, int num_kv_heads, int head_dim,
                                    int block_size, int64_t num_blocks, float sm_scale, void* out,
                                    int num_splits, fq_stream_t stream);
+int fq_split_k_paged_decode_static_status(uint32_t* status, fq_stream_t stream);
 
 /*
  * The two halves of fq_split_k_paged_decode, for a sequence whose tokens are spread over

@@ -468,7 +468,8 @@ def gather_paged(kv_cache, block_row, seq_len, num_kv_heads, head_dim, block_siz
 
 
 def paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
-                         num_kv_heads, head_dim, block_size, sm_scale=None, keep_fp32=False):
+                         num_kv_heads, head_dim, block_size, sm_scale=None, keep_fp32=False,
+                         per_kv_head=False):
     """Rotated-space paged decode (vectorised per sequence).
 
     src/flashquant/kernels/cpu_reference.py:230-368.  A sequence of length 0 yields zeros.
@@ -486,6 +487,13 @@ def paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, ce
             continue
         k, v = gather_paged(kv_cache, block_table[i], n, num_kv_heads, head_dim, block_size,
                             centroids_k, centroids_v)
+        if per_kv_head:
+            # the same expression one KV head at a time (very long sequences: the repeated
+            # K and V of all query heads would not fit)
+            for h in range(num_kv_heads):
+                s = torch.matmul(q_rot[i, h * g:(h + 1) * g].float(), k[h].T) * sm_scale
+                out[i, h * g:(h + 1) * g] = torch.matmul(torch.softmax(s, dim=-1), v[h]).to(out.dtype)
+            continue
         if g > 1:
             k = k.repeat_interleave(g, dim=0)
             v = v.repeat_interleave(g, dim=0)
@@ -545,13 +553,15 @@ def split_k_paged_decode(q, kv_cache, block_table, seq_lens, centroids_k, centro
 
 
 def split_k_paged_decode_stages(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
-                                rotation, num_kv_heads, head_dim, block_size, sm_scale=None):
+                                rotation, num_kv_heads, head_dim, block_size, sm_scale=None,
+                                per_kv_head=False):
     """``split_k_paged_decode`` together with the value it rounds: returns
     ``(o_rot_fp32, out)`` where ``o_rot_fp32`` is the rotated-space attention output before
     its cast to the query's dtype and ``out = ((o_rot_fp32.to(dtype)).float() @ Pi).to(dtype)``."""
     q_rot = torch.matmul(q.float(), rotation.T).to(q.dtype)
     o32 = paged_decode_rotated(q_rot, kv_cache, block_table, seq_lens, centroids_k, centroids_v,
-                               num_kv_heads, head_dim, block_size, sm_scale, keep_fp32=True)
+                               num_kv_heads, head_dim, block_size, sm_scale, keep_fp32=True,
+                               per_kv_head=per_kv_head)
     return o32, torch.matmul(o32.to(q.dtype).float(), rotation).to(q.dtype)
 
 

@@ -40,6 +40,61 @@ def check_norms(got, ref, rtol=NORM_RTOL):
         f"norm relative error {(err / ref.abs().clamp_min(1e-300)).max().item():.3e}"
 
 
+def _residual(x_cpu, codes, norms, rotation, centroids):
+    """r = x - (c[code] Pi) n in fp64 (src/flashquant/core/quantizer.py:186-193, 290-291), with
+    the fp32 norm the quantiser stored."""
+    d = x_cpu.shape[-1]
+    x = x_cpu.reshape(-1, d).double()
+    xt = (centroids.double()[codes.reshape(-1, d).long()] @ rotation.double()) * \
+        norms.reshape(-1, 1).double()
+    return x - xt
+
+
+def check_gamma(got, ref, x_cpu, codes_got, codes_ref, norms, rotation, centroids):
+    """Residual norms gamma = |x - x~|.  The residual is a difference of nearly equal fp32
+    numbers, so ANY fp32 evaluation - the reference's included - sits up to 1e-6 (relative)
+    from the exact value, and two such evaluations up to 2e-6 from each other.  The check:
+    the CUDA value is as close to the exact (fp64) residual norm as the reference's own value
+    is (both about 1e-6 at worst), 99.8 % of the values agree with the reference to 1e-6 and
+    all of them to 2.2e-6.  Vectors whose codes differ from the reference's (allowed next to
+    a quantiser boundary) have another residual and are left out."""
+    d = x_cpu.shape[-1]
+    same = (codes_got.reshape(-1, d) == codes_ref.reshape(-1, d)).all(dim=-1)
+    truth = _residual(x_cpu, codes_got, norms, rotation, centroids).norm(dim=-1)[same]
+    g = got.cpu().reshape(-1).double()[same]
+    r = ref.reshape(-1).double()[same]
+    scale = truth.clamp_min(1e-30)
+    e_got, e_ref, e_pair = (g - truth).abs() / scale, (r - truth).abs() / scale, (g - r).abs() / scale
+    keep = truth > 0
+    assert bool((g[~keep] == 0).all()), "gamma of a zero residual must be 0"
+    e_got, e_ref, e_pair = e_got[keep], e_ref[keep], e_pair[keep]
+    assert e_got.max().item() <= max(1e-6, 1.25 * e_ref.max().item()), \
+        f"gamma: {e_got.max().item():.3e} from the exact value (the reference: {e_ref.max().item():.3e})"
+    assert (e_pair > NORM_RTOL).double().mean().item() <= 2e-3, \
+        f"gamma: {(e_pair > NORM_RTOL).double().mean().item():.2e} of the values beyond 1e-6 of the reference"
+    assert e_pair.max().item() <= 2.2e-6, f"gamma relative error {e_pair.max().item():.3e}"
+
+
+def check_signs(bits_got, signs_ref, x_cpu, codes_got, codes_ref, norms, rotation, centroids, qjl):
+    """QJL sign bits: equal to the reference's except where the projection is within 1e-6 of
+    zero relative to |r| (the same rule as for the codes), at most 1e-4 of them."""
+    from oracle import tq_oracle as O
+    d = x_cpu.shape[-1]
+    got = O.sign_bits_unpack(bits_got.cpu()).reshape(-1, qjl.shape[0])
+    ref = signs_ref.reshape(-1, qjl.shape[0]).float()
+    same = (codes_got.reshape(-1, d) == codes_ref.reshape(-1, d)).all(dim=-1)
+    diff = (got != ref) & same.unsqueeze(1)
+    frac = diff.float().mean().item()
+    assert frac <= CODE_MISMATCH_BUDGET, f"sign mismatch fraction {frac:.2e}"
+    if bool(diff.any()):
+        r = _residual(x_cpu, codes_got, norms, rotation, centroids)
+        proj = (r @ qjl.double().T).abs() / r.norm(dim=-1, keepdim=True).clamp_min(1e-300)
+        worst = proj[diff].max().item()
+        assert worst < BOUNDARY_WINDOW, \
+            f"a sign differs where |S r|/|r| = {worst:.3e} (not next to zero)"
+    return frac
+
+
 ATTN_ATOL = 2e-3           # north-star bound on attention outputs (max-abs)
 PRE_RTOL = 2.0 ** -10      # agreement of the un-rounded rows, relative to the entry
 PRE_OUTLIERS = 1e-4        # share of entries that may miss it (by at most a factor of two)

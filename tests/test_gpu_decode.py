@@ -414,3 +414,152 @@ def test_multi_token_steps_vs_oracle(consts, n_q, lens):
     one = fq.split_k_paged_decode(q[:, -1].contiguous().to(DEV), cache.to(DEV),
                                   w.block_table.to(DEV), w.seq_lens.to(DEV), *args, 8, 128, 16)
     attention_close(out[:, -1].cpu(), one.cpu(), ref32[:, -1], args[2], slack=2.0)
+
+
+def test_sequence_longer_than_its_block_table_row_is_cut_and_reported(consts):
+    """A seq_len beyond the row's columns would make the page walk read the next row (or past
+    the table): the walk stops at the row's width and the status word says so.  The table is a
+    narrow view inside a wider allocation, so nothing leaves the allocation either way."""
+    w = W.decode_workload(seq_lens=[64, 64], num_q_heads=32, num_kv_heads=8, cfg=23)
+    cache = fill_cache_cpu(w, consts).to(DEV)
+    wide = torch.zeros(2, 16, dtype=torch.int32, device=DEV)
+    wide[:, :4] = w.block_table.to(DEV)
+    narrow = wide[:, :4]                       # stride 16, 4 valid columns
+    lens = torch.tensor([64, 64 + 3 * 16], dtype=torch.int32, device=DEV)   # 7 pages claimed
+    args = (consts["centroids_128_3"], consts["centroids_128_4"], consts["rotation_128_0"], 8, 128, 16)
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device=DEV)
+    lib = K.N.load()
+    out = torch.empty_like(w.q, device=DEV)
+    # the C ABI takes the stride as the row width: hand it the narrow width
+    rot = consts["rotation_128_0"].contiguous().to(DEV)
+    ck, cv = consts["centroids_128_3"].to(DEV), consts["centroids_128_4"].to(DEV)
+    tight = narrow.contiguous()
+    K.N.check(lib.fq_split_k_paged_decode(
+        K.N.ptr(w.q.to(DEV)), K.N.dtype_code(w.q.dtype), K.N.ptr(cache), K.N.ptr(tight), 4,
+        K.N.ptr(lens), K.N.ptr(ck), 8, K.N.ptr(cv), 16, K.N.ptr(rot), 2, 32, 8, 128, 16,
+        cache.shape[0], 1.0 / np.sqrt(128), K.N.ptr(out), 2, K.N.ptr(ws), ws.numel(),
+        K.N.stream_ptr(torch.device(DEV))))
+    assert K.workspace_status(ws) & 1          # FQ_DEV_BAD_BLOCK_INDEX
+    # sequence 0 is untouched by its neighbour's claim; sequence 1 attended over its 4 pages
+    ws.zero_()
+    ok = K.split_k_paged_decode(w.q.to(DEV), cache, tight, w.seq_lens.to(DEV), *args, num_splits=2,
+                                workspace=ws)
+    assert K.workspace_status(ws) == 0
+    assert torch.equal(out.view(torch.int16), ok.view(torch.int16))
+
+
+def test_bounded_wait_gives_up_and_the_call_returns(consts):
+    """Every device-side wait is bounded in time.  The merge phase of the single launch is told
+    to expect one segment more than its sequences will ever produce; with the limit at 2 ms the
+    waits give up, the status word carries FQ_DEV_WAIT_TIMEOUT and the call returns promptly.
+    Nothing faults and the GPU is not left spinning."""
+    import time
+    lib = K.N.load()
+    w = W.decode_workload(seq_lens=[300, 40], num_q_heads=32, num_kv_heads=8, cfg=24)
+    cache = fill_cache_cpu(w, consts).to(DEV)
+    args = (w.q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV), consts["centroids_128_3"],
+            consts["centroids_128_4"], consts["rotation_128_0"], 8, 128, 16)
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device=DEV)
+    good = K.split_k_paged_decode(*args, num_splits=2, workspace=ws)
+    old = lib.fq_get_device_wait_limit_ns()
+    try:
+        lib.fq_set_device_wait_limit_ns(2_000_000)
+        lib.fq_paged_decode_test_expect_extra_segments(1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        K.split_k_paged_decode(*args, num_splits=2, workspace=ws)
+        torch.cuda.synchronize()
+        took = time.perf_counter() - t0
+    finally:
+        lib.fq_paged_decode_test_expect_extra_segments(0)
+        lib.fq_set_device_wait_limit_ns(old)
+    assert K.workspace_status(ws) & 2          # FQ_DEV_WAIT_TIMEOUT
+    assert took < 1.0, f"the call took {took:.2f} s"
+    # the contract after a status bit: zero the head of the workspace, then it works again
+    ws[:32768].zero_()
+    again = K.split_k_paged_decode(*args, num_splits=2, workspace=ws)
+    assert K.workspace_status(ws) == 0
+    assert torch.equal(again.view(torch.int16), good.view(torch.int16))
+
+
+def test_fp32_query_and_config0_shapes(consts):
+    """configs[0]: fp32 K/V [1, 8, 1024, 128] (K two-stage, V one-stage), one fp32 query token
+    of 32 heads: codes, norms, reconstruction error and the attention output."""
+    from parity import check_codes, check_gamma, check_norms, check_signs
+    rot, S = consts["rotation_128_0"], consts["qjl_128_0"]
+    b3, c3 = consts["boundaries_128_3"], consts["centroids_128_3"]
+    b4, c4 = consts["boundaries_128_4"], consts["centroids_128_4"]
+    g = torch.Generator().manual_seed(1000)
+    k = torch.randn(1, 8, 1024, 128, generator=g)
+    k[..., W.outlier_channels(128)] *= 10.0
+    v = torch.randn(1, 8, 1024, 128, generator=torch.Generator().manual_seed(2000))
+    q = torch.randn(1, 32, 128, generator=torch.Generator().manual_seed(3000))
+    # quantisers on the fp32 tensors
+    idx, kn, signs, gamma = O.prod_quantize(k, rot, c3, b3, S)
+    pk, kn2, bits, g2 = fq.tq_prod_quantize(k[0].to(DEV), rot, b3, c3, S)   # (8, 1024, 128)
+    check_codes(pk, k, rot, b3, O.nibble_pack(idx))
+    check_norms(kn2, kn)
+    codes = O.nibble_unpack(pk.cpu())
+    check_gamma(g2, gamma, k, codes, idx, kn2.cpu(), rot, c3)
+    check_signs(bits, signs, k, codes, idx, kn2.cpu(), rot, c3, S)
+    pv_ref, vn_ref = O.compress(v[0], rot, b4)                               # (8, 1024, ...)
+    pv, vn = fq.tq4_compress(v.to(DEV).reshape(-1, 1, 128), rot, b4)
+    check_codes(pv.reshape(pv_ref.shape), v, rot, b4, pv_ref)
+    check_norms(vn, vn_ref)
+    # reconstruction error of both, against the oracle's
+    rec_v = fq.tq4_decompress_original(pv, vn, c4, rot, dtype=torch.float32).cpu().reshape(v.shape)
+    ref_v = O.mse_dequantize(O.nibble_unpack(pv_ref).long(), vn_ref, rot, c4)
+    mse, mse_ref = (rec_v - v).pow(2).mean().item(), (ref_v - v).pow(2).mean().item()
+    assert abs(mse - mse_ref) <= 1e-4 * mse_ref, (mse, mse_ref)
+    assert 0.005 < mse_ref < 0.02      # 4 bits at d = 128: about 1 % of the variance
+    # the single-query attention over a paged cache built from them (token-major rows)
+    kt, vt = k[0].transpose(0, 1).contiguous(), v[0].transpose(0, 1).contiguous()
+    w = W.decode_workload(seq_lens=[1024], num_q_heads=32, num_kv_heads=8, cfg=0)
+    cache = torch.zeros(w.num_blocks, 16, 8 * 136, dtype=torch.uint8, device=DEV)
+    K.tq4_compress_append(kt.to(DEV), vt.to(DEV), cache, w.slot_mapping.to(DEV), rot, b3, b4)
+    ref_cache = torch.zeros(w.num_blocks, 16, 8 * 136, dtype=torch.uint8)
+    O.compress_and_store(kt, vt, ref_cache, w.slot_mapping, rot, b3, b4)
+    out = K.split_k_paged_decode(q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV), c3, c4,
+                                 rot, 8, 128, 16, num_splits=4)
+    assert out.dtype == torch.float32
+    # with fp32 tensors the reference rounds nothing: out = (softmax(...) V) Pi in fp32
+    ref32, ref = O.split_k_paged_decode_stages(q, cache.cpu(), w.block_table, w.seq_lens, c3, c4,
+                                               rot, 8, 128, 16)
+    err = (out.cpu() - ref).abs()
+    assert err.max().item() <= 2e-3, err.max().item()
+    # the rotated query meets the keys as fp16 (2^-12 of each coordinate)
+    assert err.max().item() <= 2.0 ** -9 * ref.abs().max().item()
+
+
+def test_config4_shapes_ragged_long_sequences(consts):
+    """configs[4]: 64 query heads / 8 KV heads, batch 8, lengths uniform in [32768, 131072]
+    from seed 4.  The cache is written by the (parity-tested) GPU append; the oracle attends
+    over two whole sequences: the longest and the shortest."""
+    lens = W.ragged_lengths()                       # the seed-4 lengths
+    assert lens.min().item() >= 32768 and lens.max().item() <= 131072
+    hq, hkv, d, bs = 64, 8, 128, 16
+    rot = consts["rotation_128_0"]
+    b3, c3 = consts["boundaries_128_3"], consts["centroids_128_3"]
+    b4, c4 = consts["boundaries_128_4"], consts["centroids_128_4"]
+    w = W.decode_workload(seq_lens=lens.tolist(), num_q_heads=hq, num_kv_heads=hkv, cfg=4)
+    cache = torch.zeros(w.num_blocks, bs, hkv * (d + 8), dtype=torch.uint8, device=DEV)
+    at = 0
+    for i, n in enumerate(lens.tolist()):           # K/V of one sequence at a time
+        k, v = W.make_kv(n, hkv, d, cfg=400 + i)
+        K.tq4_compress_append(k.to(DEV), v.to(DEV), cache, w.slot_mapping[at:at + n].to(DEV), rot,
+                              b3, b4)
+        at += n
+    args = (w.q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV), c3, c4, rot, hkv, d, bs)
+    out = K.split_k_paged_decode(*args, num_splits=8)
+    rows = rows_from_partials(K.paged_decode_partials(*args, num_splits=8))
+    ws = K.decode_workspace(torch.device(DEV), 8, hq, hkv, d, 8)
+    assert K.workspace_status(ws) == 0
+    cache_cpu = cache.cpu()
+    for i in (int(lens.argmax()), int(lens.argmin())):
+        sel = slice(i, i + 1)
+        ref32, ref = O.split_k_paged_decode_stages(
+            w.q[sel], cache_cpu, w.block_table[sel], w.seq_lens[sel], c3, c4, rot, hkv, d, bs,
+            per_kv_head=True)
+        # eight query heads per KV head fill all product columns: one fp16 term per weight,
+        # 2^-9 of the entry before the rounding
+        attention_close(out[sel], ref, ref32, rot, got_rot32=rows[sel], rtol=2.0 ** -9)

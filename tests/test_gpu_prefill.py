@@ -120,3 +120,26 @@ def test_argument_errors(consts):
         K.fused_tq_attention(q[:, :, :32].to(DEV), kp.to(DEV), kn.to(DEV), vp.to(DEV), vn.to(DEV),
                              ck, cv, rot, is_causal=True)
     assert e.value.code == -2
+
+
+def test_config3_shape_sliced_oracle(consts):
+    """configs[3]: batch 4 x 8192 tokens, 32 q / 8 kv heads, causal.  One launch at the full
+    shape; the oracle (which would need 34 GB of scores at once) attends over three
+    (batch, KV group) slices, the query rows in chunks."""
+    b, hq, hkv, n, d = 4, 32, 8, 8192, 128
+    rot = consts["rotation_128_0"]
+    b3, c3 = consts["boundaries_128_3"], consts["centroids_128_3"]
+    b4, c4 = consts["boundaries_128_4"], consts["centroids_128_4"]
+    k, v = W.make_kv(b * n, hkv, d, cfg=3)
+    kp, kn = K.tq4_compress(k.to(DEV).reshape(b, n, hkv, d).transpose(1, 2).reshape(-1, 1, d), rot, b3)
+    vp, vn = K.tq4_compress(v.to(DEV).reshape(b, n, hkv, d).transpose(1, 2).reshape(-1, 1, d), rot, b4)
+    kp, vp = kp.reshape(b, hkv, n, d // 2), vp.reshape(b, hkv, n, d // 2)
+    kn, vn = kn.reshape(b, hkv, n, 1), vn.reshape(b, hkv, n, 1)
+    q = torch.randn(b, hq, n, d, generator=torch.Generator().manual_seed(3003)).to(torch.bfloat16)
+    out = K.fused_tq_attention(q.to(DEV), kp, kn, vp, vn, c3, c4, rot, is_causal=True)
+    assert K.attention_workspace_status(torch.device(DEV)) == 0
+    g = hq // hkv
+    for bi, h in ((0, 0), (1, 5), (3, 7)):
+        case = (q[bi:bi + 1, h * g:(h + 1) * g], kp[bi:bi + 1, h:h + 1].cpu(), kn[bi:bi + 1, h:h + 1].cpu(),
+                vp[bi:bi + 1, h:h + 1].cpu(), vn[bi:bi + 1, h:h + 1].cpu(), c3, c4, rot)
+        check(out[bi:bi + 1, h * g:(h + 1) * g], case, is_causal=True, q_chunk=1024)

@@ -80,3 +80,36 @@ def test_static_scratch_refuses_what_does_not_fit(consts):
     rc, _ = _static_call(lib, w, cache, consts, num_splits=64)
     assert rc == -3 and b"16777216" in lib.fq_last_error_string()
     assert lib.fq_launch_count() == before
+
+
+def test_static_scratch_three_launch_form_and_status_word(consts):
+    """The static entry behaves like the ordinary one in its two other respects: it honours
+    fq_paged_decode_set_single_launch(0) (three ordinary launches, same answer), and its device
+    status word - the caller has no pointer to the array - is read through
+    fq_split_k_paged_decode_static_status: a block index outside the cache is reported there,
+    not followed."""
+    lib = N.load()
+    w, cache = _inputs(consts, [300, 17, 1000], 44)
+    rc, one = _static_call(lib, w, cache, consts, num_splits=3)
+    assert rc == 0
+    K.set_single_launch(False)
+    try:
+        n0 = lib.fq_launch_count()
+        rc, three = _static_call(lib, w, cache, consts, num_splits=3)
+        assert rc == 0 and lib.fq_launch_count() - n0 == 3
+    finally:
+        K.set_single_launch(True)
+    torch.cuda.synchronize()
+    ref32, ref = O.split_k_paged_decode_stages(
+        w.q, cache.cpu(), w.block_table, w.seq_lens, consts["centroids_128_3"],
+        consts["centroids_128_4"], consts["rotation_128_0"], 8, 128, 16)
+    attention_close(one, ref, ref32, consts["rotation_128_0"])
+    attention_close(three, ref, ref32, consts["rotation_128_0"])
+    st = C.c_uint32(99)
+    assert lib.fq_split_k_paged_decode_static_status(C.byref(st), N.stream_ptr(torch.device(DEV))) == 0
+    assert st.value == 0
+    w.block_table[1, 0] = 10_000_000
+    rc, _ = _static_call(lib, w, cache, consts, num_splits=3)
+    assert rc == 0
+    assert lib.fq_split_k_paged_decode_static_status(C.byref(st), N.stream_ptr(torch.device(DEV))) == 0
+    assert st.value & 1            # FQ_DEV_BAD_BLOCK_INDEX
