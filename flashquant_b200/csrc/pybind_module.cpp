@@ -45,16 +45,39 @@ Tensor f32_on(const Tensor& t, const torch::Device& dev) {
   return t.to(torch::TensorOptions().device(dev).dtype(torch::kFloat32)).contiguous();
 }
 
+// Constants (rotations, tables): the reference keeps several of them as CPU tensors and hands
+// them to every call, which would mean a blocking host-to-device copy per call.  A constant
+// that is not already a contiguous fp32 tensor on the device is copied once and found again by
+// (storage address, version, device); the entry keeps the source alive, so its address cannot
+// be taken by another tensor meanwhile.
+Tensor const_on(const Tensor& t, const torch::Device& dev) {
+  if (t.device() == dev && t.scalar_type() == torch::kFloat32 && t.is_contiguous()) return t;
+  struct Entry { Tensor src, copy; };
+  using Key = std::tuple<const void*, int64_t, int, int64_t, int64_t>;
+  static std::mutex mu;
+  static std::map<Key, Entry> cache;
+  const Key key{t.data_ptr(), int64_t(t._version()), int(dev.index()), t.numel(),
+                t.dim() ? t.stride(0) : 0};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    if (cache.size() >= 256) cache.clear();
+    it = cache.emplace(key, Entry{t, f32_on(t, dev)}).first;
+  }
+  return it->second.copy;
+}
+
 fq_stream_t stream_of(const torch::Device& dev) {
   return reinterpret_cast<fq_stream_t>(at::cuda::getCurrentCUDAStream(dev.index()).stream());
 }
 
-// zero-initialised byte workspace per (device, kind), grown on demand
+// zero-initialised byte workspace per (device, stream, kind), grown on demand: calls on
+// different streams may overlap on the GPU and must not share counters or partial rows
 Tensor workspace(const torch::Device& dev, int kind, size_t bytes) {
   static std::mutex mu;
-  static std::map<std::pair<int, int>, Tensor> cache;
+  static std::map<std::tuple<int, const void*, int>, Tensor> cache;
   std::lock_guard<std::mutex> lock(mu);
-  auto key = std::make_pair(int(dev.index()), kind);
+  auto key = std::make_tuple(int(dev.index()), static_cast<const void*>(stream_of(dev)), kind);
   auto it = cache.find(key);
   if (it == cache.end() || size_t(it->second.numel()) < bytes) {
     size_t n = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
@@ -73,7 +96,7 @@ std::tuple<Tensor, Tensor> tq4_compress(const Tensor& x, const Tensor& rot_t_eve
   const auto dev = x.device();
   const int64_t n = x.size(0), h = x.size(1), d = x.size(2);
   Tensor xc = x.contiguous();
-  Tensor even = f32_on(rot_t_even, dev), odd = f32_on(rot_t_odd, dev), bnd = f32_on(boundaries, dev);
+  Tensor even = const_on(rot_t_even, dev), odd = const_on(rot_t_odd, dev), bnd = const_on(boundaries, dev);
   Tensor packed, norms;
   if (out.has_value()) {
     packed = std::get<0>(*out);
@@ -97,7 +120,7 @@ Tensor tq4_decompress(const Tensor& packed, const Tensor& norms, const Tensor& c
   const auto dev = packed.device();
   const int64_t n = packed.size(0), h = packed.size(1), d = 2 * packed.size(2);
   const auto st = torch::python::detail::py_object_to_dtype(dtype);
-  Tensor p = packed.contiguous(), nn = f32_on(norms, dev), c = f32_on(centroids, dev);
+  Tensor p = packed.contiguous(), nn = f32_on(norms, dev), c = const_on(centroids, dev);
   Tensor o = out.has_value() ? *out
                              : torch::empty({n, h, d}, torch::TensorOptions().device(dev).dtype(st));
   TORCH_CHECK(o.is_contiguous() && o.numel() == n * h * d && o.scalar_type() == st,
@@ -119,7 +142,7 @@ Tensor fused_tq_attention(const Tensor& q, const Tensor& k_packed, const Tensor&
   const int hkv = int(k_packed.size(1)), nkv = int(k_packed.size(2));
   Tensor qc = q.contiguous(), kp = k_packed.contiguous(), vp = v_packed.contiguous();
   Tensor kn = f32_on(k_norms.reshape({b, hkv, nkv}), dev), vn = f32_on(v_norms.reshape({b, hkv, nkv}), dev);
-  Tensor ck = f32_on(centroids_k, dev), cv = f32_on(centroids_v, dev), rot = f32_on(rotation, dev);
+  Tensor ck = const_on(centroids_k, dev), cv = const_on(centroids_v, dev), rot = const_on(rotation, dev);
   Tensor out = torch::empty_like(qc);
   const size_t need = fq_fused_tq_attention_workspace_bytes(b, hq, nq, d);
   Tensor ws = workspace(dev, 1, need);
@@ -147,10 +170,12 @@ Tensor split_k_paged_decode(const Tensor& q, const Tensor& kv_cache, const Tenso
   const int num_seqs = int(q.size(0)), hq = int(q.size(1));
   Tensor qc = q.contiguous(), bt = block_table.contiguous(), sl = seq_lens.contiguous();
   TORCH_CHECK(kv_cache.is_contiguous(), "kv_cache must be contiguous");
-  Tensor ck = f32_on(centroids_k, dev), cv = f32_on(centroids_v, dev), rot = f32_on(rotation, dev);
+  Tensor ck = const_on(centroids_k, dev), cv = const_on(centroids_v, dev), rot = const_on(rotation, dev);
+  // `out` may be a view with another shape over the same elements (vLLM hands in
+  // output[:num_actual], (tokens, H_q * D)): only contiguity, size and dtype matter
   Tensor o = out.has_value() ? *out : torch::empty_like(qc);
-  TORCH_CHECK(o.is_contiguous() && o.sizes() == qc.sizes() && o.scalar_type() == qc.scalar_type(),
-              "out must be a contiguous tensor of q's shape and dtype");
+  TORCH_CHECK(o.is_contiguous() && o.numel() == qc.numel() && o.scalar_type() == qc.scalar_type(),
+              "out must be a contiguous tensor with q's number of elements and dtype");
   const double scale = sm_scale.has_value() ? *sm_scale : 1.0 / std::sqrt(double(head_dim));
   const size_t need = fq_paged_decode_workspace_bytes(num_seqs, hq, num_kv_heads, head_dim, num_splits);
   Tensor ws = workspace(dev, 0, need);
@@ -161,6 +186,52 @@ Tensor split_k_paged_decode(const Tensor& q, const Tensor& kv_cache, const Tenso
                                 head_dim, block_size, kv_cache.size(0), float(scale), o.data_ptr(),
                                 num_splits, ws.data_ptr(), size_t(ws.numel()), stream_of(dev)));
   return o;
+}
+
+// Device status word (FQ_DEV_* bits) of the decode workspace of the current stream; a non-zero
+// word also re-zeroes the head of the workspace, as the C ABI asks before the next call.
+int64_t decode_status(const Tensor& like) {
+  need_cuda(like, "tensor");
+  c10::cuda::CUDAGuard guard(like.device());
+  const auto dev = like.device();
+  Tensor ws = workspace(dev, 0, 1);
+  uint32_t st = 0;
+  check(fq_workspace_status(ws.data_ptr(), &st, stream_of(dev)));
+  if (st) ws.narrow(0, 0, 32768).zero_();
+  return int64_t(st);
+}
+
+void tq4_compress_append_qjl(const Tensor& key, const Tensor& value, Tensor kv_cache,
+                             Tensor kq_cache, const Tensor& slot_mapping, const Tensor& rotation,
+                             const Tensor& boundaries_k, const Tensor& centroids_k,
+                             const Tensor& boundaries_v, const Tensor& qjl_matrix) {
+  need_cuda(key, "key");
+  need_cuda(kv_cache, "kv_cache");
+  need_cuda(kq_cache, "kq_cache");
+  TORCH_CHECK(key.dim() == 3 && value.sizes() == key.sizes(), "key/value must be (N, H, D)");
+  c10::cuda::CUDAGuard guard(key.device());
+  const auto dev = key.device();
+  const int64_t n = key.size(0);
+  const int h = int(key.size(1)), d = int(key.size(2));
+  Tensor k = key.contiguous(), v = value.contiguous(), slots = slot_mapping.contiguous();
+  TORCH_CHECK(slots.scalar_type() == torch::kInt64 || slots.scalar_type() == torch::kInt32,
+              "slot_mapping must be int32 or int64");
+  Tensor rot = const_on(rotation, dev), bk = const_on(boundaries_k, dev);
+  Tensor ck = const_on(centroids_k, dev), bv = const_on(boundaries_v, dev);
+  Tensor S = const_on(qjl_matrix, dev);
+  TORCH_CHECK(kv_cache.is_contiguous() && kv_cache.size(-1) == int64_t(h) * (d + 8),
+              "kv_cache must be contiguous (num_blocks, block_size, H*(D+8))");
+  TORCH_CHECK(kq_cache.is_contiguous() && kq_cache.size(-1) == int64_t(h) * (d / 8 + 4),
+              "kq_cache must be contiguous (num_blocks, block_size, H*(D/8+4))");
+  const int64_t num_slots = kv_cache.numel() / (int64_t(h) * (d + 8));
+  TORCH_CHECK(kq_cache.numel() / (int64_t(h) * (d / 8 + 4)) == num_slots,
+              "kq_cache must have as many slots as kv_cache");
+  check(fq_tq4_compress_append_qjl(
+      k.data_ptr(), v.data_ptr(), dtype_of(k), n, h, d, int64_t(h) * d, rot.data_ptr<float>(),
+      bk.data_ptr<float>(), int(bk.numel()), ck.data_ptr<float>(), bv.data_ptr<float>(),
+      int(bv.numel()), S.data_ptr<float>(), kv_cache.data_ptr<uint8_t>(),
+      kq_cache.data_ptr<uint8_t>(), num_slots, slots.data_ptr(),
+      slots.scalar_type() == torch::kInt64 ? 1 : 0, stream_of(dev)));
 }
 
 void tq4_compress_append(const Tensor& key, const Tensor& value, Tensor kv_cache,
@@ -176,8 +247,8 @@ void tq4_compress_append(const Tensor& key, const Tensor& value, Tensor kv_cache
   Tensor k = key.contiguous(), v = value.contiguous(), slots = slot_mapping.contiguous();
   TORCH_CHECK(slots.scalar_type() == torch::kInt64 || slots.scalar_type() == torch::kInt32,
               "slot_mapping must be int32 or int64");
-  Tensor rot = f32_on(rotation, dev), bk = f32_on(boundaries_k, dev);
-  Tensor bv = boundaries_v.has_value() ? f32_on(*boundaries_v, dev) : bk;
+  Tensor rot = const_on(rotation, dev), bk = const_on(boundaries_k, dev);
+  Tensor bv = boundaries_v.has_value() ? const_on(*boundaries_v, dev) : bk;
   TORCH_CHECK(kv_cache.is_contiguous() && kv_cache.size(-1) == int64_t(h) * (d + 8),
               "kv_cache must be contiguous (num_blocks, block_size, H*(D+8))");
   const int64_t num_slots = kv_cache.numel() / (int64_t(h) * (d + 8));
@@ -214,5 +285,10 @@ PYBIND11_MODULE(_C, m) {
   m.def("tq4_compress_append", &tq4_compress_append, py::arg("key"), py::arg("value"),
         py::arg("kv_cache"), py::arg("slot_mapping"), py::arg("rotation"),
         py::arg("boundaries_k"), py::arg("boundaries_v") = py::none());
+  m.def("tq4_compress_append_qjl", &tq4_compress_append_qjl, py::arg("key"), py::arg("value"),
+        py::arg("kv_cache"), py::arg("kq_cache"), py::arg("slot_mapping"), py::arg("rotation"),
+        py::arg("boundaries_k"), py::arg("centroids_k"), py::arg("boundaries_v"),
+        py::arg("qjl_matrix"));
+  m.def("decode_status", &decode_status, py::arg("like"));
   m.def("launch_count", []() { return fq_launch_count(); });
 }

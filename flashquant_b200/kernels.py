@@ -371,7 +371,9 @@ def decode_workspace(device, num_seqs: int, num_q_heads: int, num_kv_heads: int,
     lib = N.load()
     need = lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
                                                num_splits)
-    key = (device.type, device.index)
+    # one workspace per (device, stream): calls on different streams may overlap on the GPU
+    # and must not share counters or partial rows
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
@@ -386,10 +388,15 @@ def set_single_launch(enabled: bool) -> None:
     N.load().fq_paged_decode_set_single_launch(1 if enabled else 0)
 
 
-def workspace_status(ws: torch.Tensor) -> int:
-    """Device status word of a decode workspace (0 = no error); synchronises the stream."""
+def workspace_status(ws: torch.Tensor, reset: bool = False) -> int:
+    """Device status word of a decode workspace (0 = no error); synchronises the stream.
+    ``reset`` re-zeroes the head of the workspace when the word is non-zero, which the C ABI
+    asks for before the workspace is used again (the counters the CTAs signal each other
+    through are only left at zero by a call that completes)."""
     st = C.c_uint32(0)
     N.check(N.load().fq_workspace_status(N.ptr(ws), C.byref(st), N.stream_ptr(ws.device)))
+    if st.value and reset:
+        ws[:32768].zero_()
     return st.value
 
 
