@@ -9,7 +9,7 @@ rotation.  With N > 1 (launched by torchrun, one rank per GPU) every rank decode
 batch of the same shape - sequences are independent, so there is no collective on the data
 path (weak scaling) - and the time is the maximum over ranks.
 
-One JSON line is printed by rank 0; see DESIGN.md for the meaning of every key.
+One JSON line is printed by rank 0; `python bench.py --help` lists the secondary workloads.
 """
 
 from __future__ import annotations
@@ -31,6 +31,7 @@ import torch  # noqa: E402
 METRIC = "tq4_paged_decode_tokens_per_s"
 UNIT = "tokens/s"
 NUM_SEQS, CONTEXT, HQ, HKV, D, BS, SPLITS = 32, 4096, 32, 8, 128, 16, 8
+D_ = D  # (the secondary blocks import flashquant_b200.distributed as D)
 CACHE_COPIES = 3  # 3 x 142.6 MB of packed cache are cycled so that no step finds its pages in L2
 
 
@@ -247,7 +248,7 @@ def run_ours(args):
         kernel_ms = k0.elapsed_time(k1) / (reps * CACHE_COPIES)
 
     # ---- end to end: host buffers in, host buffer out, every step -----------------------
-    e2e_steps = min(args.steps, 200)
+    e2e_steps = max(args.steps, 200) if args.steps < 2000 else 2000  # 20 steps would be noise
     hq_ = w.q.pin_memory()
     new_k = k_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
     new_v = v_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
@@ -276,6 +277,24 @@ def run_ours(args):
     e2e_s = time.perf_counter() - tw
     e2e_launches = lib.fq_launch_count() - n0
     barrier()
+
+    # ---- further rows of the hot path, short runs in the same process ------------------------
+    extras = {}
+    if not args.no_extras:
+        ctx = dict(dev=dev, rank=rank, world=world, dist=dist, rot=rot, S=S, bk=bk, ck=ck, bv=bv, cv=cv,
+                   peaks=_peaks(), caches=caches, w=w, ws=ws)
+        for name, fn in (("strong_scaling", extra_strong_scaling), ("long_context", extra_long_context),
+                         ("multi_token", extra_multi_token), ("append", extra_append),
+                         ("decompress", extra_decompress), ("prefill", extra_prefill)):
+            if world > 1 and name in ("multi_token", "append", "decompress", "prefill"):
+                continue  # one-GPU rows: measured at N = 1 only
+            try:
+                extras[name] = fn(ctx)
+            except Exception as e:  # a secondary block must not take the headline down
+                extras[name] = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
 
     # ---- reductions over ranks ----------------------------------------------------------
     vals = torch.tensor([ms, kernel_ms, e2e_s], dtype=torch.float64, device=dev)
@@ -323,24 +342,268 @@ def run_ours(args):
                             "compress-on-append, decode, output -> pinned host, synchronise; "
                             "the packed cache itself stays in HBM"},
             "roofline": {"bound": "hbm",
-                         "kernel": "paged_decode_kernel<128, true, 1> (single launch per call)",
+                         "kernel": "paged_decode_fast_kernel<KPRMT, FUSE=1, two-term weights> "
+                                   "(single cooperative launch per call)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                          "algorithmic_bytes": alg, "kernel_ms": call_ms,
                          "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "traffic": args.traffic,
+                         "traffic": args.traffic if args.traffic is not None else _recorded_traffic(),
                          "streaming_phase_alone": {
-                             "kernel": "paged_decode_kernel<128, true, 0>",
+                             "kernel": "paged_decode_fast_kernel<KPRMT, FUSE=0, two-term weights>",
                              "kernel_ms": kernel_ms, "achieved": stream_gbs,
                              "frac": stream_gbs / peak}},
         }
+        line.update(extras)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w, caches[0].cpu(), ck.cpu(), cv.cpu(), rot.cpu(),
                                                 budget_s=20.0)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# secondary blocks of the line
+# --------------------------------------------------------------------------------------
+def _event_loop(fn, steps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / steps
+
+
+def _max_over_ranks(ctx, value):
+    if ctx["dist"] is None:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=ctx["dev"])
+    ctx["dist"].all_reduce(t, op=ctx["dist"].ReduceOp.MAX)
+    return float(t.item())
+
+
+def _graph_of(fn, side):
+    with torch.cuda.stream(side):
+        fn()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def extra_strong_scaling(ctx):
+    """configs[1] with its 32 sequences split over the ranks (32 / N each): the same total
+    work at every N, next to the weak-scaling headline."""
+    from flashquant_b200 import distributed as D, kernels as K
+    w, world, rank, dev = ctx["w"], ctx["world"], ctx["rank"], ctx["dev"]
+    mine = D.shard_sequences(NUM_SEQS, rank, world)
+    n = mine.stop - mine.start
+    q = w.q[mine].contiguous().to(dev)
+    bt, sl = w.block_table[mine].contiguous().to(dev), w.seq_lens[mine].contiguous().to(dev)
+    out = torch.empty_like(q)
+    side = torch.cuda.Stream()
+    graphs = [_graph_of(lambda c=c: K.split_k_paged_decode(
+        q, c, bt, sl, ctx["ck"], ctx["cv"], ctx["rot"], HKV, D_, BS, out=out, num_splits=SPLITS,
+        workspace=ctx["ws"]), side) for c in ctx["caches"]]
+    i = [0]
+
+    def step():
+        graphs[i[0] % CACHE_COPIES].replay()
+        i[0] += 1
+    ms = _max_over_ranks(ctx, _event_loop(step, 300, 10))
+    return {"ms_per_step": ms, "tokens_per_s": NUM_SEQS / (ms * 1e-3),
+            "what": f"configs[1], {NUM_SEQS} sequences in total, {n} per rank, no collective; "
+                    "time = max over ranks", "scaling": "strong"}
+
+
+def extra_long_context(ctx):
+    """configs[4]: 64 q / 8 kv heads, batch 8, seed-4 lengths in [32768, 131072].
+    (a) KV heads sharded over the ranks (8 / N each), no communication;
+    (b) one sequence of 131072 tokens split over the ranks by token range: partial rows, ONE
+        all-gather of (H_q, D+4) fp32 per rank, merge on every rank."""
+    from flashquant_b200 import distributed as D, kernels as K, workloads as W
+    world, rank, dev, dist = ctx["world"], ctx["rank"], ctx["dev"], ctx["dist"]
+    rot, bk, ck, bv, cv = ctx["rot"], ctx["bk"], ctx["ck"], ctx["bv"], ctx["cv"]
+    hq, hkv, d, bs = 64, 8, 128, 16
+    peak = float(ctx["peaks"].get("hbm_gbs", 6650.0))
+    res = {}
+    # ---- (a) head-sharded ---------------------------------------------------------------------
+    if hkv % world == 0:
+        lens = W.ragged_lengths()
+        kv, qh = D.shard_kv_heads(hkv, hq, rank, world)
+        h_loc = kv.stop - kv.start
+        w = W.decode_workload(seq_lens=lens.tolist(), num_q_heads=hq, num_kv_heads=h_loc, cfg=4)
+        cache = torch.zeros(w.num_blocks, bs, h_loc * (d + 8), dtype=torch.uint8, device=dev)
+        at = 0
+        for i, n in enumerate(lens.tolist()):
+            k, v = W.make_kv(n, hkv, d, cfg=400 + i)
+            K.tq4_compress_append(k[:, kv].contiguous().to(dev), v[:, kv].contiguous().to(dev), cache,
+                                  w.slot_mapping[at:at + n].to(dev), rot, bk, bv)
+            at += n
+        q = w.q[:, qh].contiguous().to(dev)
+        bt, sl = w.block_table.to(dev), w.seq_lens.to(dev)
+        out = torch.empty_like(q)
+        ws = K.decode_workspace(dev, 8, qh.stop - qh.start, h_loc, d, 8)
+        g = _graph_of(lambda: K.split_k_paged_decode(q, cache, bt, sl, ck, cv, rot, h_loc, d, bs,
+                                                     out=out, num_splits=8, workspace=ws),
+                      torch.cuda.Stream())
+        ms = _max_over_ranks(ctx, _event_loop(g.replay, 100, 5))
+        alg = int(lens.sum()) * 136 * h_loc + 2 * q.numel() * 2
+        res["head_sharded"] = {
+            "ms_per_step": ms, "tokens_per_s": 8 / (ms * 1e-3), "kv_heads_per_gpu": h_loc,
+            "algorithmic_bytes_per_gpu": alg, "hbm_gb_s_per_gpu": alg / (ms * 1e-3) / 1e9,
+            "frac_of_peak_per_gpu": alg / (ms * 1e-3) / 1e9 / peak,
+            "l2": f"{cache.numel() / 1e6:.0f} MB of cache per GPU (> 126 MB L2 only above 1 head "
+                  "per GPU)" if h_loc == 1 else f"{cache.numel() / 1e6:.0f} MB of cache per GPU",
+            "status": K.workspace_status(ws)}
+        del cache
+    # ---- (b) one long sequence, token ranges per rank ---------------------------------------------
+    L = 131072
+    w1 = W.decode_workload(seq_lens=[L], num_q_heads=hq, num_kv_heads=hkv, cfg=41)
+    lo, hi = D.token_range(L, bs, rank, world)
+    k, v = W.make_kv(L, hkv, d, cfg=441)
+    # every rank writes only the pages it owns (the block table is global)
+    cache = torch.zeros(w1.num_blocks, bs, hkv * (d + 8), dtype=torch.uint8, device=dev)
+    K.tq4_compress_append(k[lo:hi].to(dev), v[lo:hi].to(dev), cache, w1.slot_mapping[lo:hi].to(dev),
+                          rot, bk, bv)
+    bt_l, len_l = D.local_view(w1.block_table, w1.seq_lens, bs, rank, world)
+    q = w1.q.to(dev)
+    bt_l, len_l = bt_l.to(dev), len_l.to(dev)
+    ws = K.decode_workspace(dev, 1, hq, hkv, d, 8)
+    part = torch.empty(1, hq, d + 4, dtype=torch.float32, device=dev)
+    gathered = torch.empty(world, 1, hq, d + 4, dtype=torch.float32, device=dev)
+    out = torch.empty_like(q)
+
+    def partial():
+        K.paged_decode_partials(q, cache, bt_l, len_l, ck, cv, rot, hkv, d, bs, num_splits=8,
+                                partials=part, workspace=ws)
+
+    def gather():
+        if dist is not None:
+            dist.all_gather_into_tensor(gathered, part)
+        else:
+            gathered.copy_(part.unsqueeze(0))
+
+    def merge():
+        K.split_k_merge(gathered, rot, q.dtype, out=out)
+
+    def whole():
+        partial(); gather(); merge()
+    ms_whole = _max_over_ranks(ctx, _event_loop(whole, 100, 5))
+    ms_part = _max_over_ranks(ctx, _event_loop(partial, 100, 5))
+    ms_gather = _max_over_ranks(ctx, _event_loop(gather, 200, 10))
+    ms_merge = _max_over_ranks(ctx, _event_loop(merge, 100, 5))
+    whole()
+    # correctness evidence that travels with the timing: against a second merge of the same
+    # gathered rows on the CPU in fp64 (rounded the way the kernel rounds), on every rank
+    g64 = gathered.double().cpu()
+    m = g64[..., d].amax(dim=0, keepdim=True)
+    wgt = torch.where(torch.isinf(g64[..., d]), torch.zeros_like(m), torch.exp2(g64[..., d] - m))
+    num = (wgt.unsqueeze(-1) * g64[..., :d]).sum(0)
+    den = (wgt * g64[..., d + 1]).sum(0).unsqueeze(-1)
+    ref = ((num / den).float().to(q.dtype).float() @ rot.float().cpu()).to(q.dtype)
+    err = _max_over_ranks(ctx, (out.float().cpu() - ref.float()).abs().max().item())
+    alg = (hi - lo) * hkv * 136
+    res["cross_gpu_split_k"] = {
+        "tokens": L, "tokens_per_gpu": hi - lo, "ms_whole": ms_whole, "ms_partials": ms_part,
+        "ms_all_gather": ms_gather, "ms_merge": ms_merge,
+        "all_gather_bytes_per_rank": part.numel() * 4, "ranks_in_all_gather": world,
+        "hbm_gb_s_per_gpu_partials": alg / (ms_part * 1e-3) / 1e9,
+        "max_abs_err_vs_fp64_merge": err,
+        "what": "fq_paged_decode_partials over the rank's token range -> one "
+                "all_gather_into_tensor of (H_q, D+4) fp32 -> fq_split_k_merge on every rank; "
+                "three launches + one collective per call, timed without graphs"}
+    return res
+
+
+def extra_multi_token(ctx):
+    """Decode steps of n_q tokens per sequence at configs[1] (fq_split_k_paged_decode_multi)."""
+    import flashquant_b200 as fq
+    w, dev = ctx["w"], ctx["dev"]
+    bt, sl = w.block_table.to(dev), w.seq_lens.to(dev)
+    res = {}
+    for n_q in (1, 2, 4):
+        q = torch.randn(NUM_SEQS, n_q, HQ, D_, generator=torch.Generator().manual_seed(n_q)).to(
+            torch.bfloat16).to(dev)
+        i = [0]
+
+        def step():
+            fq.split_k_paged_decode_multi(q, ctx["caches"][i[0] % CACHE_COPIES], bt, sl, ctx["ck"],
+                                          ctx["cv"], ctx["rot"], HKV, D_, BS, num_splits=SPLITS)
+            i[0] += 1
+        ms = _event_loop(step, 150, 5)
+        res[f"n_q_{n_q}"] = {"us_per_step": ms * 1e3, "tokens_per_s": NUM_SEQS * n_q / (ms * 1e-3)}
+    res["what"] = ("the last n_q tokens of every sequence in one call; with 4 query heads per KV "
+                   "head two tokens share a pass over the pages; Python call, no graph")
+    return res
+
+
+def extra_append(ctx):
+    """configs[2]: compress-on-append of 8192 tokens x 8 heads into a 65536-slot cache."""
+    from flashquant_b200 import kernels as K, workloads as W
+    dev = ctx["dev"]
+    w = W.append_workload()
+    key, val, slots = w.key.to(dev), w.value.to(dev), w.slot_mapping.to(dev)
+    nb = w.num_slots // w.block_size
+    cache = torch.zeros(nb, BS, HKV * (D_ + 8), dtype=torch.uint8, device=dev)
+    plane = torch.zeros(nb, BS, HKV * (D_ // 8 + 4), dtype=torch.uint8, device=dev)
+    ms_qjl = _event_loop(lambda: K.tq4_compress_append_qjl(key, val, cache, plane, slots, ctx["rot"],
+                                                           ctx["bk"], ctx["ck"], ctx["bv"], ctx["S"]), 100)
+    ms_mse = _event_loop(lambda: K.tq4_compress_append(key, val, cache, slots, ctx["rot"], ctx["bk"],
+                                                       ctx["bv"]), 100)
+    peak = float(ctx["peaks"].get("hbm_gbs", 6650.0))
+    alg = w.algorithmic_bytes(with_qjl=True)
+    return {"us_per_call_two_stage": ms_qjl * 1e3, "us_per_call_one_stage": ms_mse * 1e3,
+            "tokens_per_s": 8192 / (ms_qjl * 1e-3), "algorithmic_bytes": alg,
+            "hbm_gb_s": alg / (ms_qjl * 1e-3) / 1e9, "frac_of_hbm_peak": alg / (ms_qjl * 1e-3) / 1e9 / peak,
+            "note": "bound by the split-fp16 rotations on mma.sync, not by HBM"}
+
+
+def extra_decompress(ctx):
+    """Decompress: 65536 x 8 vectors of head_dim 128, rotated space (bf16 out) and original
+    space (fq_tq4_decompress_original)."""
+    import flashquant_b200 as fq
+    dev = ctx["dev"]
+    n, h = 65536, 8
+    g = torch.Generator().manual_seed(77)
+    packed = torch.randint(0, 256, (n, h, D_ // 2), dtype=torch.uint8, generator=g).to(dev)
+    norms = (torch.rand(n, h, 1, generator=g) + 0.5).to(dev)
+    out = torch.empty(n, h, D_, dtype=torch.bfloat16, device=dev)
+    ms = _event_loop(lambda: fq.tq4_decompress(packed, norms, ctx["cv"], dtype=torch.bfloat16, out=out), 100)
+    ms_orig = _event_loop(lambda: fq.tq4_decompress_original(packed, norms, ctx["cv"], ctx["rot"],
+                                                            dtype=torch.bfloat16), 30)
+    peak = float(ctx["peaks"].get("hbm_gbs", 6650.0))
+    alg = n * h * (D_ // 2 + 4 + 2 * D_)
+    return {"vectors": n * h, "us_rotated_space": ms * 1e3, "us_original_space": ms_orig * 1e3,
+            "algorithmic_bytes": alg, "hbm_gb_s": alg / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": alg / (ms * 1e-3) / 1e9 / peak,
+            "l2": "168 MB of codes, norms and output per call (> 126 MB L2)"}
+
+
+def extra_prefill(ctx):
+    """configs[3]: fused causal TQ4 prefill, batch 4 x 8192, 32 q / 8 kv heads."""
+    from flashquant_b200 import kernels as K, workloads as W
+    dev = ctx["dev"]
+    b, n = 4, 8192
+    k, v = W.make_kv(b * n, HKV, D_, cfg=3)
+    kp, kn = K.tq4_compress(k.to(dev).reshape(b, n, HKV, D_).transpose(1, 2).reshape(-1, 1, D_), ctx["rot"], ctx["bk"])
+    vp, vn = K.tq4_compress(v.to(dev).reshape(b, n, HKV, D_).transpose(1, 2).reshape(-1, 1, D_), ctx["rot"], ctx["bv"])
+    kp, vp = kp.reshape(b, HKV, n, D_ // 2), vp.reshape(b, HKV, n, D_ // 2)
+    kn, vn = kn.reshape(b, HKV, n, 1), vn.reshape(b, HKV, n, 1)
+    q = torch.randn(b, HQ, n, D_, generator=torch.Generator().manual_seed(3003)).to(torch.bfloat16).to(dev)
+    ms = _event_loop(lambda: K.fused_tq_attention(q, kp, kn, vp, vn, ctx["ck"], ctx["cv"], ctx["rot"],
+                                                  is_causal=True), 5, 2)
+    flops = 4.0 * b * HQ * n * n * D_ / 2
+    peak = float(ctx["peaks"].get("bf16_tflops_sustained", 1400.0))
+    return {"ms_per_call": ms, "tflops_causal_half": flops / (ms * 1e-3) / 1e12,
+            "frac_of_sustained_tensor_peak": flops / (ms * 1e-3) / 1e12 / peak}
 
 
 # --------------------------------------------------------------------------------------
@@ -354,6 +617,19 @@ def cpu_decode_sample(w, cache, ck, cv, rot, n_seq):
 
 def cpu_baseline(w, cache, ck, cv, rot, budget_s):
     torch.set_num_threads(os.cpu_count() or 1)
+    ref_pd = _reference_package()
+    if ref_pd is not None:
+        # the reference's own token loop: a few seconds per sequence, so a sample of them
+        t = time.perf_counter()
+        n = 0
+        while n < NUM_SEQS and time.perf_counter() - t < budget_s:
+            ref_pd.split_k_paged_decode(w.q[n:n + 1], cache, w.block_table[n:n + 1],
+                                        w.seq_lens[n:n + 1], ck, cv, rot, HKV, D, BS)
+            n += 1
+        dt = time.perf_counter() - t
+        return {"value": n / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "reference",
+                "sample": f"{n} of the {NUM_SEQS} sequences (context {CONTEXT}) through the "
+                          f"reference's own split_k_paged_decode CPU branch, {dt:.1f} s"}
     t = time.perf_counter()
     cpu_decode_sample(w, cache, ck, cv, rot, 1)
     one = time.perf_counter() - t
@@ -366,9 +642,25 @@ def cpu_baseline(w, cache, ck, cv, rot, budget_s):
                       f"vectorised oracle restatement of the reference's CPU decode, {dt:.2f} s"}
 
 
+def _reference_package():
+    """The reference's own package, if oracle/make_ref.py has placed it under oracle/_ref/."""
+    ref_root = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "flashquant")):
+        return None
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    try:
+        from flashquant.kernels import paged_decode as ref_pd  # noqa: WPS433
+        return ref_pd
+    except Exception:
+        return None
+
+
 def run_reference(args):
-    """Times the oracle port of the reference's CPU path (the reference is pure PyTorch and
-    cannot travel to the GPU box) on a bounded sample of the same workload."""
+    """The reference's CPU implementation of the path on this host's cores, on a bounded sample
+    of the same workload: its own ``split_k_paged_decode`` (a Python loop over tokens and heads,
+    src/flashquant/kernels/paged_decode.py:112-128 + cpu_reference.py:230-368) when
+    oracle/_ref holds the package, else the vectorised oracle restatement."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     from flashquant_b200 import workloads as W
@@ -380,32 +672,44 @@ def run_reference(args):
     rot = q4.rotation
     bk, ck = q3.mse_quantizer.boundaries, q3.mse_quantizer.centroids
     bv, cv = q4.boundaries, q4.centroids
-    n_seq = 2
+    ref_pd = _reference_package()
+    # one sequence of the 32 per step for the reference's token loop (about 4 s), two for the
+    # vectorised port
+    n_seq = 1 if ref_pd is not None else 2
     w = W.decode_workload(n_seq, CONTEXT, HQ, HKV, D, BS, cfg=1)
     k, v = W.make_kv(w.total_tokens, HKV, D, cfg=1)
     cache = torch.zeros(w.num_blocks, BS, HKV * (D + 8), dtype=torch.uint8)
     O.compress_and_store(k, v, cache, w.slot_mapping, rot, bk, bv)
-    for _ in range(max(1, min(args.warmup, 3))):
-        cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
-    steps = args.steps
+
+    def step():
+        if ref_pd is not None:
+            return ref_pd.split_k_paged_decode(w.q, cache, w.block_table, w.seq_lens, ck, cv, rot,
+                                               HKV, D, BS)
+        return cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
+
+    for _ in range(1 if ref_pd is not None else max(1, min(args.warmup, 3))):
+        step()
     t = time.perf_counter()
     done = 0
-    for _ in range(steps):
-        cpu_decode_sample(w, cache, ck, cv, rot, n_seq)
+    for _ in range(args.steps):
+        step()
         done += 1
-        if time.perf_counter() - t > 120.0:  # keep the whole run within a few minutes
+        if time.perf_counter() - t > 100.0:  # keep the whole run within a few minutes
             break
     dt = time.perf_counter() - t
     value = n_seq * done / dt
-    sample = (f"{n_seq} sequences x context {CONTEXT} per step (of the 32 in the workload), "
-              f"{done} steps timed")
+    kind = "reference" if ref_pd is not None else "port"
+    sample = (f"{n_seq} sequence(s) x context {CONTEXT} per step (of the 32 in the workload), "
+              f"{done} steps timed, " +
+              ("the reference's own split_k_paged_decode CPU branch (Python loop per token and "
+               "KV head)" if ref_pd is not None else "vectorised oracle restatement"))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": done, "warmup": args.warmup, "ms_per_step": dt / done * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+                         "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -598,6 +902,15 @@ def run_cache(args):
     }), flush=True)
 
 
+def _recorded_traffic():
+    """DRAM bytes per decode launch from the last ncu capture, recorded next to its summary."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", "decode_traffic.json")))
+        return float(rec["dram_bytes_per_launch"])
+    except Exception:
+        return None
+
+
 def _peaks():
     try:
         return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -616,9 +929,13 @@ def main():
                     help="decode is the headline; the others time further rows on one GPU")
     ap.add_argument("--prefill-batch", type=int, default=4)
     ap.add_argument("--prefill-seq", type=int, default=8192)
-    ap.add_argument("--traffic", type=float, default=148.76e6,
-                    help="DRAM bytes per launch of the decode kernel (dram read + write) from "
-                         "the ncu capture summarised in profiles/paged_decode_kernel_config1.md")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the decode kernel (dram read + write of one "
+                         "ncu capture); default: the figure recorded in "
+                         "profiles/decode_traffic.json, null if that file is missing")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the secondary blocks of the line (append, prefill, decompress, "
+                         "multi-token, long-context)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

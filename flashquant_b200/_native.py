@@ -62,6 +62,7 @@ SIGNATURES = {
     "fq_workspace_status": (_i, [_p, _p, _p]),
     "fq_tq4_compress_into": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _i64, _i64, _i64, _i64, _i, _p]),
     "fq_split_k_paged_decode_multi_scratch_bytes": (_sz, [_i, _i, _i]),
+    "fq_split_k_paged_decode_multi_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "fq_split_k_paged_decode_multi": (_i, [_p, _i, _p, _p, _i64, _i, _p, _p, _i, _p, _i, _p, _i, _i,
                                            _i, _i, _i, _i, _i64, _f, _p, _i, _p, _sz, _p, _sz, _p]),
     "fq_pack_2bit": (_i, [_p, _p, _i64, _p, _p]),

@@ -334,6 +334,18 @@ struct RowMap {
   }
 };
 
+// paged_decode.cu: the decode call for n_q query tokens per sequence in one pass (q and out
+// (num_seqs, n_q, H_q, D); query token i sees keys 0 .. seq_len - n_q + i), and how many
+// tokens a pass can take for a given geometry
+int decode_tokens_per_pass(int num_q_heads, int num_kv_heads, int head_dim, int block_size);
+int decode_tokens(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                  const int32_t* block_table, int64_t block_table_stride, const int32_t* seq_lens,
+                  const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                  int n_centroids_v, const float* rotation, int num_seqs, int n_q, int num_q_heads,
+                  int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+                  float sm_scale, void* out, int num_splits, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream);
+
 // rotate.cu: row rotations around the prefill kernel
 int rotate_q_to_half(const void* q, int dtype, const float* rotation, __half* out,
                      int64_t n_rows, int head_dim, cudaStream_t stream);

@@ -1925,7 +1925,7 @@ static int decode_call(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                        int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                        int block_size, int64_t num_blocks, float sm_scale, void* out,
                        int num_splits, void* workspace, size_t workspace_bytes,
-                       cudaStream_t stream);
+                       cudaStream_t stream, int n_q = 1);
 
 extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                                        const int32_t* block_table, int64_t block_table_stride,
@@ -1952,7 +1952,10 @@ static int decode_call(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                        int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                        int block_size, int64_t num_blocks, float sm_scale, void* out,
                        int num_splits, void* workspace, size_t workspace_bytes,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int n_q) {
+  // n_q > 1: every sequence brings n_q query tokens, q and out are (num_seqs, n_q, H_q, D) and
+  // num_q_heads counts the heads of ONE token (fast path only, see decode_tokens_per_pass)
+  const int q_rows = num_q_heads * n_q;
   int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
                            centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                            num_kv_heads, head_dim, block_size, num_blocks, num_splits);
@@ -1965,23 +1968,49 @@ static int decode_call(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   // query is not rounded (it meets the keys as fp16), its output is not rounded either
   if (g_single_launch.load(std::memory_order_relaxed) && dtype != FQ_F32) {
     rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, q_rows,
                       num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
-                      workspace, workspace_bytes, ctas, stream, out);
+                      workspace, workspace_bytes, ctas, stream, out, nullptr, nullptr, n_q);
     if (rc != kCoopRefused) return rc;
   }
   // three launches: q rotation, streaming, merge (no CTA waits for another one)
   rc = decode_front(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
-                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                    n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, q_rows,
                     num_kv_heads, head_dim, block_size, num_blocks, sm_scale, num_splits,
-                    workspace, workspace_bytes, ctas, stream);
+                    workspace, workspace_bytes, ctas, stream, nullptr, nullptr, nullptr, n_q);
   if (rc != FQ_OK) return rc;
-  MergeArgs m = slot_merge_args(workspace, num_seqs, num_q_heads, num_kv_heads, head_dim,
+  MergeArgs m = slot_merge_args(workspace, num_seqs, q_rows, num_kv_heads, head_dim,
                                 num_splits, ctas, seq_lens, block_size, block_table_stride);
   m.rotation = rotation;
   m.out = out;
   return launch_merge<true, true>(m, head_dim, dtype, stream);
 }
+
+namespace fq {
+// How many query tokens of a sequence one pass of the decode can take together: the (token,
+// head) pairs of a KV head are the eight columns of its products, so 8 / (heads per KV head)
+// where the specialised kernel applies, else 1.
+int decode_tokens_per_pass(int num_q_heads, int num_kv_heads, int head_dim, int block_size) {
+  if (num_kv_heads < 1 || num_q_heads % num_kv_heads) return 1;
+  const int group = num_q_heads / num_kv_heads;
+  if (group > 8 || !fast_path_fits(num_q_heads, 1, num_kv_heads, head_dim, block_size, false))
+    return 1;
+  return 8 / group;
+}
+
+int decode_tokens(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                  const int32_t* block_table, int64_t block_table_stride, const int32_t* seq_lens,
+                  const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                  int n_centroids_v, const float* rotation, int num_seqs, int n_q, int num_q_heads,
+                  int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+                  float sm_scale, void* out, int num_splits, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream) {
+  return decode_call(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
+                     n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
+                     num_kv_heads, head_dim, block_size, num_blocks, sm_scale, out, num_splits,
+                     workspace, workspace_bytes, stream, n_q);
+}
+}  // namespace fq
 
 extern "C" void fq_paged_decode_set_single_launch(int enabled) {
   g_single_launch.store(enabled ? 1 : 0, std::memory_order_relaxed);

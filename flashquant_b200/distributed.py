@@ -69,6 +69,6 @@ def cross_gpu_decode(partial_fn: Callable[[], torch.Tensor],
     part = partial_fn().contiguous()
     world = dist.get_world_size(group)
     gathered = torch.empty((world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
-    # views of one buffer: a single collective, and the result is already in merge layout
-    dist.all_gather(list(gathered.unbind(0)), part, group=group)
+    # one collective into one buffer: the result is already in merge layout
+    dist.all_gather_into_tensor(gathered, part, group=group)
     return merge_fn(gathered)

@@ -366,11 +366,11 @@ _workspaces = {}
 
 
 def decode_workspace(device, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int,
-                     num_splits: int) -> torch.Tensor:
+                     num_splits: int, min_bytes: int = 0) -> torch.Tensor:
     """A zero-initialised, cached workspace tensor large enough for the given decode shape."""
     lib = N.load()
-    need = lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                               num_splits)
+    need = max(min_bytes, lib.fq_paged_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads,
+                                                              head_dim, num_splits))
     # one workspace per (device, stream): calls on different streams may overlap on the GPU
     # and must not share counters or partial rows
     key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
@@ -488,7 +488,10 @@ def split_k_paged_decode_multi(q, kv_cache, block_table, seq_lens, centroids_k, 
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(head_dim)
     lib = N.load()
-    workspace = decode_workspace(dev, num_seqs * n_q, hq, num_kv_heads, d, num_splits)
+    need_ws = lib.fq_split_k_paged_decode_multi_workspace_bytes(num_seqs, n_q, hq, num_kv_heads, d,
+                                                                int(num_splits))
+    workspace = decode_workspace(dev, num_seqs * n_q, hq, num_kv_heads, d, num_splits,
+                                 min_bytes=need_ws)
     max_blocks = block_table.shape[1]
     need = lib.fq_split_k_paged_decode_multi_scratch_bytes(num_seqs, n_q, max_blocks)
     scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)

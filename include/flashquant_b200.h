@@ -266,15 +266,23 @@ int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint8_t* kv_cac
  * varlen attention (impl.py:265-336, 477-509).  Here the last n_q tokens of every sequence,
  * already appended to the cache and counted in seq_lens, attend in one decode launch: query i
  * of a sequence sees keys 0 .. seq_len - n_q + i (a query without a visible key gives zeros).
+ * Where the specialised kernel applies (head_dim 128, 8 KV heads, pages of 16 tokens) the
+ * (token, head) pairs of a KV head share the eight columns of its products: with 4 query heads
+ * per KV head two tokens are served by ONE pass over the sequence's pages, and a step of
+ * n_q tokens takes n_q / 2 passes instead of n_q.
  *   q, out        (num_seqs, n_q, num_q_heads, head_dim)
  *   block_table   (num_seqs, block_table_stride) int32, max_blocks (<= stride) columns used
  *   scratch       caller-owned, 16-byte aligned, fq_split_k_paged_decode_multi_scratch_bytes(...)
  *                 bytes: the per-(sequence, token) lengths and block-table rows a small kernel
  *                 writes before the decode
- * num_seqs * n_q <= 2048; workspace as for fq_split_k_paged_decode with num_seqs * n_q rows;
- * everything else as fq_split_k_paged_decode.
+ * num_seqs * n_q <= 2048; workspace as for fq_split_k_paged_decode, at least
+ * fq_split_k_paged_decode_multi_workspace_bytes(...) bytes; everything else as
+ * fq_split_k_paged_decode.
  */
 size_t fq_split_k_paged_decode_multi_scratch_bytes(int num_seqs, int n_q, int max_blocks);
+size_t fq_split_k_paged_decode_multi_workspace_bytes(int num_seqs, int n_q, int num_q_heads,
+                                                     int num_kv_heads, int head_dim,
+                                                     int num_splits);
 int fq_split_k_paged_decode_multi(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
                                   const int32_t* block_table, int64_t block_table_stride,
                                   int max_blocks, const int32_t* seq_lens,

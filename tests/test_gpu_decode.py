@@ -390,7 +390,8 @@ def test_three_launch_form_gives_the_same_answer(consts):
 
 
 @pytest.mark.parametrize("n_q,lens", [(4, [0, 1, 3, 4, 5, 64, 301, 1000]), (2, [17, 2048]),
-                                      (1, [9, 300])])
+                                      (1, [9, 300]), (3, [2, 40, 33, 700]),
+                                      (2, [0, 1, 2, 15, 16, 17, 18, 31, 32, 33])])
 def test_multi_token_steps_vs_oracle(consts, n_q, lens):
     # the last n_q tokens of every sequence in one call: query i sees keys 0 .. L - n_q + i;
     # sequences shorter than n_q have queries without any key (zeros)
