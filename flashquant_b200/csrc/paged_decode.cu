@@ -1048,6 +1048,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
           qf[s][0] = valid ? v.x : 0u;
           qf[s][1] = valid ? v.y : 0u;
         }
+        // the loads must have delivered before the buffer goes back to the producer: a load in
+        // flight is not ordered before the arrive by anything else
+        __threadfence_block();
         __syncwarp();
         if (lane == 0) mbar_arrive(qempty_bar);
         ++qcnt;
@@ -1281,6 +1284,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       }
     }
 
+    __threadfence_block();  // as for the query buffer: loads from the stage delivered, then release
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar + stage);
     if (++stage == stages) { stage = 0; fphase ^= 1; }

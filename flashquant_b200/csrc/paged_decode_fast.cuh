@@ -723,6 +723,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
             qf[s][0] = col_ok ? v.x : 0u;
             qf[s][1] = col_ok ? v.y : 0u;
           }
+          // The loads above must have delivered before the buffer is handed back: nothing else
+          // orders a shared-memory load that is still in flight before the arrive, and the
+          // producer's next copy may land on the buffer as soon as the eighth warp has arrived.
+          __threadfence_block();
           __syncwarp();
           if (lane == 0) mbar_arrive_s(qempty);
           ++qcnt;
@@ -732,7 +736,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       FQ_ACC(pf_q, cc, cb);
       FastMid mid;
       fast_front<KPRMT>(w, raw, ring + uint32_t(stage) * kFStage, qf, mid);
-      // every value read from the stage has been used in an instruction above: release it
+      // every load from the stage has been issued above; the fence makes them deliver before
+      // the stage goes back to the producers (costs nothing measurable: they are long done)
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) mbar_arrive_s(empty + stage * 8);
       if (++stage == stages) { stage = 0; fphase ^= 1; }

@@ -164,6 +164,23 @@ def test_partials_then_merge_equals_fused_call(consts):
     assert (merged[3] == 0).all()
 
 
+def test_short_runs_that_cross_sequences_repeat_bit_for_bit(consts):
+    """637 pages over 296 page runs: runs of two or three pages, several of them with the end
+    of one sequence and the start of the next, so a team switches its query while the first
+    one's tile is still being computed.  The partial rows must not depend on timing."""
+    w = W.decode_workload(seq_lens=[10000, 173, 16], cfg=23)
+    cache = fill_cache_cpu(w, consts)
+    rot = consts["rotation_128_0"]
+    args = (w.q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+            consts["centroids_128_3"], consts["centroids_128_4"], rot, 8, 128, 16)
+    first = K.paged_decode_partials(*args, num_splits=1).clone()
+    for _ in range(40):
+        again = K.paged_decode_partials(*args, num_splits=1)
+        assert torch.equal(first, again)
+    merged = K.split_k_merge(first, rot, torch.bfloat16)
+    close(merged, run_oracle(w, cache, consts), consts, got_rot32=rows_from_partials(first))
+
+
 def test_token_ranges_on_two_groups_merge_like_one(consts):
     """What a cross-GPU split does: group 0 attends over the first pages of every sequence,
     group 1 over the rest; merging the two partial rows equals attending over everything."""
