@@ -22,6 +22,7 @@ extern "C" int fq_cache_update(
     uint8_t* v_packed, float* v_norms, int64_t n_segments, int64_t n_new, int64_t capacity,
     int64_t position, void* k_out, void* v_out, int64_t out_capacity, int64_t out_position,
     int head_dim, void* workspace, size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_cache_update");
   FQ_REQUIRE(n_segments >= 0 && n_new >= 0 && capacity >= 0 && position >= 0,
              FQ_ERR_INVALID_ARGUMENT, "fq_cache_update: negative size");
   FQ_REQUIRE(position + n_new <= capacity, FQ_ERR_INVALID_ARGUMENT,

@@ -862,6 +862,7 @@ extern "C" int fq_tq4_compress(const void* x, fq_dtype dtype, const float* rot_T
                                const float* rot_T_odd, const float* boundaries,
                                int n_boundaries, uint8_t* packed, float* norms,
                                int64_t n_vectors, int head_dim, fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_compress");
   FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
   if (n_vectors == 0) return FQ_OK;
   FQ_REQUIRE(x && rot_T_even && rot_T_odd && boundaries && packed && norms,
@@ -885,6 +886,7 @@ extern "C" int fq_tq4_compress_into(const void* x, fq_dtype dtype, const float* 
                                     int n_boundaries, uint8_t* packed, float* norms,
                                     int64_t n_segments, int64_t n_new, int64_t capacity,
                                     int64_t position, int head_dim, fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_compress_into");
   FQ_REQUIRE(n_segments >= 0 && n_new >= 0 && capacity >= 0 && position >= 0,
              FQ_ERR_INVALID_ARGUMENT, "fq_tq4_compress_into: negative size");
   FQ_REQUIRE(position + n_new <= capacity, FQ_ERR_INVALID_ARGUMENT,
@@ -915,6 +917,7 @@ extern "C" int fq_tq_prod_quantize(const void* x, fq_dtype dtype, const float* r
                                    const float* centroids, const float* qjl, uint8_t* packed,
                                    float* norms, uint8_t* sign_bits, float* gamma,
                                    int64_t n_vectors, int head_dim, fq_stream_t stream) {
+  FQ_RANGE("fq_tq_prod_quantize");
   FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
   if (n_vectors == 0) return FQ_OK;
   FQ_REQUIRE(x && rotation && boundaries && centroids && qjl && packed && norms && sign_bits &&
@@ -995,6 +998,7 @@ extern "C" int fq_tq4_compress_append(const void* key, const void* value, fq_dty
                                       uint8_t* kv_cache, int64_t num_slots,
                                       const void* slot_mapping, int slot_is_int64,
                                       fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_compress_append");
   return append_common(key, value, dtype, n_tokens, num_kv_heads, head_dim, token_stride,
                        rotation, boundaries_k, n_boundaries_k, nullptr, boundaries_v,
                        n_boundaries_v, nullptr, kv_cache, nullptr, num_slots, slot_mapping,
@@ -1007,6 +1011,7 @@ extern "C" int fq_tq4_compress_append_qjl(
     int n_boundaries_k, const float* centroids_k, const float* boundaries_v, int n_boundaries_v,
     const float* qjl, uint8_t* kv_cache, uint8_t* kq_cache, int64_t num_slots,
     const void* slot_mapping, int slot_is_int64, fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_compress_append_qjl");
   return append_common(key, value, dtype, n_tokens, num_kv_heads, head_dim, token_stride,
                        rotation, boundaries_k, n_boundaries_k, centroids_k, boundaries_v,
                        n_boundaries_v, qjl, kv_cache, kq_cache, num_slots, slot_mapping,

@@ -65,6 +65,7 @@ extern "C" int fq_split_k_paged_decode_multi(
     int head_dim, int block_size, int64_t num_blocks, float sm_scale, void* out, int num_splits,
     void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
     fq_stream_t stream) {
+  FQ_RANGE("fq_split_k_paged_decode_multi");
   FQ_REQUIRE(num_seqs >= 0 && n_q >= 0 && max_blocks >= 0, FQ_ERR_INVALID_ARGUMENT,
              "multi-token decode: negative size");
   const int64_t rows = int64_t(num_seqs) * n_q;

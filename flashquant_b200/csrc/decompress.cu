@@ -98,6 +98,7 @@ extern "C" int fq_tq4_decompress(const uint8_t* packed, const float* norms,
                                  const float* centroids, int n_centroids, void* out,
                                  fq_dtype out_dtype, int64_t n_vectors, int head_dim,
                                  fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_decompress");
   return decompress_rows(packed, norms, centroids, n_centroids, out, int(out_dtype), n_vectors,
                          head_dim, RowMap(), stream);
 }
@@ -116,6 +117,7 @@ extern "C" int fq_tq4_decompress_original(const uint8_t* packed, const float* no
                                           const float* rotation, void* out, fq_dtype out_dtype,
                                           int64_t n_vectors, int head_dim, void* workspace,
                                           size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_tq4_decompress_original");
   FQ_REQUIRE(n_vectors >= 0, FQ_ERR_INVALID_ARGUMENT, "n_vectors is negative");
   if (n_vectors == 0) return FQ_OK;
   FQ_REQUIRE(rotation && out, FQ_ERR_INVALID_ARGUMENT, "fq_tq4_decompress_original: null pointer");

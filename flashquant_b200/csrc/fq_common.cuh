@@ -2,6 +2,7 @@
 // mbarrier / bulk-copy PTX wrappers with bounded waits, warp-level MMA wrappers.
 #pragma once
 
+#include <nvtx3/nvToolsExt.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -40,6 +41,17 @@ inline int check_launch(const char* what) {
   do {                                           \
     if (!(cond)) return fq::fail(code, __VA_ARGS__); \
   } while (0)
+
+// A named range around every launcher, for timeline tools (the reference wraps its dispatchers
+// the same way: src/flashquant/profiling.py:31-82).  Without a tool attached the calls are
+// no-ops of the header-only NVTX layer.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+#define FQ_RANGE(name) fq::NvtxRange fq_nvtx_range_(name)
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

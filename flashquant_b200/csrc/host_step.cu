@@ -3,14 +3,19 @@
 //
 // Mirrors FlashQuantAttentionImpl._fused_decode_path (src/flashquant/vllm/impl.py:362-395):
 // compress the step's new K/V token of every sequence into the paged cache, then run the
-// fused paged decode.  Around those two launches this entry point does the copies itself -
-// six host-to-device copies into a caller-owned device staging area (those that only the
-// decode needs go through a side stream and overlap the compress-on-append), one
-// device-to-host copy of the result - and waits for the stream, so that one C call is the
-// whole step and no interpreter time sits between the pieces.  (Letting the kernels read page-locked host
-// arrays in place was measured and is slower: the sequence lengths and the block table sit
-// at the head of the decode kernel's dependency chain, and every CTA would fetch them over
-// the bus.)
+// fused paged decode.  Around those two launches the entry points here do the copies
+// themselves and wait for the stream, so that one C call is the whole step and no interpreter
+// time sits between the pieces.  Two forms:
+//   fq_decode_step_host         six host arrays, six host-to-device copies into a caller-owned
+//                               device staging area (those that only the decode needs go
+//                               through a side stream and overlap the compress-on-append);
+//   fq_decode_step_host_packed  the caller keeps the step's inputs in ONE page-locked block
+//                               laid out like the staging area (fq_decode_step_offsets), and
+//                               the step is one copy in - or two halves of the block, the
+//                               second under the compress-on-append - and one copy out.
+// (Letting the kernels read page-locked host arrays in place was measured and is slower: the
+// sequence lengths and the block table sit at the head of the decode kernel's dependency
+// chain, and every CTA would fetch them over the bus.)
 #include <mutex>
 
 #include "fq_common.cuh"
@@ -47,8 +52,10 @@ static int step_aux(StepAux** out) {
   return FQ_OK;
 }
 
+// Inputs of the compress-on-append first, then what only the decode reads, then the result:
+// the packed form copies [k, sl) and [sl, out) as two contiguous halves.
 struct StepLayout {
-  size_t q, k, v, slots, bt, sl, out, total;
+  size_t k, v, slots, sl, bt, q, out, total;
 };
 
 static size_t up256_(size_t v) { return (v + 255) / 256 * 256; }
@@ -62,15 +69,69 @@ static StepLayout step_layout(int num_seqs, int hq, int hkv, int d, int64_t bt_s
     off = up256_(off + bytes);
     return at;
   };
-  L.q = take(size_t(num_seqs) * hq * d * 2);
   L.k = take(size_t(num_seqs) * hkv * d * 2);
   L.v = take(size_t(num_seqs) * hkv * d * 2);
   L.slots = take(size_t(num_seqs) * (slot_is_int64 ? 8 : 4));
-  L.bt = take(size_t(num_seqs) * size_t(bt_stride) * 4);
   L.sl = take(size_t(num_seqs) * 4);
+  L.bt = take(size_t(num_seqs) * size_t(bt_stride) * 4);
+  L.q = take(size_t(num_seqs) * hq * d * 2);
   L.out = take(size_t(num_seqs) * hq * d * 2);
   L.total = off;
   return L;
+}
+
+}  // namespace fq
+
+namespace fq {
+
+// The two launches and the copy of the result back to the host, on inputs that the copies
+// issued before have put (or are putting: `join_side`) into the staging area.
+static int step_kernels_and_result(
+    const StepLayout& L, unsigned char* st, StepAux* aux, fq_dtype dtype, int slot_is_int64,
+    int64_t block_table_stride, uint8_t* kv_cache, uint8_t* kq_cache, const float* rotation,
+    const float* boundaries_k, int n_boundaries_k, const float* centroids_k, int n_centroids_k,
+    const float* boundaries_v, int n_boundaries_v, const float* centroids_v, int n_centroids_v,
+    const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+    int block_size, int64_t num_blocks, float sm_scale, int num_splits, void* out_host,
+    void* workspace, size_t workspace_bytes, fq_stream_t stream_, bool join_side) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t n = size_t(num_seqs);
+  int rc = FQ_OK;
+  const void *q_d = st + L.q, *k_d = st + L.k, *v_d = st + L.v, *slots_d = st + L.slots;
+  const void *bt_d = st + L.bt, *sl_d = st + L.sl;
+  void* out_d = st + L.out;
+  const int64_t num_slots = num_blocks * block_size;
+  if (kq_cache) {
+    rc = fq_tq4_compress_append_qjl(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
+                                    int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
+                                    n_boundaries_k, centroids_k, boundaries_v, n_boundaries_v, qjl,
+                                    kv_cache, kq_cache, num_slots, slots_d, slot_is_int64,
+                                    stream_);
+  } else {
+    rc = fq_tq4_compress_append(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
+                                int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
+                                n_boundaries_k, boundaries_v, n_boundaries_v, kv_cache, num_slots,
+                                slots_d, slot_is_int64, stream_);
+  }
+  if (rc != FQ_OK) return rc;
+  if (join_side) {
+    cudaError_t ce = cudaStreamWaitEvent(stream, aux->join, 0);
+    if (ce != cudaSuccess)
+      return fail(FQ_ERR_CUDA, "decode step: joining the side stream: %s", cudaGetErrorString(ce));
+  }
+  rc = fq_split_k_paged_decode(q_d, dtype, kv_cache, static_cast<const int32_t*>(bt_d),
+                               block_table_stride, static_cast<const int32_t*>(sl_d), centroids_k,
+                               n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs,
+                               num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
+                               sm_scale, out_d, num_splits, workspace, workspace_bytes,
+                               stream_);
+  if (rc != FQ_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(out_host, out_d, n * num_q_heads * head_dim * 2,
+                                  cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "decode step: result copy or synchronise: %s", cudaGetErrorString(e));
+  return FQ_OK;
 }
 
 }  // namespace fq
@@ -98,6 +159,7 @@ extern "C" int fq_decode_step_host(
     int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
     float sm_scale, int num_splits, void* out_host, void* staging, size_t staging_bytes,
     void* workspace, size_t workspace_bytes, fq_stream_t stream_) {
+  FQ_RANGE("fq_decode_step_host");
   FQ_REQUIRE(q_host && key_host && value_host && slot_mapping_host && block_table_host &&
                  seq_lens_host && out_host,
              FQ_ERR_INVALID_ARGUMENT, "decode step: null host pointer");
@@ -144,37 +206,81 @@ extern "C" int fq_decode_step_host(
   if (ce == cudaSuccess) ce = cudaEventRecord(aux->join, aux->stream);
   if (ce != cudaSuccess)
     return fail(FQ_ERR_CUDA, "decode step: host-to-device copies: %s", cudaGetErrorString(ce));
-  const void *q_d = st + L.q, *k_d = st + L.k, *v_d = st + L.v, *slots_d = st + L.slots;
-  const void *bt_d = st + L.bt, *sl_d = st + L.sl;
-  void* out_d = st + L.out;
-  const int64_t num_slots = num_blocks * block_size;
-  if (kq_cache) {
-    rc = fq_tq4_compress_append_qjl(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
-                                    int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
-                                    n_boundaries_k, centroids_k, boundaries_v, n_boundaries_v, qjl,
-                                    kv_cache, kq_cache, num_slots, slots_d, slot_is_int64,
-                                    stream_);
-  } else {
-    rc = fq_tq4_compress_append(k_d, v_d, dtype, num_seqs, num_kv_heads, head_dim,
-                                int64_t(num_kv_heads) * head_dim, rotation, boundaries_k,
-                                n_boundaries_k, boundaries_v, n_boundaries_v, kv_cache, num_slots,
-                                slots_d, slot_is_int64, stream_);
-  }
-  if (rc != FQ_OK) return rc;
-  ce = cudaStreamWaitEvent(stream, aux->join, 0);
-  if (ce != cudaSuccess)
-    return fail(FQ_ERR_CUDA, "decode step: joining the side stream: %s", cudaGetErrorString(ce));
-  rc = fq_split_k_paged_decode(q_d, dtype, kv_cache, static_cast<const int32_t*>(bt_d),
-                               block_table_stride, static_cast<const int32_t*>(sl_d), centroids_k,
-                               n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs,
-                               num_q_heads, num_kv_heads, head_dim, block_size, num_blocks,
-                               sm_scale, out_d, num_splits, workspace, workspace_bytes,
-                               stream_);
-  if (rc != FQ_OK) return rc;
-  cudaError_t e = cudaMemcpyAsync(out_host, out_d, n * num_q_heads * head_dim * 2,
-                                  cudaMemcpyDeviceToHost, stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-  if (e != cudaSuccess)
-    return fail(FQ_ERR_CUDA, "decode step: result copy or synchronise: %s", cudaGetErrorString(e));
+  return step_kernels_and_result(L, st, aux, dtype, slot_is_int64, block_table_stride, kv_cache,
+                                 kq_cache, rotation, boundaries_k, n_boundaries_k, centroids_k,
+                                 n_centroids_k, boundaries_v, n_boundaries_v, centroids_v,
+                                 n_centroids_v, qjl, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                 block_size, num_blocks, sm_scale, num_splits, out_host, workspace,
+                                 workspace_bytes, stream_, true);
+}
+
+extern "C" int fq_decode_step_offsets(int num_seqs, int num_q_heads, int num_kv_heads,
+                                      int head_dim, int64_t block_table_stride,
+                                      int slot_is_int64, uint64_t offsets[8]) {
+  FQ_REQUIRE(offsets, FQ_ERR_INVALID_ARGUMENT, "decode step: null offsets array");
+  FQ_REQUIRE(num_seqs >= 0 && num_q_heads >= 1 && num_kv_heads >= 1 && head_dim >= 1 &&
+                 block_table_stride >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "decode step: negative size");
+  const StepLayout L = step_layout(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                   block_table_stride, slot_is_int64);
+  offsets[0] = L.k;
+  offsets[1] = L.v;
+  offsets[2] = L.slots;
+  offsets[3] = L.sl;
+  offsets[4] = L.bt;
+  offsets[5] = L.q;
+  offsets[6] = L.out;
+  offsets[7] = L.total;
   return FQ_OK;
+}
+
+extern "C" int fq_decode_step_host_packed(
+    const void* block_host, void* out_host, int overlap_copies, fq_dtype dtype, int slot_is_int64,
+    int64_t block_table_stride, uint8_t* kv_cache, uint8_t* kq_cache, const float* rotation,
+    const float* boundaries_k, int n_boundaries_k, const float* centroids_k, int n_centroids_k,
+    const float* boundaries_v, int n_boundaries_v, const float* centroids_v, int n_centroids_v,
+    const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+    int block_size, int64_t num_blocks, float sm_scale, int num_splits, void* staging,
+    size_t staging_bytes, void* workspace, size_t workspace_bytes, fq_stream_t stream_) {
+  FQ_RANGE("fq_decode_step_host_packed");
+  FQ_REQUIRE(block_host && out_host, FQ_ERR_INVALID_ARGUMENT, "decode step: null host pointer");
+  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
+             "decode step: q, key and value must be fp16 or bf16");
+  FQ_REQUIRE(num_seqs >= 0 && num_q_heads >= 1 && num_kv_heads >= 1 && head_dim >= 1 &&
+                 block_table_stride >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "decode step: negative size");
+  FQ_REQUIRE(staging && aligned(staging, 256), FQ_ERR_WORKSPACE,
+             "decode step: staging is null or not 256-byte aligned");
+  const StepLayout L = step_layout(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                   block_table_stride, slot_is_int64);
+  FQ_REQUIRE(staging_bytes >= L.total, FQ_ERR_WORKSPACE,
+             "decode step: staging has %zu bytes, %zu needed", staging_bytes, L.total);
+  if (num_seqs == 0) return FQ_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  unsigned char* st = static_cast<unsigned char*>(staging);
+  const unsigned char* src = static_cast<const unsigned char*>(block_host);
+  StepAux* aux = nullptr;
+  cudaError_t ce = cudaSuccess;
+  if (overlap_copies) {
+    // what the compress-on-append reads on the caller's stream, the rest on the side stream
+    int rc = step_aux(&aux);
+    if (rc != FQ_OK) return rc;
+    ce = cudaEventRecord(aux->fork, stream);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(aux->stream, aux->fork, 0);
+    if (ce == cudaSuccess)
+      ce = cudaMemcpyAsync(st + L.sl, src + L.sl, L.out - L.sl, cudaMemcpyHostToDevice, aux->stream);
+    if (ce == cudaSuccess) ce = cudaEventRecord(aux->join, aux->stream);
+    if (ce == cudaSuccess)
+      ce = cudaMemcpyAsync(st + L.k, src + L.k, L.sl - L.k, cudaMemcpyHostToDevice, stream);
+  } else {
+    ce = cudaMemcpyAsync(st, src, L.out, cudaMemcpyHostToDevice, stream);
+  }
+  if (ce != cudaSuccess)
+    return fail(FQ_ERR_CUDA, "decode step: host-to-device copy: %s", cudaGetErrorString(ce));
+  return step_kernels_and_result(L, st, aux, dtype, slot_is_int64, block_table_stride, kv_cache,
+                                 kq_cache, rotation, boundaries_k, n_boundaries_k, centroids_k,
+                                 n_centroids_k, boundaries_v, n_boundaries_v, centroids_v,
+                                 n_centroids_v, qjl, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                 block_size, num_blocks, sm_scale, num_splits, out_host, workspace,
+                                 workspace_bytes, stream_, overlap_copies != 0);
 }

@@ -60,6 +60,7 @@ using namespace fq;
 
 extern "C" int fq_pack_2bit(const uint8_t* codes, uint8_t* packed, int64_t n_codes,
                             uint32_t* out_of_range, fq_stream_t stream) {
+  FQ_RANGE("fq_pack_2bit");
   FQ_REQUIRE(n_codes >= 0 && n_codes % 16 == 0, FQ_ERR_INVALID_ARGUMENT,
              "fq_pack_2bit: %lld codes (a multiple of 16 is needed)", (long long)n_codes);
   if (n_codes == 0) return FQ_OK;
@@ -74,6 +75,7 @@ extern "C" int fq_pack_2bit(const uint8_t* codes, uint8_t* packed, int64_t n_cod
 
 extern "C" int fq_unpack_2bit(const uint8_t* packed, uint8_t* codes, int64_t n_codes,
                               fq_stream_t stream) {
+  FQ_RANGE("fq_unpack_2bit");
   FQ_REQUIRE(n_codes >= 0 && n_codes % 16 == 0, FQ_ERR_INVALID_ARGUMENT,
              "fq_unpack_2bit: %lld codes (a multiple of 16 is needed)", (long long)n_codes);
   if (n_codes == 0) return FQ_OK;

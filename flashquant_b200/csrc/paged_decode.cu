@@ -1940,6 +1940,7 @@ extern "C" int fq_split_k_paged_decode(const void* q, fq_dtype dtype, const uint
                                        int block_size, int64_t num_blocks, float sm_scale,
                                        void* out, int num_splits, void* workspace,
                                        size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_split_k_paged_decode");
   return decode_call(q, dtype, kv_cache, block_table, block_table_stride, seq_lens, centroids_k,
                      n_centroids_k, centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                      num_kv_heads, head_dim, block_size, num_blocks, sm_scale, out, num_splits,
@@ -2039,6 +2040,7 @@ extern "C" int fq_split_k_paged_decode_qjl(
     const float* rotation, const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads,
     int head_dim, int block_size, int64_t num_blocks, float sm_scale, void* out, int num_splits,
     void* workspace, size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_split_k_paged_decode_qjl");
   int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
                            centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                            num_kv_heads, head_dim, block_size, num_blocks, num_splits);
@@ -2100,6 +2102,7 @@ extern "C" int fq_paged_decode_partials(const void* q, fq_dtype dtype, const uin
                                         int block_size, int64_t num_blocks, float sm_scale,
                                         int num_splits, float* partials, void* workspace,
                                         size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_paged_decode_partials");
   int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
                            centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                            num_kv_heads, head_dim, block_size, num_blocks, num_splits);
@@ -2117,6 +2120,7 @@ extern "C" int fq_paged_decode_partials_rotated(
     int num_kv_heads, int head_dim, int block_size, int64_t num_blocks, float sm_scale,
     int num_splits, float* partials, void* workspace, size_t workspace_bytes,
     fq_stream_t stream) {
+  FQ_RANGE("fq_paged_decode_partials_rotated");
   alignas(16) static const float kDummy[4] = {0.f, 0.f, 0.f, 0.f};  // validate wants non-null
   int rc = validate_decode(q_rot_f16, FQ_F16, kv_cache, block_table, seq_lens, centroids_k,
                            n_centroids_k, centroids_v, n_centroids_v, kDummy, num_seqs,
@@ -2138,6 +2142,7 @@ extern "C" int fq_paged_decode_stream(const void* q_rot_f16, const uint8_t* kv_c
                                       int64_t num_blocks, float sm_scale, int num_splits,
                                       void* workspace, size_t workspace_bytes,
                                       fq_stream_t stream) {
+  FQ_RANGE("fq_paged_decode_stream");
   alignas(16) static const float kDummy[4] = {0.f, 0.f, 0.f, 0.f};  // validate wants non-null
   int rc = validate_decode(q_rot_f16, FQ_F16, kv_cache, block_table, seq_lens, centroids_k,
                            n_centroids_k, centroids_v, n_centroids_v, kDummy, num_seqs,
@@ -2155,6 +2160,7 @@ extern "C" int fq_paged_decode_stream(const void* q_rot_f16, const uint8_t* kv_c
 extern "C" int fq_split_k_merge(const float* partials, int n_groups, const float* rotation,
                                 int num_seqs, int num_q_heads, int head_dim, void* out,
                                 fq_dtype dtype, fq_stream_t stream) {
+  FQ_RANGE("fq_split_k_merge");
   FQ_REQUIRE(partials && rotation && out, FQ_ERR_INVALID_ARGUMENT, "fq_split_k_merge: null pointer");
   FQ_REQUIRE(n_groups >= 1 && n_groups <= kMaxParts && num_seqs >= 0 && num_q_heads >= 1,
              FQ_ERR_INVALID_ARGUMENT, "fq_split_k_merge: bad size");
@@ -2234,6 +2240,7 @@ extern "C" int fq_split_k_paged_decode_static(
     int n_centroids_k, const float* centroids_v, int n_centroids_v, const float* rotation,
     int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
     int64_t num_blocks, float sm_scale, void* out, int num_splits, fq_stream_t stream) {
+  FQ_RANGE("fq_split_k_paged_decode_static");
   int rc = validate_decode(q, dtype, kv_cache, block_table, seq_lens, centroids_k, n_centroids_k,
                            centroids_v, n_centroids_v, rotation, num_seqs, num_q_heads,
                            num_kv_heads, head_dim, block_size, num_blocks, num_splits);

@@ -740,6 +740,7 @@ extern "C" int fq_fused_tq_attention(const void* q, fq_dtype dtype, const uint8_
                                      int head_dim, float sm_scale, int is_causal, void* out,
                                      void* workspace, size_t workspace_bytes,
                                      fq_stream_t stream) {
+  FQ_RANGE("fq_fused_tq_attention");
   return attention_common(q, dtype, k_packed, k_norms, v_packed, v_norms, centroids_k,
                           n_centroids_k, centroids_v, n_centroids_v, rotation, rotation, batch,
                           num_q_heads, num_kv_heads, n_q, n_kv, n_kv, head_dim, sm_scale,
@@ -756,6 +757,7 @@ extern "C" int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uin
                                         int64_t kv_capacity, int head_dim, float sm_scale,
                                         int is_causal, void* out, void* workspace,
                                         size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_fused_tq_attention_kv");
   return attention_common(q, dtype, k_packed, k_norms, v_packed, v_norms, centroids_k,
                           n_centroids_k, centroids_v, n_centroids_v, rotation_k, rotation_v,
                           batch, num_q_heads, num_kv_heads, n_q, n_kv, kv_capacity, head_dim,

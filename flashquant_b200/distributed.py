@@ -70,5 +70,7 @@ def cross_gpu_decode(partial_fn: Callable[[], torch.Tensor],
     world = dist.get_world_size(group)
     gathered = torch.empty((world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
     # one collective into one buffer: the result is already in merge layout
-    dist.all_gather_into_tensor(gathered, part, group=group)
+    # (gloo wants the output as the inputs stacked along dim 0: same storage, flat view)
+    dist.all_gather_into_tensor(gathered.view(world * part.shape[0], *part.shape[1:]), part,
+                                group=group)
     return merge_fn(gathered)

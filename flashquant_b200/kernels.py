@@ -574,6 +574,55 @@ class HostDecodeStep:
         self.staging = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         self.workspace = decode_workspace(dev, num_seqs, num_q_heads, num_kv_heads, head_dim,
                                           num_splits)
+        self._block = None
+
+    def host_block(self):
+        """The page-locked block of the packed form and named views into it.
+
+        Returns ``(block, views)``: ``views`` maps ``key, value, slot_mapping, seq_lens,
+        block_table, q, out`` to tensors that alias the block at the offsets of
+        ``fq_decode_step_offsets``.  Write a step's inputs into the views, call ``packed()``,
+        read ``views["out"]``.
+        """
+        if self._block is None:
+            num_seqs, hq, hkv, d, _ = self.shape
+            off = (C.c_uint64 * 8)()
+            N.check(self.lib.fq_decode_step_offsets(num_seqs, hq, hkv, d, self.bt_stride,
+                                                    self.slot_is_int64, off))
+            block = torch.zeros(max(int(off[7]), 256), dtype=torch.uint8).pin_memory()
+
+            def view(at, shape, dt):
+                n = int(torch.tensor(shape).prod()) * torch.empty(0, dtype=dt).element_size()
+                return block[at:at + n].view(dt).view(shape)
+
+            views = {
+                "key": view(off[0], (num_seqs, hkv, d), self.dtype),
+                "value": view(off[1], (num_seqs, hkv, d), self.dtype),
+                "slot_mapping": view(off[2], (num_seqs,), self.slot_dtype),
+                "seq_lens": view(off[3], (num_seqs,), torch.int32),
+                "block_table": view(off[4], (num_seqs, self.bt_stride), torch.int32),
+                "q": view(off[5], (num_seqs, hq, d), self.dtype),
+                "out": view(off[6], (num_seqs, hq, d), self.dtype),
+            }
+            self._block = (block, views)
+        return self._block
+
+    def packed(self, overlap_copies=True, kv_cache=None, kq_cache=None):
+        """One step from the block of ``host_block()`` (``fq_decode_step_host_packed``)."""
+        block, views = self.host_block()
+        num_seqs, hq, hkv, d, bs = self.shape
+        kv_cache = self.kv_cache if kv_cache is None else kv_cache
+        kq_cache = self.kq_cache if kq_cache is None else kq_cache
+        rot, bk, ck, bv, cv, qjl = self.consts
+        N.check(self.lib.fq_decode_step_host_packed(
+            block.data_ptr(), views["out"].data_ptr(), 1 if overlap_copies else 0,
+            N.dtype_code(self.dtype), self.slot_is_int64, self.bt_stride, N.ptr(kv_cache),
+            N.ptr(kq_cache) if kq_cache is not None else None, N.ptr(rot), N.ptr(bk), bk.numel(),
+            N.ptr(ck), ck.numel(), N.ptr(bv), bv.numel(), N.ptr(cv), cv.numel(),
+            N.ptr(qjl) if qjl is not None else None, num_seqs, hq, hkv, d, bs, kv_cache.shape[0],
+            self.sm_scale, self.num_splits, N.ptr(self.staging), self.staging.numel(),
+            N.ptr(self.workspace), self.workspace.numel(), N.stream_ptr(self.dev)))
+        return views["out"]
 
     def __call__(self, q_host, key_host, value_host, slot_mapping_host, block_table_host,
                  seq_lens_host, out_host, kv_cache=None, kq_cache=None):

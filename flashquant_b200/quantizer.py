@@ -83,10 +83,10 @@ class TurboQuantMSE:
         lead = indices.shape[:-1]
         idx = indices.reshape(-1, self.dim).to(torch.uint8)
         packed = ((idx[:, 0::2] << 4) | idx[:, 1::2]).reshape(-1, 1, self.dim // 2)
-        y = K.tq4_decompress(packed, norms.reshape(-1, 1, 1).float(), self.centroids,
-                             dtype=torch.float32)
-        # rotated-space values carry the norm already; the back-rotation is a plain GEMM
-        return (y.reshape(-1, self.dim) @ self.rotation.to(y.device)).reshape(*lead, self.dim)
+        # centroid look-up, norm and back-rotation in the library (fq_tq4_decompress_original)
+        y = K.tq4_decompress_original(packed, norms.reshape(-1, 1, 1).float(), self.centroids,
+                                      self.rotation, dtype=torch.float32)
+        return y.reshape(*lead, self.dim)
 
 
 class TurboQuantProd:

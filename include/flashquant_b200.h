@@ -527,6 +527,32 @@ int fq_decode_step_host(const void* q_host, const void* key_host, const void* va
                         int num_splits, void* out_host, void* staging, size_t staging_bytes,
                         void* workspace, size_t workspace_bytes, fq_stream_t stream);
 
+/* The same step with the host inputs in ONE page-locked block, laid out like the staging
+ * area: the step is one host-to-device copy (overlap_copies = 0), or two halves of the block
+ * with the second - sequence lengths, block table, query - in flight under the
+ * compress-on-append (overlap_copies = 1), the two launches, one copy of the result to
+ * out_host (which may point into the same block, at offsets[6]) and a synchronise.
+ *
+ * fq_decode_step_offsets fills offsets[0..7] with the byte offsets of
+ *   key, value, slot_mapping, seq_lens, block_table, q, out, and the total size;
+ * every part starts on a 256-byte boundary, shapes and dtypes as for fq_decode_step_host.
+ * The caller writes each step's inputs at those offsets of its block, then calls
+ * fq_decode_step_host_packed(block, ...); the staging area has the same size as before.
+ */
+int fq_decode_step_offsets(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                           int64_t block_table_stride, int slot_is_int64, uint64_t offsets[8]);
+int fq_decode_step_host_packed(const void* block_host, void* out_host, int overlap_copies,
+                               fq_dtype dtype, int slot_is_int64, int64_t block_table_stride,
+                               uint8_t* kv_cache, uint8_t* kq_cache, const float* rotation,
+                               const float* boundaries_k, int n_boundaries_k,
+                               const float* centroids_k, int n_centroids_k,
+                               const float* boundaries_v, int n_boundaries_v,
+                               const float* centroids_v, int n_centroids_v, const float* qjl,
+                               int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                               int block_size, int64_t num_blocks, float sm_scale, int num_splits,
+                               void* staging, size_t staging_bytes, void* workspace,
+                               size_t workspace_bytes, fq_stream_t stream);
+
 /* Copies the device status word of a decode workspace to *status (synchronises stream). */
 int fq_workspace_status(const void* workspace, uint32_t* status, fq_stream_t stream);
 

@@ -345,6 +345,18 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
                                         rot, hkv, d, bs, num_splits=2)
         assert torch.equal(hout.view(torch.int16), ref_it.cpu().view(torch.int16)), f"call {it}"
     assert K.workspace_status(step.workspace) == 0
+    # the packed form: all inputs in one page-locked block, one or two copies in
+    if pinned:
+        _, views = step.host_block()
+        for name, t in (("key", new_k), ("value", new_v), ("slot_mapping", new_slots),
+                        ("seq_lens", lens), ("block_table", bt), ("q", w.q)):
+            views[name].copy_(t)
+        for overlap in (False, True):
+            views["out"].zero_()
+            got = step.packed(overlap_copies=overlap)
+            assert torch.equal(got.view(torch.int16), ref.cpu().view(torch.int16)), overlap
+            assert torch.equal(grown, ref_cache)
+        assert K.workspace_status(step.workspace) == 0
     hout.copy_(ref.cpu())
     # and against the oracle end to end
     ref32, ref_out = O.split_k_paged_decode_stages(w.q, ref_cache.cpu(), bt, lens, ck, cv, rot,
