@@ -249,6 +249,8 @@ def run_ours(args):
 
     # ---- end to end: host buffers in, host buffer out, every step -----------------------
     e2e_steps = max(args.steps, 200) if args.steps < 2000 else 2000  # 20 steps would be noise
+    if args.e2e_steps:
+        e2e_steps = args.e2e_steps  # short profiling runs
     hq_ = w.q.pin_memory()
     new_k = k_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
     new_v = v_cpu.reshape(NUM_SEQS, CONTEXT, HKV, D)[:, -1].contiguous().pin_memory()
@@ -952,6 +954,8 @@ def main():
                     help="DRAM bytes per launch of the decode kernel (dram read + write of one "
                          "ncu capture); default: the figure recorded in "
                          "profiles/decode_traffic.json, null if that file is missing")
+    ap.add_argument("--e2e-steps", type=int, default=0,
+                    help="host-buffer steps of the end-to-end figure (default: max(steps, 200))")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary blocks of the line (append, prefill, decompress, "
                          "multi-token, long-context)")
