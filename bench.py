@@ -304,8 +304,10 @@ def run_ours(args):
                    peaks=_peaks(), caches=caches, w=w, ws=ws)
         for name, fn in (("strong_scaling", extra_strong_scaling), ("long_context", extra_long_context),
                          ("multi_token", extra_multi_token), ("append", extra_append),
-                         ("decompress", extra_decompress), ("prefill", extra_prefill)):
-            if world > 1 and name in ("multi_token", "append", "decompress", "prefill"):
+                         ("decompress", extra_decompress), ("prefill", extra_prefill),
+                         ("paged_prefill", extra_paged_prefill)):
+            if world > 1 and name in ("multi_token", "append", "decompress", "prefill",
+                                      "paged_prefill"):
                 continue  # one-GPU rows: measured at N = 1 only
             try:
                 extras[name] = fn(ctx)
@@ -625,6 +627,41 @@ def extra_prefill(ctx):
     peak = float(ctx["peaks"].get("bf16_tflops_sustained", 1400.0))
     return {"ms_per_call": ms, "tflops_causal_half": flops / (ms * 1e-3) / 1e12,
             "frac_of_sustained_tensor_peak": flops / (ms * 1e-3) / 1e12 / peak}
+
+
+def extra_paged_prefill(ctx):
+    """Prefill over the PAGED cache (fq_paged_tq4_prefill): the configs[3] shape read through a
+    block table (4 whole prompts of 8192 tokens), and a chunked step (8 sequences, chunk 512
+    after 4096 keys of context); the cache is filled by the compress-on-append."""
+    from flashquant_b200 import kernels as K, workloads as W
+    dev = ctx["dev"]
+    peak = float(ctx["peaks"].get("bf16_tflops_sustained", 1400.0))
+    out = {}
+    for name, lens, chunks in (("whole_prompts_4x8192", [8192] * 4, [8192] * 4),
+                               ("chunk_512_after_4096_x8", [4608] * 8, [512] * 8)):
+        w = W.decode_workload(seq_lens=lens, num_q_heads=HQ, num_kv_heads=HKV, cfg=7)
+        k, v = W.make_kv(w.total_tokens, HKV, D_, cfg=7)
+        cache = torch.zeros(w.num_blocks, BS, HKV * (D_ + 8), dtype=torch.uint8, device=dev)
+        K.tq4_compress_append(k.to(dev), v.to(dev), cache, w.slot_mapping.to(dev), ctx["rot"],
+                              ctx["bk"], ctx["bv"])
+        cu = torch.zeros(len(chunks) + 1, dtype=torch.int32)
+        cu[1:] = torch.cumsum(torch.tensor(chunks), 0)
+        q = torch.randn(int(cu[-1]), HQ, D_, generator=torch.Generator().manual_seed(3007)).to(
+            torch.bfloat16).to(dev)
+        bt, sl, cu_d = w.block_table.to(dev), w.seq_lens.to(dev), cu.to(dev)
+        ws = torch.zeros(K.N.load().fq_paged_tq4_prefill_workspace_bytes(q.shape[0], HQ, D_),
+                         dtype=torch.uint8, device=dev)
+        o = torch.empty_like(q)
+        ms = _event_loop(lambda: K.paged_tq4_prefill(q, cache, bt, sl, cu_d, max(chunks), ctx["ck"],
+                                                     ctx["cv"], ctx["rot"], HKV, D_, BS, out=o,
+                                                     workspace=ws), 5, 2)
+        # visible (query, key) pairs: chunk rows see the context and the causal half of the chunk
+        pairs = sum(c * (l - c) + c * (c + 1) / 2 for l, c in zip(lens, chunks))
+        flops = 4.0 * HQ * pairs * D_
+        out[name] = {"ms_per_call": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                     "frac_of_sustained_tensor_peak": flops / (ms * 1e-3) / 1e12 / peak,
+                     "status": K.workspace_status(ws)}
+    return out
 
 
 # --------------------------------------------------------------------------------------

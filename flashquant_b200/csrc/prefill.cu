@@ -159,6 +159,18 @@ struct PrefillArgs {
   int split_tokens;
   int64_t total_rows;
   float* part;
+  // Paged, variable-length mode (PAGED kernel): q_rot / o_rot are (tokens, Hq, D); sequence b
+  // owns query tokens cu_q[b] .. cu_q[b+1] - the LAST ones of its seq_lens[b] keys, so query i
+  // sees keys 0 .. seq_lens[b] - q_len + i - and its keys and values sit in the pages
+  // block_table[b][*] of the packed cache ([K codes | K norms | V codes | V norms] per token).
+  const uint8_t* kv_cache;
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* seq_lens;
+  const int32_t* cu_q;
+  int block_size;
+  int64_t num_blocks;
+  int round_out;  // FQ_BF16 / FQ_F16: rows are rounded to that type before they are stored
 };
 
 template <int D>
@@ -190,7 +202,24 @@ struct PrefillSmem {
 //                 issue O += P V(t)                                             (tensor)
 // so a score product always has a whole softmax to complete in, and the PV product the next
 // tile's key dequantisation.  Codes and norms arrive by bulk copies one tile ahead.
-template <int D>
+// 16 or 4 bytes global -> shared without a register in between; `valid` false writes zeros
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(valid ? 16u : 0u)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src),
+               "r"(valid ? 4u : 0u)
+               : "memory");
+}
+// the barrier receives one arrival from this thread once all its copies above have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int D, bool PAGED>
 __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(PrefillArgs p) {
   using S = PrefillSmem<D>;
   constexpr uint32_t kIdescS = umma_idesc(kPfM, kPfN, false);
@@ -222,10 +251,26 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   const int group = p.hq / p.hkv;
   const int hkv = hq / group;
   const int m0 = m_tile * kPfM;
-  const int rows = p.nq - m0 < kPfM ? p.nq - m0 : kPfM;
+  // paged mode: this sequence's query tokens and keys; ctx keys precede the first query token
+  int q_first = 0, q_len = p.nq, kv_len = p.nkv, ctx = 0;
+  bool clamped = false;
+  if constexpr (PAGED) {
+    q_first = p.cu_q[b];
+    q_len = p.cu_q[b + 1] - q_first;
+    kv_len = p.seq_lens[b];
+    const int64_t room = p.bt_stride * int64_t(p.block_size);  // keys a block-table row can name
+    if (kv_len > room) {
+      kv_len = int(room);
+      clamped = true;
+    }
+    ctx = kv_len - q_len;
+    if (m0 >= q_len) return;  // the grid is sized for the longest chunk
+  }
+  const int rows = q_len - m0 < kPfM ? q_len - m0 : kPfM;
 
-  int kv_end = p.nkv;
-  if (p.causal && m0 + rows < kv_end) kv_end = m0 + rows;
+  int kv_end = kv_len;
+  if (p.causal && ctx + m0 + rows < kv_end) kv_end = ctx + m0 + rows;
+  if (kv_end < 0) kv_end = 0;
   // a slice of the keys: move the bases, the loop below then sees tokens 0 .. kv_end of it
   const int kv_begin = split * p.split_tokens;
   if (split_mode) {
@@ -234,18 +279,20 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   }
   const int n_tiles = (kv_end + kPfN - 1) / kPfN;
 
-  const int64_t kv_row0 = (int64_t(b) * p.hkv + hkv) * p.kv_stride + kv_begin;
-  const uint8_t* kc_base = p.k_packed + kv_row0 * (D / 2);
-  const uint8_t* vc_base = p.v_packed + kv_row0 * (D / 2);
-  const float* kn_base = p.k_norms + kv_row0;
-  const float* vn_base = p.v_norms + kv_row0;
-  // norms ride along with the codes when a bulk copy can take them (16-byte granularity)
-  const bool norm_bulk = ((reinterpret_cast<uintptr_t>(kn_base) | reinterpret_cast<uintptr_t>(vn_base)) & 15) == 0;
+  const int64_t kv_row0 = PAGED ? 0 : (int64_t(b) * p.hkv + hkv) * p.kv_stride + kv_begin;
+  const uint8_t* kc_base = PAGED ? nullptr : p.k_packed + kv_row0 * (D / 2);
+  const uint8_t* vc_base = PAGED ? nullptr : p.v_packed + kv_row0 * (D / 2);
+  const float* kn_base = PAGED ? nullptr : p.k_norms + kv_row0;
+  const float* vn_base = PAGED ? nullptr : p.v_norms + kv_row0;
+  // norms ride along with the codes when a bulk copy can take them (16-byte granularity);
+  // in paged mode they always arrive with the codes
+  const bool norm_bulk =
+      PAGED || ((reinterpret_cast<uintptr_t>(kn_base) | reinterpret_cast<uintptr_t>(vn_base)) & 15) == 0;
 
   // ---- set-up ---------------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(bar_k, 1);
-    mbar_init(bar_v, 1);
+    mbar_init(bar_k, PAGED ? kPfThreads : 1);  // paged: one arrival per thread and tile
+    mbar_init(bar_v, PAGED ? kPfThreads : 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 1, 1);
     mbar_init(bar_o, 1);
@@ -262,11 +309,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   }
   // Q tile -> [k-chunk][row][16 B]
   {
-    const __half* qsrc = p.q_rot + ((int64_t(b) * p.hq + hq) * p.nq + m0) * D;
+    const __half* qsrc = PAGED ? p.q_rot + (int64_t(q_first + m0) * p.hq + hq) * D
+                               : p.q_rot + ((int64_t(b) * p.hq + hq) * p.nq + m0) * D;
+    const int64_t q_pitch = PAGED ? int64_t(p.hq) * D : D;
     for (int i = tid; i < kPfM * int(S::kChunks); i += kPfThreads) {
       const int r = i / int(S::kChunks), kc = i % int(S::kChunks);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < rows) v = *reinterpret_cast<const uint4*>(qsrc + int64_t(r) * D + kc * 8);
+      if (r < rows) v = *reinterpret_cast<const uint4*>(qsrc + int64_t(r) * q_pitch + kc * 8);
       *reinterpret_cast<uint4*>(smem + S::kOffQ + kc * S::kSlabQ + r * 16) = v;
     }
   }
@@ -305,6 +354,36 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (with_norms)
       bulk_g2s(is_k ? nk_raw : nv_raw, (is_k ? kn_base : vn_base) + t0, kPfN * 4, bar);
   };
+  // Paged mode, ALL threads: the tile's codes and norms gathered through the block table, 16
+  // bytes per thread (thread = (token, quarter of its 64 code bytes)) and one norm for the
+  // first 64 threads; tokens past the end arrive as zeros.
+  [[maybe_unused]] bool bad_page = false;
+  [[maybe_unused]] auto gather_codes = [&](int tile, bool is_k) {
+    const int tok = tid >> 2, piece = tid & 3;
+    const int row_bytes = p.hkv * (D + 8);
+    const int code_off = (is_k ? 0 : p.hkv * (D / 2 + 4)) + hkv * (D / 2);
+    const int norm_off = (is_k ? 0 : p.hkv * (D / 2 + 4)) + p.hkv * (D / 2) + 4 * hkv;
+    auto token_row = [&](int t, bool& valid) -> const uint8_t* {
+      valid = t < kv_end;
+      if (!valid) return p.kv_cache;
+      const int page = t / p.block_size;
+      int64_t phys = p.block_table[int64_t(b) * p.bt_stride + page];
+      if (phys < 0 || phys >= p.num_blocks) {  // reported, not followed
+        phys = 0;
+        bad_page = true;
+      }
+      return p.kv_cache + (phys * p.block_size + (t - page * p.block_size)) * int64_t(row_bytes);
+    };
+    bool valid;
+    const uint8_t* src = token_row(tile * kPfN + tok, valid);
+    cp_async16(smem_u32(smem + S::kOffRaw + (is_k ? 0 : S::kRawTile)) + tid * 16,
+               src + code_off + piece * 16, valid);
+    if (tid < kPfN) {
+      const uint8_t* nsrc = token_row(tile * kPfN + tid, valid);
+      cp_async4(smem_u32(is_k ? nk_raw : nv_raw) + tid * 4, nsrc + norm_off, valid);
+    }
+    cp_async_arrive(is_k ? bar_k : bar_v);
+  };
   // all threads: codes of the landed tile -> fp16 operand tile at `op_off`
   auto dequantise = [&](int tile, bool is_k, uint32_t op_off) {
     const int n_tok = tile_tokens(tile);
@@ -342,7 +421,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   // threads 0..63: the norm of token `tid` of the tile, from the bulk copy or from memory
   auto tile_norm = [&](int tile, bool is_k) {
     const int t0 = tile * kPfN, n_tok = tile_tokens(tile);
-    if (norm_bulk && n_tok == kPfN) return (is_k ? nk_raw : nv_raw)[tid];
+    if (PAGED || (norm_bulk && n_tok == kPfN)) return (is_k ? nk_raw : nv_raw)[tid];
     return tid < n_tok ? (is_k ? kn_base : vn_base)[t0 + tid] : 0.f;
   };
   auto issue_scores = [&](int tile) {  // thread 0
@@ -361,7 +440,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 
   // ---- prologue: K(0) -> operand, S(0) issued, K(1) and V(0) on their way ------------------
   if (n_tiles > 0) {
-    if (tid == 0) {
+    if constexpr (PAGED) {
+      gather_codes(0, true);
+      gather_codes(0, false);
+    } else if (tid == 0) {
       issue_codes(0, true);
       issue_codes(0, false);
     }
@@ -376,8 +458,9 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (tid == 0 && !dead) {
       tc_fence_after();
       issue_scores(0);
-      if (n_tiles > 1) issue_codes(1, true);
+      if (!PAGED && n_tiles > 1) issue_codes(1, true);
     }
+    if (PAGED && n_tiles > 1) gather_codes(1, true);
   }
 
   for (int tile = 0; tile < n_tiles && !dead; ++tile) {
@@ -410,8 +493,14 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (tid == 0 && !dead) {
       tc_fence_after();
       if (more) issue_scores(tile + 1);  // runs while this tile's softmax does
-      if (tile + 2 < n_tiles) issue_codes(tile + 2, true);
-      if (more) issue_codes(tile + 1, false);
+      if constexpr (!PAGED) {
+        if (tile + 2 < n_tiles) issue_codes(tile + 2, true);
+        if (more) issue_codes(tile + 1, false);
+      }
+    }
+    if constexpr (PAGED) {
+      if (tile + 2 < n_tiles) gather_codes(tile + 2, true);
+      if (more) gather_codes(tile + 1, false);
     }
     // ---- S(t), issued one iteration ago -----------------------------------------------------
     if (!mbar_wait(bar_s + (tile & 1), (tile >> 1) & 1)) dead = true;
@@ -422,7 +511,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     // ---- online softmax on row `row` ---------------------------------------------------------
     // A tile that lies wholly below the diagonal of every row of the CTA and is full needs no
     // masking: the common case gets a loop body without predicates.
-    const bool unmasked = n_tok == kPfN && (!p.causal || t0 + kPfN - 1 <= m0);
+    const bool unmasked = n_tok == kPfN && (!p.causal || t0 + kPfN - 1 <= m0 + ctx);
     // pass 1: row maximum of logit*log2e + clamped log2|v| over this thread's half of the tile
     float mx = -INFINITY;
     auto row_max = [&](auto masked) {
@@ -439,7 +528,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
           float e = fmaf(sv[j + u], nk[u], lv[u]);
           if constexpr (decltype(masked)::value) {
             const int col = c0 + j + u;
-            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos + ctx);
             e = ok ? e : -INFINITY;
           }
           mx = fmaxf(mx, e);
@@ -493,7 +582,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
           float pe = fast_exp2(fmaf(sv[j + u], nk[u], neg_m));
           if constexpr (decltype(masked)::value) {
             const int col = c0 + j + u;
-            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos);
+            const bool ok = col < n_tok && (!p.causal || t0 + col <= q_pos + ctx);
             pe = ok ? pe : 0.f;
           }
           l_run += pe;
@@ -530,12 +619,16 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 
   // ---- epilogue: normalise, round, store the rotated-space row -----------------------------
   if (dead && tid == 0 && p.status) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
+  if constexpr (PAGED) {
+    if ((bad_page || clamped) && p.status) atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
+  }
   {
     __syncthreads();  // the last tile's maxima have been read
     xch[tid] = l_run;
     __syncthreads();
     const float l_row = l_run + xch[tid ^ kPfM];  // both halves of the row
-    const int64_t row_global = (int64_t(b) * p.hq + hq) * p.nq + q_pos;
+    const int64_t row_global = PAGED ? int64_t(q_first + q_pos) * p.hq + hq
+                                     : (int64_t(b) * p.hq + hq) * p.nq + q_pos;
     // 2^-kPfPScaleLog2, and 1/l unless the rows of the slices are still to be merged
     const float inv = split_mode ? 1.f / 256.f : (l_row > 0.f ? 1.f / (l_row * 256.f) : 0.f);
     float* dst = split_mode ? p.part + (int64_t(split) * p.total_rows + row_global) * (D + 4)
@@ -555,9 +648,16 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
       }
       if (row < rows) {
 #pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          o[j] *= inv;
+          // the reference's attention over de-quantised pages returns rows of the activation
+          // type, which it then rotates (src/flashquant/vllm/impl.py:477-509): round here too
+          if (p.round_out == FQ_BF16) o[j] = __bfloat162float(__float2bfloat16_rn(o[j]));
+          if (p.round_out == FQ_F16) o[j] = __half2float(__float2half_rn(o[j]));
+        }
+#pragma unroll
         for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + c0 + j) =
-              make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+          *reinterpret_cast<float4*>(dst + c0 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
       }
     }
   }
@@ -598,10 +698,10 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restr
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
-template <int D>
+template <int D, bool PAGED = false>
 static int launch_prefill_t(const PrefillArgs& a, cudaStream_t stream) {
   using S = PrefillSmem<D>;
-  auto kern = prefill_attention_kernel<D>;
+  auto kern = prefill_attention_kernel<D, PAGED>;
   static thread_local int set_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -762,4 +862,75 @@ extern "C" int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uin
                           n_centroids_k, centroids_v, n_centroids_v, rotation_k, rotation_v,
                           batch, num_q_heads, num_kv_heads, n_q, n_kv, kv_capacity, head_dim,
                           sm_scale, is_causal, out, workspace, workspace_bytes, stream);
+}
+
+extern "C" size_t fq_paged_tq4_prefill_workspace_bytes(int total_q_tokens, int num_q_heads,
+                                                       int head_dim) {
+  if (total_q_tokens < 0 || num_q_heads < 0 || head_dim < 0) return 0;
+  return prefill_workspace(int64_t(total_q_tokens) * num_q_heads, head_dim, false).total;
+}
+
+extern "C" int fq_paged_tq4_prefill(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                                    const int32_t* block_table, int64_t block_table_stride,
+                                    const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                                    const float* centroids_k, int n_centroids_k,
+                                    const float* centroids_v, int n_centroids_v,
+                                    const float* rotation, int num_seqs, int total_q_tokens,
+                                    int max_q_len, int num_q_heads, int num_kv_heads,
+                                    int head_dim, int block_size, int64_t num_blocks,
+                                    float sm_scale, void* out, void* workspace,
+                                    size_t workspace_bytes, fq_stream_t stream) {
+  FQ_RANGE("fq_paged_tq4_prefill");
+  FQ_REQUIRE(num_seqs >= 0 && total_q_tokens >= 0 && max_q_len >= 0 && num_q_heads >= 1 &&
+                 num_kv_heads >= 1 && block_size >= 1 && num_blocks >= 0 && block_table_stride >= 0,
+             FQ_ERR_INVALID_ARGUMENT, "paged prefill: negative size");
+  if (num_seqs == 0 || total_q_tokens == 0 || max_q_len == 0) return FQ_OK;
+  FQ_REQUIRE(q && kv_cache && block_table && seq_lens && cu_seqlens_q && centroids_k &&
+                 centroids_v && rotation && out,
+             FQ_ERR_INVALID_ARGUMENT, "paged prefill: null pointer");
+  FQ_REQUIRE(dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_UNSUPPORTED,
+             "paged prefill: q must be fp16 or bf16");
+  FQ_REQUIRE(head_dim == 128, FQ_ERR_UNSUPPORTED,
+             "paged prefill: head_dim %d (the tensor-core kernel is built for 128)", head_dim);
+  FQ_REQUIRE(num_q_heads % num_kv_heads == 0, FQ_ERR_INVALID_ARGUMENT,
+             "paged prefill: q heads not a multiple of KV heads");
+  FQ_REQUIRE(n_centroids_k >= 1 && n_centroids_k <= 16 && n_centroids_v >= 1 &&
+                 n_centroids_v <= 16,
+             FQ_ERR_INVALID_ARGUMENT, "centroid count outside [1, 16]");
+  FQ_REQUIRE(num_kv_heads % 4 == 0, FQ_ERR_UNSUPPORTED,
+             "paged prefill: %d KV heads (the 16-byte gathers need a multiple of 4)", num_kv_heads);
+  FQ_REQUIRE(num_seqs <= 65535 && num_q_heads <= 65535, FQ_ERR_UNSUPPORTED,
+             "paged prefill: more than 65535 sequences or query heads");
+  FQ_REQUIRE(aligned(q, 16) && aligned(out, 16) && aligned(kv_cache, 16) && aligned(rotation, 16),
+             FQ_ERR_ALIGNMENT, "paged prefill: q, out, the cache and the rotation must be 16-byte aligned");
+  const int64_t rows = int64_t(total_q_tokens) * num_q_heads;
+  const PrefillWorkspace w = prefill_workspace(rows, head_dim, false);
+  FQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
+             "paged prefill: workspace of %zu bytes needed (256-byte aligned)", w.total);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  __half* q_rot = reinterpret_cast<__half*>(ws + w.q_rot_off);
+  float* o_rot = reinterpret_cast<float*>(ws + w.o_rot_off);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = rotate_q_to_half(q, dtype, rotation, q_rot, rows, head_dim, s);
+  if (rc != FQ_OK) return rc;
+  PrefillArgs a{};
+  a.q_rot = q_rot;
+  a.cent_k = centroids_k; a.nck = n_centroids_k;
+  a.cent_v = centroids_v; a.ncv = n_centroids_v;
+  a.o_rot = o_rot;
+  a.batch = num_seqs; a.hq = num_q_heads; a.hkv = num_kv_heads; a.nq = max_q_len; a.nkv = 0;
+  a.scale_log2 = sm_scale * 1.4426950408889634f;
+  a.causal = 1;
+  a.status = reinterpret_cast<uint32_t*>(ws);
+  a.kv_cache = kv_cache;
+  a.block_table = block_table;
+  a.bt_stride = block_table_stride;
+  a.seq_lens = seq_lens;
+  a.cu_q = cu_seqlens_q;
+  a.block_size = block_size;
+  a.num_blocks = num_blocks;
+  a.round_out = int(dtype);
+  rc = launch_prefill_t<128, true>(a, s);
+  if (rc != FQ_OK) return rc;
+  return rotate_back(o_rot, dtype, rotation, out, rows, head_dim, s);
 }

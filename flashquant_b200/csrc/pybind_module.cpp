@@ -188,6 +188,44 @@ Tensor split_k_paged_decode(const Tensor& q, const Tensor& kv_cache, const Tenso
   return o;
 }
 
+// Prefill chunks over the paged cache: the call that stands in for the reference's
+// decompress-everything + flash_attn_varlen_func prefill path
+// (src/flashquant/vllm/impl.py:265-336, 477-509), with its metadata names.
+Tensor paged_tq4_prefill(const Tensor& q, const Tensor& kv_cache, const Tensor& block_table,
+                         const Tensor& seq_lens, const Tensor& query_start_loc, int max_query_len,
+                         const Tensor& centroids_k, const Tensor& centroids_v,
+                         const Tensor& rotation, int num_kv_heads, int head_dim, int block_size,
+                         std::optional<double> sm_scale, std::optional<Tensor> out) {
+  need_cuda(q, "q");
+  need_cuda(kv_cache, "kv_cache");
+  TORCH_CHECK(q.dim() == 3, "q must be (num_tokens, H_q, D)");
+  TORCH_CHECK(block_table.scalar_type() == torch::kInt32 && seq_lens.scalar_type() == torch::kInt32 &&
+                  query_start_loc.scalar_type() == torch::kInt32,
+              "block_table, seq_lens and query_start_loc must be int32");
+  TORCH_CHECK(query_start_loc.numel() == seq_lens.numel() + 1,
+              "query_start_loc must have one entry more than seq_lens");
+  c10::cuda::CUDAGuard guard(q.device());
+  const auto dev = q.device();
+  const int total = int(q.size(0)), hq = int(q.size(1));
+  Tensor qc = q.contiguous(), bt = block_table.contiguous(), sl = seq_lens.contiguous();
+  Tensor cu = query_start_loc.contiguous();
+  TORCH_CHECK(kv_cache.is_contiguous(), "kv_cache must be contiguous");
+  Tensor ck = const_on(centroids_k, dev), cv = const_on(centroids_v, dev), rot = const_on(rotation, dev);
+  Tensor o = out.has_value() ? *out : torch::empty_like(qc);
+  TORCH_CHECK(o.is_contiguous() && o.numel() == qc.numel() && o.scalar_type() == qc.scalar_type(),
+              "out must be a contiguous tensor with q's number of elements and dtype");
+  const double scale = sm_scale.has_value() ? *sm_scale : 1.0 / std::sqrt(double(head_dim));
+  Tensor ws = workspace(dev, 2, fq_paged_tq4_prefill_workspace_bytes(total, hq, head_dim));
+  check(fq_paged_tq4_prefill(qc.data_ptr(), dtype_of(qc), kv_cache.data_ptr<uint8_t>(),
+                             bt.data_ptr<int32_t>(), bt.stride(0), sl.data_ptr<int32_t>(),
+                             cu.data_ptr<int32_t>(), ck.data_ptr<float>(), int(ck.numel()),
+                             cv.data_ptr<float>(), int(cv.numel()), rot.data_ptr<float>(),
+                             int(sl.numel()), total, max_query_len, hq, num_kv_heads, head_dim,
+                             block_size, kv_cache.size(0), float(scale), o.data_ptr(),
+                             ws.data_ptr(), size_t(ws.numel()), stream_of(dev)));
+  return o;
+}
+
 // Device status word (FQ_DEV_* bits) of the decode workspace of the current stream; a non-zero
 // word also re-zeroes the head of the workspace, as the C ABI asks before the next call.
 int64_t decode_status(const Tensor& like) {
@@ -289,6 +327,11 @@ PYBIND11_MODULE(_C, m) {
         py::arg("kv_cache"), py::arg("kq_cache"), py::arg("slot_mapping"), py::arg("rotation"),
         py::arg("boundaries_k"), py::arg("centroids_k"), py::arg("boundaries_v"),
         py::arg("qjl_matrix"));
+  m.def("paged_tq4_prefill", &paged_tq4_prefill, py::arg("q"), py::arg("kv_cache"),
+        py::arg("block_table"), py::arg("seq_lens"), py::arg("query_start_loc"),
+        py::arg("max_query_len"), py::arg("centroids_k"), py::arg("centroids_v"),
+        py::arg("rotation"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("block_size"),
+        py::arg("sm_scale") = py::none(), py::arg("out") = py::none());
   m.def("decode_status", &decode_status, py::arg("like"));
   m.def("launch_count", []() { return fq_launch_count(); });
 }

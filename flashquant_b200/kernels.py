@@ -538,6 +538,46 @@ def split_k_paged_decode_qjl(q, kv_cache, kq_cache, block_table, seq_lens, centr
     return out
 
 
+def paged_tq4_prefill(q, kv_cache, block_table, seq_lens, cu_seqlens_q, max_q_len, centroids_k,
+                      centroids_v, rotation, num_kv_heads, head_dim, block_size, sm_scale=None,
+                      out=None, workspace=None) -> torch.Tensor:
+    """Causal attention of prefill chunks over the paged TQ4 cache (``fq_paged_tq4_prefill``).
+
+    ``q`` ``(total_q_tokens, H_q, D)``: the chunks of all sequences one after the other,
+    ``cu_seqlens_q`` ``(num_seqs + 1)`` their bounds, ``seq_lens`` the keys of each sequence
+    including its chunk (already appended to the cache).  What the reference's prefill path
+    computes after de-quantising the whole cache (src/flashquant/vllm/impl.py:265-336,
+    477-509); ``workspace`` word 0 is the device status word.
+    """
+    N.require_cuda(q, kv_cache, block_table, seq_lens, cu_seqlens_q)
+    dev = q.device
+    total, hq, d = q.shape
+    if d != head_dim:
+        raise ValueError(f"q has head_dim {d}, expected {head_dim}")
+    num_seqs = seq_lens.numel()
+    if cu_seqlens_q.numel() != num_seqs + 1:
+        raise ValueError("cu_seqlens_q must have num_seqs + 1 entries")
+    q = _contig(q)
+    block_table = block_table if block_table.stride(-1) == 1 else block_table.contiguous()
+    seq_lens, cu = _contig(seq_lens.to(torch.int32)), _contig(cu_seqlens_q.to(torch.int32))
+    ck, cv, rot = _f32(centroids_k, dev), _f32(centroids_v, dev), _f32(rotation, dev)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(head_dim)
+    if out is None:
+        out = torch.empty_like(q)
+    lib = N.load()
+    need = lib.fq_paged_tq4_prefill_workspace_bytes(total, hq, d)
+    if workspace is None:
+        workspace = torch.zeros(max(need, 256), dtype=torch.uint8, device=dev)
+    N.check(lib.fq_paged_tq4_prefill(
+        N.ptr(q), N.dtype_code(q.dtype), N.ptr(kv_cache), N.ptr(block_table),
+        block_table.stride(0), N.ptr(seq_lens), N.ptr(cu), N.ptr(ck), ck.numel(), N.ptr(cv),
+        cv.numel(), N.ptr(rot), num_seqs, total, int(max_q_len), hq, num_kv_heads, d, block_size,
+        kv_cache.shape[0], float(sm_scale), N.ptr(out), N.ptr(workspace), workspace.numel(),
+        N.stream_ptr(dev)))
+    return out
+
+
 class HostDecodeStep:
     """One decode step with host tensors in and out (``fq_decode_step_host``).
 

@@ -493,6 +493,41 @@ int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uint8_t* k_pac
                              fq_stream_t stream);
 
 /*
+ * Fused TQ4 attention over the PAGED cache for prefill chunks of any length: replaces
+ * FlashQuantAttentionImpl's prefill path (src/flashquant/vllm/impl.py:265-336, 477-509), which
+ * de-quantises the whole cache and calls flash_attn_varlen_func on every prefill step.  Here
+ * the pages of each sequence are read through its block-table row, de-quantised tile by tile
+ * in shared memory and attended to on the tensor cores; nothing de-quantised reaches memory.
+ *
+ *   q, out          (total_q_tokens, num_q_heads, head_dim), FQ_F16 or FQ_BF16: the query
+ *                   tokens of all sequences one after the other (vLLM's layout)
+ *   cu_seqlens_q    (num_seqs + 1) int32: sequence b owns tokens cu[b] .. cu[b+1]
+ *   seq_lens        (num_seqs) int32: keys of sequence b INCLUDING its query tokens, whose
+ *                   K/V must already be in the cache (compress-on-append runs first, as in
+ *                   the reference); the mask is causal and aligned at the END of the keys:
+ *                   query i of a chunk of n sees keys 0 .. seq_lens[b] - n + i.  A query
+ *                   without visible keys gives zeros.
+ *   block_table     (num_seqs, block_table_stride) int32 page ids; an id outside
+ *                   [0, num_blocks) or a length beyond the row sets FQ_DEV_BAD_BLOCK_INDEX in
+ *                   word 0 of the workspace and is not followed
+ *   max_q_len       longest chunk (sizes the grid)
+ *   rounding        q Pi^T and the attention rows are rounded to the activation type before
+ *                   the products with K and Pi, as the reference's two matmul + cast steps do
+ *   workspace       256-byte aligned, fq_paged_tq4_prefill_workspace_bytes(...) bytes; word 0
+ *                   is the status word (zero it before the first call)
+ * head_dim 128 and a multiple of 4 KV heads (16-byte gathers from the token rows) only.
+ */
+size_t fq_paged_tq4_prefill_workspace_bytes(int total_q_tokens, int num_q_heads, int head_dim);
+int fq_paged_tq4_prefill(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
+                         const int32_t* block_table, int64_t block_table_stride,
+                         const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                         const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                         int n_centroids_v, const float* rotation, int num_seqs,
+                         int total_q_tokens, int max_q_len, int num_q_heads, int num_kv_heads,
+                         int head_dim, int block_size, int64_t num_blocks, float sm_scale,
+                         void* out, void* workspace, size_t workspace_bytes, fq_stream_t stream);
+
+/*
  * One decode step with HOST buffers: the host-side form of
  * FlashQuantAttentionImpl._fused_decode_path (src/flashquant/vllm/impl.py:362-395), which
  * compresses the step's new K/V token of every sequence into the paged cache and then runs

@@ -607,6 +607,29 @@ def paged_decode_multi_stages(q, kv_cache, block_table, seq_lens, centroids_k, c
     return o_rot, torch.matmul(o_rot.to(q.dtype).float(), rotation).to(q.dtype)
 
 
+def paged_prefill_varlen_stages(q, kv_cache, block_table, seq_lens, cu_seqlens_q, centroids_k,
+                                centroids_v, rotation, num_kv_heads, head_dim, block_size,
+                                sm_scale=None):
+    """Prefill chunks of different lengths over the paged cache: ``(o_rot_fp32, out)``.
+
+    q ``(total_q_tokens, Hq, D)``, sequence b owns tokens cu[b] .. cu[b+1], the last ones of its
+    seq_lens[b] keys.  The reference's prefill path (src/flashquant/vllm/impl.py:265-336,
+    477-509: rotate q, de-quantise, flash_attn_varlen_func(cu_seqlens_q, seqused_k, causal=True),
+    rotate back) sequence by sequence, through ``paged_decode_multi_stages``.
+    """
+    o32 = torch.zeros(q.shape, dtype=torch.float32)
+    out = torch.zeros_like(q)
+    for b in range(len(seq_lens)):
+        lo, hi = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
+        if hi == lo:
+            continue
+        r32, r = paged_decode_multi_stages(q[lo:hi].unsqueeze(0), kv_cache, block_table[b:b + 1],
+                                           seq_lens[b:b + 1], centroids_k, centroids_v, rotation,
+                                           num_kv_heads, head_dim, block_size, sm_scale)
+        o32[lo:hi], out[lo:hi] = r32[0], r[0]
+    return o32, out
+
+
 def split_k_partials(q_rot, k, v, sm_scale, bounds):
     """Per-split (m, l, acc) of one head: the quantities a split-K decode exchanges.
 

@@ -69,7 +69,8 @@ def test_pybind_module_exports_the_probed_names():
     import torch  # noqa: F401  (the module links against libtorch)
     from flashquant_b200 import _C
     for name in ["tq4_compress", "tq4_decompress", "fused_tq_attention", "split_k_paged_decode",
-                 "fused_paged_tq4_decode"]:
+                 "fused_paged_tq4_decode", "tq4_compress_append", "tq4_compress_append_qjl",
+                 "paged_tq4_prefill"]:
         assert hasattr(_C, name)
     assert not hasattr(_C, "codebook")  # would hijack the reference's Lloyd-Max solver
     import pytest

@@ -1,0 +1,99 @@
+"""GPU parity of the fused TQ4 attention over the PAGED cache for prefill chunks
+(fq_paged_tq4_prefill) against the oracle's decompress-then-attend path.
+
+Cases follow the reference's chunked-prefill situations: chunks of 1, 17 and 512 tokens,
+contexts from 0 to 4096 keys before the chunk, ragged batches, GQA.
+"""
+
+import pytest
+import torch
+
+from flashquant_b200 import kernels as K
+from flashquant_b200 import workloads as W
+from oracle import tq_oracle as O
+from parity import attention_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# The tensor-core attention kernel keeps plain fp16 centroid tables (no common scale): its
+# un-rounded rows agree with the reference's to 2^-8 of the entry (stated, as for the prefill
+# over contiguous buffers).
+PAGED_PREFILL_RTOL = 2.0 ** -8
+
+
+def build(consts, seq_lens, chunks, hq=32, hkv=8, cfg=31, dtype=torch.bfloat16, block_size=16):
+    """Paged cache holding seq_lens[b] keys of every sequence (oracle-compressed), and the last
+    chunks[b] tokens of each as the query chunk."""
+    d = 128
+    w = W.decode_workload(seq_lens=seq_lens, num_q_heads=hq, num_kv_heads=hkv, head_dim=d,
+                          block_size=block_size, cfg=cfg, dtype=dtype)
+    rot = consts["rotation_128_0"]
+    k, v = W.make_kv(w.total_tokens, hkv, d, cfg, dtype)
+    cache = torch.zeros(w.num_blocks, block_size, hkv * (d + 8), dtype=torch.uint8)
+    O.compress_and_store(k, v, cache, w.slot_mapping, rot, consts["boundaries_128_3"],
+                         consts["boundaries_128_4"])
+    cu = torch.zeros(len(chunks) + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(chunks), 0)
+    g = torch.Generator().manual_seed(1000 + cfg)
+    q = torch.randn(int(cu[-1]), hq, d, generator=g).to(dtype)
+    return w, cache, q, cu
+
+
+def run_and_check(consts, w, cache, q, cu, chunks):
+    rot, ck, cv = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    ws = torch.zeros(K.N.load().fq_paged_tq4_prefill_workspace_bytes(q.shape[0], q.shape[1], 128),
+                     dtype=torch.uint8, device=DEV)
+    out = K.paged_tq4_prefill(q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+                              cu.to(DEV), max(chunks), ck, cv, rot, w.num_kv_heads, 128,
+                              w.block_size, workspace=ws)
+    assert K.workspace_status(ws) == 0
+    ref32, ref = O.paged_prefill_varlen_stages(q, cache, w.block_table, w.seq_lens, cu, ck, cv, rot,
+                                               w.num_kv_heads, 128, w.block_size)
+    attention_close(out, ref, ref32, rot, rtol=PAGED_PREFILL_RTOL)
+    return out
+
+
+@pytest.mark.parametrize("seq_lens,chunks", [
+    ([17], [17]),                          # whole prompt, no context, ragged tile
+    ([512], [512]),                        # whole prompt, several query tiles
+    ([1, 64, 65], [1, 64, 65]),            # ragged batch of whole prompts
+    ([300, 1000, 4096 + 17], [1, 17, 17]),  # short chunks after long contexts
+    ([4096 + 512, 777, 130], [512, 130, 1]),  # chunk 512 after 4096 keys; mixed
+])
+def test_chunks_vs_oracle(consts, seq_lens, chunks):
+    w, cache, q, cu = build(consts, seq_lens, chunks)
+    run_and_check(consts, w, cache, q, cu, chunks)
+
+
+def test_sequence_without_chunk_and_gqa_layouts(consts):
+    """A sequence that contributes no query tokens, 64 q heads over 8 KV heads, fp16."""
+    seq_lens, chunks = [200, 96, 1030], [40, 0, 129]
+    w, cache, q, cu = build(consts, seq_lens, chunks, hq=64, hkv=8, cfg=33, dtype=torch.float16)
+    run_and_check(consts, w, cache, q, cu, chunks)
+    w, cache, q, cu = build(consts, [50, 260], [50, 4], hq=8, hkv=8, cfg=34, block_size=32)
+    run_and_check(consts, w, cache, q, cu, [50, 4])
+
+
+def test_chunk_equals_decode_for_single_tokens(consts):
+    """One query token per sequence is the decode step: same rows as fq_split_k_paged_decode up
+    to the two kernels' different operand precisions (both within the stated bounds)."""
+    seq_lens = [33, 700, 16, 257]
+    w, cache, q, cu = build(consts, seq_lens, [1, 1, 1, 1], cfg=35)
+    out = run_and_check(consts, w, cache, q, cu, [1, 1, 1, 1])
+    rot, ck, cv = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    dec = K.split_k_paged_decode(q.to(DEV), cache.to(DEV), w.block_table.to(DEV),
+                                 w.seq_lens.to(DEV), ck, cv, rot, 8, 128, 16)
+    assert (out.float() - dec.float()).abs().max() < 2e-2
+
+
+def test_bad_page_index_is_reported_not_followed(consts):
+    w, cache, q, cu = build(consts, [100], [100], cfg=36)
+    rot, ck, cv = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    bt = w.block_table.clone()
+    bt[0, 2] = w.num_blocks + 5
+    ws = torch.zeros(K.N.load().fq_paged_tq4_prefill_workspace_bytes(100, 32, 128),
+                     dtype=torch.uint8, device=DEV)
+    K.paged_tq4_prefill(q.to(DEV), cache.to(DEV), bt.to(DEV), w.seq_lens.to(DEV), cu.to(DEV), 100,
+                        ck, cv, rot, 8, 128, 16, workspace=ws)
+    assert K.workspace_status(ws) & 1  # FQ_DEV_BAD_BLOCK_INDEX

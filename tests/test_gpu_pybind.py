@@ -122,3 +122,29 @@ def test_compress_append_entries(_C, consts):
     cache2 = torch.zeros_like(cache)
     _C.tq4_compress_append(w.key.to(DEV), w.value.to(DEV), cache2, w.slot_mapping.to(DEV), rot, b3, b4)
     assert torch.equal(cache2, cache)
+
+
+def test_paged_prefill_with_vllm_metadata_names(_C, consts):
+    """``_C.paged_tq4_prefill`` with the metadata the reference's prefill path hands to
+    flash_attn_varlen_func (query_start_loc, max_query_len, seq_lens, block_table;
+    src/flashquant/vllm/impl.py:477-509), constants on the CPU, ``out=`` a slice."""
+    rot, c3, c4 = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    hq, hkv, d, bs = 32, 8, 128, 16
+    seq_lens, chunks = [200, 77, 1030], [40, 77, 129]
+    w = W.decode_workload(seq_lens=seq_lens, num_q_heads=hq, num_kv_heads=hkv, cfg=41)
+    k, v = W.make_kv(w.total_tokens, hkv, d, 41)
+    cache = torch.zeros(w.num_blocks, bs, hkv * (d + 8), dtype=torch.uint8, device=DEV)
+    _C.tq4_compress_append(k.to(DEV), v.to(DEV), cache, w.slot_mapping.to(DEV), rot,
+                           consts["boundaries_128_3"], consts["boundaries_128_4"])
+    cu = torch.zeros(4, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(chunks), 0)
+    n = int(cu[-1])
+    q = torch.randn(n, hq, d, generator=torch.Generator().manual_seed(41)).to(torch.bfloat16)
+    output = torch.zeros(n + 16, hq * d, dtype=torch.bfloat16, device=DEV)   # padded, 2-D
+    ret = _C.paged_tq4_prefill(q.to(DEV), cache, w.block_table.to(DEV), w.seq_lens.to(DEV),
+                               cu.to(DEV), max(chunks), c3, c4, rot, hkv, d, bs,
+                               sm_scale=1.0 / d ** 0.5, out=output[:n])
+    assert ret.data_ptr() == output.data_ptr() and (output[n:] == 0).all()
+    ref32, ref = O.paged_prefill_varlen_stages(q, cache.cpu(), w.block_table, w.seq_lens, cu, c3, c4,
+                                               rot, hkv, d, bs)
+    attention_close(output[:n].view(n, hq, d), ref, ref32, rot, rtol=2.0 ** -8)
