@@ -82,7 +82,6 @@ struct DecodeArgs {
   int n_q;             // query tokens per sequence (fast path; hq counts all of their heads)
   uint64_t wait_ns;    // limit of every wait on another CTA or on a copy
   uint32_t seg_extra;  // test hook: the merge expects this many segment arrivals too many
-  uint32_t xflags;     // experiment switches
   float* slots;  // (num_seqs * S + workers, Hq, D+4), workers = gridDim.x * teams
   uint32_t* status;
   uint32_t off_ring, off_q, off_prefix, off_desc, off_bar, off_cent;
@@ -1293,7 +1292,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
   }  // phase b
 
   if constexpr (FUSE != 0) {
-    if (!(p.xflags & 2u)) fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
+    fused_merge<D, TQ>(p, smem, prefix, total, active, teams, stages);
   }
 }
 
@@ -1866,7 +1865,6 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.n_q = n_q;
   a.wait_ns = device_wait_limit_ns();
   a.seg_extra = uint32_t(g_test_extra_segments.load(std::memory_order_relaxed));
-  { const char* e = getenv("FQ_XFLAGS"); a.xflags = e ? uint32_t(atoi(e)) : 0u; }
   if (!fused_out)
     return fast ? launch_fast<0>(a, sp, ctas, stream) : launch_stream<0>(a, sp, ctas, head_dim, stream);
   a.q_src = q;
@@ -2290,10 +2288,3 @@ extern "C" int fq_split_k_paged_decode_static_status(uint32_t* status, fq_stream
   return FQ_OK;
 }
 
-#ifdef FQ_PROF
-extern "C" void* fq_fast_prof_ptr() {
-  void* p = nullptr;
-  cudaGetSymbolAddress(&p, fq::g_fast_prof);
-  return p;
-}
-#endif

@@ -326,25 +326,9 @@ __device__ __forceinline__ int seq_of_page(const int* prefix, int num_seqs, int6
 }
 
 // FUSE: 0 = streaming phase only; 1 / 2 = single-launch form for bf16 / fp16 q and out
-#ifdef FQ_PROF
-__device__ unsigned long long g_fast_prof[192 * 20 * 8 + 192 * 16 * 8];
-#endif
-#if defined(FQ_PROF) && FQ_PROF >= 2
-#define FQ_T(v) const long long v = clock64()
-#define FQ_ACC(a, t1, t0) a += (t1) - (t0)
-#else
-#define FQ_T(v)
-#define FQ_ACC(a, t1, t0)
-#endif
 
 template <bool KPRMT, int FUSE, bool PSPLIT>
 __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(DecodeArgs p) {
-#ifdef FQ_PROF
-  long long pf_wait = 0, pf_tile = 0, pf_q = 0, pf_end = 0;
-  const long long pf_start = clock64();
-  const unsigned long long pf_g0 = global_timer_ns();
-  unsigned long long pf_g1 = 0, pf_g2 = 0, pf_g3 = 0;
-#endif
   using TQ = typename std::conditional<FUSE == 2, __half, __nv_bfloat16>::type;
   constexpr int D = kFD;
   constexpr int ROWF = D + kPartPad;
@@ -460,9 +444,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       }
   }
 
-#ifdef FQ_PROF
-  pf_g1 = global_timer_ns();  // set-up and this warp's rotation tiles done
-#endif
   // ---- the flat page list and its cut into runs -----------------------------------------------------
   const int64_t total = prefix[p.num_seqs];
   const int64_t workers = int64_t(gridDim.x) * kFTeams;
@@ -499,7 +480,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     const int first_seq = seq_of_page(prefix, p.num_seqs, f0);
 #pragma unroll 1
     for (int i = describer ? 0 : 1; i < n_run; i += 2) {
-      FQ_T(pa);
       if (describer) {
         if ((i & 31) == 0) {
           // ---- run pages i .. i+31: x = valid tokens | flags << 8 | query number << 12,
@@ -556,14 +536,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       } else {
         phys = __shfl_sync(0xffffffffu, entry, ((i - 1) >> 1) & 31);
       }
-      FQ_T(pb);
-      FQ_ACC(pf_end, pb, pa);
       if (i >= stages && !mbar_wait_warp_s(empty + stage * 8, parity, p.wait_ns)) {
         if (lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
         break;
       }
-      FQ_T(pc);
-      FQ_ACC(pf_wait, pc, pb);
       const uint32_t st = ring + uint32_t(stage) * kFStage;
       if (lane == 0) mbar_expect_tx_s(full + stage * 8, kFBS * kFRowG);
       __syncwarp();
@@ -571,8 +547,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
         bulk_g2s_hint_s(st + lane * kFPair,
                         p.kv_cache + int64_t(phys) * (kFBS * kFRowG) + lane * (2 * kFRowG),
                         2 * kFRowG, full + stage * 8, stream_policy);
-      FQ_T(pd);
-      FQ_ACC(pf_tile, pd, pc);
       if (describer) {
         // queries of this page and of the other warp's next page, in run order.  The buffer is
         // single: the team must have taken the previous query into registers, and (single
@@ -605,18 +579,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
           break;
         }
       }
-      FQ_T(pe);
-      FQ_ACC(pf_q, pe, pd);
       stage += 2;
       while (stage >= stages) { stage -= stages; parity ^= 1u; }
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(p.status, FQ_DEV_BAD_BLOCK_INDEX);
-#ifdef FQ_PROF
-    if (lane == 0) {
-      unsigned long long* o = g_fast_prof + (blockIdx.x * 20 + warp) * 8;
-      o[0] = pf_wait; o[1] = pf_q; o[2] = pf_tile; o[3] = pf_end; o[4] = n_run; o[5] = clock64() - pf_start;
-    }
-#endif
     return;
   }
   asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
@@ -682,22 +648,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
     FastRaw raw;
     uint4 d = make_uint4(0u, 0u, 0u, 0u);  // descriptor of the page in `raw`
     {
-      FQ_T(ca);
       if (!mbar_wait_warp_s(full, 0, p.wait_ns)) {
         timed_out = true;
       } else {
         d = lds128<0>(desc);
         fast_load(w, ring, raw);
       }
-      FQ_T(cb);
-      FQ_ACC(pf_wait, cb, ca);
-#ifdef FQ_PROF
-      pf_g2 = global_timer_ns();  // first page in shared memory
-#endif
     }
 #pragma unroll 1
     for (int it = 0; it < n_run && !timed_out; ++it) {
-      FQ_T(cb);
       const int n_valid = d.x & 0xff, flags = (d.x >> 8) & 0xf;
       const int seg_seq = d.y, seg_slot = d.z;
       if (flags & kSegStart) {
@@ -732,8 +691,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
           ++qcnt;
         }
       }
-      FQ_T(cc);
-      FQ_ACC(pf_q, cc, cb);
       FastMid mid;
       fast_front<KPRMT>(w, raw, ring + uint32_t(stage) * kFStage, qf, mid);
       // every load from the stage has been issued above; the fence makes them deliver before
@@ -744,17 +701,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
       if (++stage == stages) { stage = 0; fphase ^= 1; }
       // the next page: its descriptor and raw codes travel under the second half of this tile
       if (it + 1 < n_run) {
-        FQ_T(ca);
         if (!mbar_wait_warp_s(full + stage * 8, fphase, p.wait_ns)) {
           timed_out = true;  // this tile is still finished below
         } else {
           d = lds128<0>(desc + uint32_t((it + 1) & (kFDescRing - 1)) * 16);
           fast_load(w, ring + uint32_t(stage) * kFStage, raw);
         }
-        FQ_T(cx);
-        FQ_ACC(pf_wait, cx, ca);
       }
-      FQ_T(cy);
       // one path for the whole warp (both hold warp-wide operations): the unmasked one only if
       // even the first query token of the step sees all 16 tokens of the page
       const int lim0 = n_valid - back0, lim1 = n_valid - back1;
@@ -762,8 +715,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
         fast_back<false, PSPLIT>(w, mid, g, t >= 2, 16, 16, k_scale_log2, oacc, m_run, l_run);
       else
         fast_back<true, PSPLIT>(w, mid, g, t >= 2, lim0, lim1, k_scale_log2, oacc, m_run, l_run);
-      FQ_T(cd);
-      FQ_ACC(pf_tile, cd, cy);
       if (flags & kSegEnd) {
         // ---- this warp's partial rows of the segment --------------------------------------------
 #pragma unroll
@@ -799,30 +750,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_fast_kernel(De
           if (lane == 0) red_release_add(p.seg_count + seg_seq, 1u);
         }
       }
-      FQ_T(ce);
-      FQ_ACC(pf_end, ce, cd);
     }
 
     if (timed_out && lane == 0) atomicOr(p.status, FQ_DEV_WAIT_TIMEOUT);
-#ifdef FQ_PROF
-    if (lane == 0) {
-      unsigned long long* o = g_fast_prof + (blockIdx.x * 20 + warp) * 8;
-      o[0] = pf_wait; o[1] = pf_q; o[2] = pf_tile; o[3] = pf_end; o[4] = n_run;
-      o[5] = clock64() - pf_start;
-    }
-    pf_g3 = global_timer_ns();  // streaming done
-#endif
   }  // phase b
 
   if constexpr (FUSE != 0) {
-    if (!(p.xflags & 2u)) fused_merge<D, TQ>(p, smem, prefix, total, active, kFTeams, stages);
+    fused_merge<D, TQ>(p, smem, prefix, total, active, kFTeams, stages);
   }
-#ifdef FQ_PROF
-  if (lane == 0 && warp < kCW) {
-    unsigned long long* o = g_fast_prof + (192 * 20 + blockIdx.x * 16 + warp) * 8;
-    o[0] = pf_g0; o[1] = pf_g1; o[2] = pf_g2; o[3] = pf_g3; o[4] = global_timer_ns();
-  }
-#endif
 }
 
 }  // namespace fq
