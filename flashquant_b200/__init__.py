@@ -10,6 +10,7 @@ from .kernels import (  # noqa: F401
     fused_tq_attention_kv,
     pack_2bit,
     paged_decode_partials,
+    paged_tq4_prefill,
     split_k_merge,
     split_k_paged_decode,
     split_k_paged_decode_multi,
