@@ -261,7 +261,9 @@ def run_ours(args):
     d2h = hout.numel() * hout.element_size()
     # the reference-facing call with host buffers: one C-ABI call per step does the copies,
     # the compress-on-append, the decode and the copy back, and waits for the stream
-    step = K.HostDecodeStep(caches[0], planes[0], rot, bk, ck, bv, cv, S, NUM_SEQS, HQ, HKV, D,
+    # (the reference's step writes the main cache row only - its _compress_and_store has no QJL
+    # plane - so the step appends with the one-stage quantiser)
+    step = K.HostDecodeStep(caches[0], None, rot, bk, ck, bv, cv, None, NUM_SEQS, HQ, HKV, D,
                             BS, hbt.shape[1], dtype=hq_.dtype, num_splits=SPLITS,
                             slot_dtype=new_slots.dtype)
 
@@ -274,11 +276,10 @@ def run_ours(args):
 
     def six_arrays(i):
         step(hq_, new_k, new_v, new_slots, hbt, hsl, hout,
-             kv_cache=caches[i % CACHE_COPIES], kq_cache=planes[i % CACHE_COPIES])
+             kv_cache=caches[i % CACHE_COPIES])
 
     def packed(overlap):
-        return lambda i: step.packed(overlap_copies=overlap, kv_cache=caches[i % CACHE_COPIES],
-                                     kq_cache=planes[i % CACHE_COPIES])
+        return lambda i: step.packed(overlap_copies=overlap, kv_cache=caches[i % CACHE_COPIES])
 
     e2e_forms = {}
     for form, fn in (("six_host_arrays", six_arrays), ("packed_block_one_copy", packed(False)),
@@ -362,7 +363,8 @@ def run_ours(args):
                                             for f, (t, _) in e2e_forms.items()},
                     "what": "fq_decode_step_host_packed, one C-ABI call per step: the step's "
                             "q / new K,V token / slot / block table / lengths in one pinned "
-                            "host block -> device, compress-on-append, decode, output -> "
+                            "host block -> device, compress-on-append (one-stage, as the "
+                            "reference's _compress_and_store), decode, output -> "
                             "pinned host, synchronise; the packed cache itself stays in HBM"},
             "roofline": {"bound": "hbm",
                          "kernel": "paged_decode_fast_kernel<KPRMT, FUSE=1, two-term weights> "
