@@ -1,6 +1,6 @@
 """Places the reference's own Python package under ``oracle/_ref/`` (git-ignored).
 
-    python oracle/make_ref.py [/path/to/reference]
+    python oracle/make_ref.py /path/to/reference      (or FLASHQUANT_REFERENCE_ROOT=...)
 
 The reference (ayinedjimi/flashquant) is pure Python on its CPU path, so "building" it is a
 copy of ``src/flashquant`` as it lies in the checkout.  The copy is test and benchmark
@@ -20,7 +20,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 
 
-def make_ref(reference_root: str = "/root/reference") -> str | None:
+def make_ref(reference_root: str | None = None) -> str | None:
+    reference_root = reference_root or os.environ.get("FLASHQUANT_REFERENCE_ROOT", "")
     src = os.path.join(reference_root, "src", "flashquant")
     if not os.path.isdir(src):
         return None
