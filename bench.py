@@ -365,7 +365,9 @@ def run_ours(args):
                             "q / new K,V token / slot / block table / lengths in one pinned "
                             "host block -> device, compress-on-append (one-stage, as the "
                             "reference's _compress_and_store), decode, output -> "
-                            "pinned host, synchronise; the packed cache itself stays in HBM"},
+                            "pinned host, synchronise (the packed one-copy form replays the "
+                            "four operations as one CUDA graph); the packed cache itself "
+                            "stays in HBM"},
             "roofline": {"bound": "hbm",
                          "kernel": "paged_decode_fast_kernel<KPRMT, FUSE=1, two-term weights> "
                                    "(single cooperative launch per call)",

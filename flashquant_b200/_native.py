@@ -89,6 +89,7 @@ SIGNATURES = {
     "fq_paged_tq4_prefill_workspace_bytes": (_sz, [_i, _i, _i]),
     "fq_paged_tq4_prefill": (_i, [_p, _i, _p, _p, _i64, _p, _p, _p, _i, _p, _i, _p, _i, _i, _i, _i,
                                   _i, _i, _i, _i64, _f, _p, _p, _sz, _p]),
+    "fq_decode_step_set_graph": (None, [_i]),
     "fq_decode_step_offsets": (_i, [_i, _i, _i, _i, _i64, _i, _p]),
     "fq_decode_step_host_packed": (_i, [_p, _p, _i, _i, _i, _i64, _p, _p, _p, _p, _i, _p, _i, _p,
                                         _i, _p, _i, _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p, _sz,

@@ -9,7 +9,7 @@ char* last_error_buffer() {
   return buf;
 }
 static std::atomic<uint64_t> g_launches{0};
-void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 // 200 ms by default: two orders of magnitude beyond the longest decode launch, short enough
 // for a stuck launch to give the GPU back promptly.
 static std::atomic<uint64_t> g_wait_limit_ns{200000000ull};

@@ -28,7 +28,7 @@ inline int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-void count_launch();  // library-wide counter of kernel launches (capi.cu)
+void count_launch(uint64_t n = 1);  // library-wide counter of kernel launches (capi.cu)
 
 inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();

@@ -16,7 +16,10 @@
 // (Letting the kernels read page-locked host arrays in place was measured and is slower: the
 // sequence lengths and the block table sit at the head of the decode kernel's dependency
 // chain, and every CTA would fetch them over the bus.)
+#include <atomic>
+#include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "fq_common.cuh"
 
@@ -93,7 +96,8 @@ static int step_kernels_and_result(
     const float* boundaries_v, int n_boundaries_v, const float* centroids_v, int n_centroids_v,
     const float* qjl, int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
     int block_size, int64_t num_blocks, float sm_scale, int num_splits, void* out_host,
-    void* workspace, size_t workspace_bytes, fq_stream_t stream_, bool join_side) {
+    void* workspace, size_t workspace_bytes, fq_stream_t stream_, bool join_side,
+    bool synchronise = true) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const size_t n = size_t(num_seqs);
   int rc = FQ_OK;
@@ -128,11 +132,30 @@ static int step_kernels_and_result(
   if (rc != FQ_OK) return rc;
   cudaError_t e = cudaMemcpyAsync(out_host, out_d, n * num_q_heads * head_dim * 2,
                                   cudaMemcpyDeviceToHost, stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && synchronise) e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess)
     return fail(FQ_ERR_CUDA, "decode step: result copy or synchronise: %s", cudaGetErrorString(e));
   return FQ_OK;
 }
+
+// The packed step as a CUDA graph: one copy in, two launches, one copy out are the same nodes
+// with the same arguments step after step (the block, the staging area and the cache do not
+// move), so the sequence is captured once per distinct argument set and replayed - one
+// submission instead of four.  Per host thread, a handful of entries (a server cycles through
+// a few caches / layers; beyond that the oldest entry is dropped).
+struct StepGraphKey {
+  const void* block; void* out; int dtype, slot64; int64_t bt_stride;
+  const void *kv, *kq, *rot, *bk, *ck, *bv, *cv, *qjl;
+  int nbk, nck, nbv, ncv, num_seqs, hq, hkv, d, bs; int64_t num_blocks; float scale; int splits;
+  void* staging; void* workspace; size_t workspace_bytes; cudaStream_t stream; int device;
+};
+struct StepGraph {
+  StepGraphKey key;
+  cudaGraphExec_t exec;
+  uint64_t kernels;  // kernel nodes: what a replay adds to the library's launch counter
+};
+constexpr int kStepGraphs = 16;
+static std::atomic<int> g_step_graph{1};
 
 }  // namespace fq
 
@@ -261,6 +284,81 @@ extern "C" int fq_decode_step_host_packed(
   const unsigned char* src = static_cast<const unsigned char*>(block_host);
   StepAux* aux = nullptr;
   cudaError_t ce = cudaSuccess;
+  if (!overlap_copies && g_step_graph.load(std::memory_order_relaxed)) {
+    static thread_local std::vector<StepGraph> graphs;
+    StepGraphKey key;
+    std::memset(&key, 0, sizeof(key));  // padding too: the key is compared byte by byte
+    key.block = block_host; key.out = out_host; key.dtype = int(dtype); key.slot64 = slot_is_int64;
+    key.bt_stride = block_table_stride; key.kv = kv_cache; key.kq = kq_cache; key.rot = rotation;
+    key.bk = boundaries_k; key.ck = centroids_k; key.bv = boundaries_v; key.cv = centroids_v;
+    key.qjl = qjl; key.nbk = n_boundaries_k; key.nck = n_centroids_k; key.nbv = n_boundaries_v;
+    key.ncv = n_centroids_v; key.num_seqs = num_seqs; key.hq = num_q_heads; key.hkv = num_kv_heads;
+    key.d = head_dim; key.bs = block_size; key.num_blocks = num_blocks; key.scale = sm_scale;
+    key.splits = num_splits; key.staging = staging; key.workspace = workspace;
+    key.workspace_bytes = workspace_bytes; key.stream = stream;
+    cudaGetDevice(&key.device);
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
+    for (const StepGraph& g : graphs)
+      if (std::memcmp(&g.key, &key, sizeof(key)) == 0) {
+        exec = g.exec;
+        kernels = g.kernels;
+      }
+    // captured on the library's own side stream (the caller's may be the legacy default
+    // stream, which cannot capture); the graph is then launched into the caller's stream
+    cudaStream_t cap = nullptr;
+    if (!exec && step_aux(&aux) == FQ_OK) cap = aux->stream;
+    if (cap && cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();
+      cap = nullptr;
+    }
+    if (cap) {
+      fq_stream_t cap_ = cap;
+      const uint64_t launches_at_capture = fq_launch_count();
+      ce = cudaMemcpyAsync(st, src, L.out, cudaMemcpyHostToDevice, cap);
+      int rc = ce == cudaSuccess
+                   ? step_kernels_and_result(L, st, nullptr, dtype, slot_is_int64,
+                                             block_table_stride, kv_cache, kq_cache, rotation,
+                                             boundaries_k, n_boundaries_k, centroids_k,
+                                             n_centroids_k, boundaries_v, n_boundaries_v,
+                                             centroids_v, n_centroids_v, qjl, num_seqs,
+                                             num_q_heads, num_kv_heads, head_dim, block_size,
+                                             num_blocks, sm_scale, num_splits, out_host, workspace,
+                                             workspace_bytes, cap_, false, false)
+                   : FQ_ERR_CUDA;
+      const uint64_t after_issue = fq_launch_count();
+      cudaGraph_t graph = nullptr;
+      const cudaError_t end = cudaStreamEndCapture(cap, &graph);
+      kernels = 0;  // the capture counted its launches once; they only run at the replay
+      const uint64_t captured = after_issue - launches_at_capture;
+      if (rc == FQ_OK && end == cudaSuccess && graph &&
+          cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+        if (int(graphs.size()) >= kStepGraphs) {
+          cudaGraphExecDestroy(graphs.front().exec);
+          graphs.erase(graphs.begin());
+        }
+        kernels = captured;
+        graphs.push_back(StepGraph{key, exec, kernels});
+      } else {
+        exec = nullptr;
+        cudaGetLastError();  // a capture that could not be completed: issue the step directly
+      }
+      if (graph) cudaGraphDestroy(graph);
+    }
+    if (exec) {
+      ce = cudaGraphLaunch(exec, stream);
+      if (ce == cudaSuccess) {
+        // (the launches counted during the capture itself stand for this first replay)
+        if (!cap) count_launch(kernels);
+        ce = cudaStreamSynchronize(stream);
+      }
+      if (ce != cudaSuccess)
+        return fail(FQ_ERR_CUDA, "decode step: graph launch or synchronise: %s",
+                    cudaGetErrorString(ce));
+      return FQ_OK;
+    }
+    ce = cudaSuccess;
+  }
   if (overlap_copies) {
     // what the compress-on-append reads on the caller's stream, the rest on the side stream
     int rc = step_aux(&aux);
@@ -283,4 +381,8 @@ extern "C" int fq_decode_step_host_packed(
                                  n_centroids_v, qjl, num_seqs, num_q_heads, num_kv_heads, head_dim,
                                  block_size, num_blocks, sm_scale, num_splits, out_host, workspace,
                                  workspace_bytes, stream_, overlap_copies != 0);
+}
+
+extern "C" void fq_decode_step_set_graph(int enabled) {
+  fq::g_step_graph.store(enabled ? 1 : 0, std::memory_order_relaxed);
 }

@@ -351,11 +351,27 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
         for name, t in (("key", new_k), ("value", new_v), ("slot_mapping", new_slots),
                         ("seq_lens", lens), ("block_table", bt), ("q", w.q)):
             views[name].copy_(t)
-        for overlap in (False, True):
+        # (False, False: the second call replays the graph that the first one captured)
+        for overlap in (False, False, True):
             views["out"].zero_()
             got = step.packed(overlap_copies=overlap)
             assert torch.equal(got.view(torch.int16), ref.cpu().view(torch.int16)), overlap
             assert torch.equal(grown, ref_cache)
+        # new contents in the same block are seen by the replayed graph
+        q_it = (w.q.float() * 1.5).to(w.q.dtype)
+        views["q"].copy_(q_it)
+        got = step.packed(overlap_copies=False)
+        ref_it = K.split_k_paged_decode(q_it.to(DEV), ref_cache, bt.to(DEV), lens.to(DEV), ck, cv,
+                                        rot, hkv, d, bs, num_splits=2)
+        assert torch.equal(got.view(torch.int16), ref_it.cpu().view(torch.int16))
+        # and the same step issued call by call
+        K.N.load().fq_decode_step_set_graph(0)
+        try:
+            views["q"].copy_(w.q)
+            got = step.packed(overlap_copies=False)
+            assert torch.equal(got.view(torch.int16), ref.cpu().view(torch.int16))
+        finally:
+            K.N.load().fq_decode_step_set_graph(1)
         assert K.workspace_status(step.workspace) == 0
     hout.copy_(ref.cpu())
     # and against the oracle end to end
