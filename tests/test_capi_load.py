@@ -54,6 +54,37 @@ def test_argument_errors_need_no_gpu(lib_path):
     assert lib.fq_paged_decode_workspace_bytes(32, 32, 8, 128, 8) >= 32 * 32 * 8 * 132 * 4
 
 
+def test_host_step_layout_and_new_entry_points_need_no_gpu(lib_path):
+    """Host-only parts of the newer entry points: the packed step's offsets, workspace sizes and
+    argument checks that run before any CUDA call."""
+    from flashquant_b200 import _native
+    lib = _native.load()
+    off = (ctypes.c_uint64 * 8)()
+    assert lib.fq_decode_step_offsets(32, 32, 8, 128, 256, 1, off) == 0
+    key, value, slots, lens, table, q, out, total = list(off)
+    assert all(o % 256 == 0 for o in off)
+    assert key == 0 and key < value < slots < lens < table < q < out < total
+    assert value - key >= 32 * 8 * 128 * 2 and slots - value >= 32 * 8 * 128 * 2
+    assert lens - slots >= 32 * 8 and table - lens >= 32 * 4 and q - table >= 32 * 256 * 4
+    assert out - q >= 32 * 32 * 128 * 2 and total - out >= 32 * 32 * 128 * 2
+    assert total == lib.fq_decode_step_host_staging_bytes(32, 32, 8, 128, 256, 1)
+    assert lib.fq_decode_step_offsets(32, 32, 8, 128, 256, 1, None) == -1
+    assert lib.fq_decode_step_offsets(-1, 32, 8, 128, 256, 1, off) == -1
+    # paged prefill: sizes, and refusals that precede every launch
+    need = lib.fq_paged_tq4_prefill_workspace_bytes(1000, 32, 128)
+    assert need >= 256 + 1000 * 32 * 128 * (2 + 4)
+    assert lib.fq_paged_tq4_prefill_workspace_bytes(-1, 32, 128) == 0
+    args = [None, 2, None, None, 4, None, None, None, 8, None, 16, None, 2, 100, 50, 32, 8, 128, 16,
+            64, 0.1, None, None, 0, None]
+    assert lib.fq_paged_tq4_prefill(*args) == -1 and b"null" in lib.fq_last_error_string()
+    empty = list(args)
+    empty[13] = 0                                   # no query tokens: nothing to do
+    assert lib.fq_paged_tq4_prefill(*empty) == 0
+    bad = list(args)
+    bad[12] = -1
+    assert lib.fq_paged_tq4_prefill(*bad) == -1
+
+
 def test_package_refuses_cpu_tensors(lib_path):
     import torch
     import flashquant_b200 as fq
