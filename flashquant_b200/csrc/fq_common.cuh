@@ -29,6 +29,8 @@ inline int fail(int code, const char* fmt, ...) {
 }
 
 void count_launch(uint64_t n = 1);  // library-wide counter of kernel launches (capi.cu)
+uint64_t settings_epoch();  // changes whenever a process-wide setter is called (capi.cu)
+void settings_changed();
 
 inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();

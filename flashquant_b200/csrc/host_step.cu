@@ -148,6 +148,7 @@ struct StepGraphKey {
   const void *kv, *kq, *rot, *bk, *ck, *bv, *cv, *qjl;
   int nbk, nck, nbv, ncv, num_seqs, hq, hkv, d, bs; int64_t num_blocks; float scale; int splits;
   void* staging; void* workspace; size_t workspace_bytes; cudaStream_t stream; int device;
+  uint64_t settings;  // process-wide switches and limits are baked into the recorded launches
 };
 struct StepGraph {
   StepGraphKey key;
@@ -297,6 +298,7 @@ extern "C" int fq_decode_step_host_packed(
     key.splits = num_splits; key.staging = staging; key.workspace = workspace;
     key.workspace_bytes = workspace_bytes; key.stream = stream;
     cudaGetDevice(&key.device);
+    key.settings = settings_epoch();
     cudaGraphExec_t exec = nullptr;
     uint64_t kernels = 0;
     for (const StepGraph& g : graphs)

@@ -2017,18 +2017,22 @@ int decode_tokens(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
 
 extern "C" void fq_paged_decode_set_single_launch(int enabled) {
   g_single_launch.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  settings_changed();
 }
 
 extern "C" void fq_paged_decode_set_fast_path(int enabled) {
   g_fast_path.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  settings_changed();
 }
 
 extern "C" void fq_paged_decode_set_weight_split(int enabled) {
   g_weight_split.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  settings_changed();
 }
 
 extern "C" void fq_paged_decode_test_expect_extra_segments(int n) {
   g_test_extra_segments.store(n < 0 ? 0 : n, std::memory_order_relaxed);
+  settings_changed();
 }
 
 extern "C" int fq_split_k_paged_decode_qjl(
