@@ -57,6 +57,13 @@ constexpr float kMaxSlack = 6.f;                // ... and may exceed 1 by 2^6 b
 constexpr int kMergeHeads = 8;                  // query heads per merge job
 constexpr int kMaxParts = 4096;   // partial rows one sequence can have (teams + splits)
 constexpr int kPartChunk = 128;  // rows merged per pass
+// Single-launch merge of a sequence with very many partial rows (few KV heads per GPU: sixteen
+// one-warp teams per CTA): the rows are cut into up to kMaxMergeChunks chunks, one merge job
+// each; the job that finishes last merges the chunks' rows.  kMaxChunkJobs bounds
+// (sequences x head groups) of such a call (its counters sit behind the per-sequence ones).
+constexpr int kMaxMergeChunks = 16;
+constexpr int kRowsPerMergeChunk = 20;  // one batch of row loads per merge job
+constexpr int kMaxChunkJobs = 1024;
 // shared memory of a merge job of the single-launch form besides Pi: rounded rows, row list
 constexpr uint32_t kMergeScratchBytes =
     (kMergeHeads * 128 + kMergeHeads * kComputeThreads / 2 + 64 + kMaxParts + 4) * 4;
@@ -93,6 +100,9 @@ struct DecodeArgs {
   uint32_t* q_count;      // [kMaxSeqs] rotated tiles of a sequence that are stored
   uint32_t* seg_count;    // [kMaxSeqs] (segment, warp) pairs of a sequence that are stored
   uint32_t* merge_count;  // [kMaxSeqs] merge jobs of a sequence that are finished
+  uint32_t* chunk_count;  // [kMaxChunkJobs] finished chunks of a (sequence, head group) merge
+  float* chunk_rows;      // [(job * merge_chunks + chunk) * kMergeHeads + head][D + 4]
+  int merge_chunks;       // 1: one job merges all rows of a (sequence, head group)
   // two-stage (QJL) scoring only: logit += gamma * sqrt(pi/2)/m * <S q, signs>
   const uint8_t* kq_cache;  // (num_blocks, block_size, Hkv * (D/8 + 4)): sign bits | gamma
   const float* qjl;         // S (D, D)
@@ -450,8 +460,11 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
   const int tid = threadIdx.x;
   const int hgroups = (p.hq + kMergeHeads - 1) / kMergeHeads;
   const int jobs = p.num_seqs * hgroups;
+  // C > 1: the rows of a (sequence, head group) are cut into C chunks, one merge job each;
+  // the job that finishes last merges the C rows the chunks leave behind
+  const int C = p.merge_chunks;
   compute_sync();  // every warp of the CTA has left the table and the rings
-  if (int(blockIdx.x) >= jobs) return;
+  if (int(blockIdx.x) >= jobs * C) return;
 
   float* pi_s = reinterpret_cast<float*>(smem);  // [k][j]
   float* o_s = reinterpret_cast<float*>(smem + p.off_ring);  // [8][D]
@@ -469,7 +482,9 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
   const int d = tid % D, hh0 = tid / D;
   const int grp = tid / TPG, mh = (tid % TPG) / (D / 4), dq = tid % (D / 4);
 
-  for (int job = blockIdx.x; job < jobs; job += gridDim.x) {
+  int* last_s = n_parts_s + 1;  // C > 1: whether this job was the last chunk of its rows
+  for (int sub = blockIdx.x; sub < jobs * C; sub += gridDim.x) {
+    const int job = sub / C, chunk = sub - job * C;
     const int seq = job / hgroups, h0 = (job - seq * hgroups) * kMergeHeads;
     // ---- the sequence's partial rows (one lane per split), and the wait until all of them
     // are stored ---------------------------------------------------------------------------
@@ -519,24 +534,28 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
     compute_sync();
     const int n_parts = *n_parts_s;
     // rows were written by other SMs during this launch: read them past the L1
-    auto row_ptr = [&](int i, int h) { return p.slots + (int64_t(part_row[i]) * p.hq + h) * ROWF; };
+    // (`chunks`: the rows that the C chunk jobs of this (sequence, head group) left behind)
+    auto row_ptr = [&](int i, int h, bool chunks) {
+      return chunks ? p.chunk_rows + ((int64_t(job) * C + i) * kMergeHeads + (h - h0)) * ROWF
+                    : p.slots + (int64_t(part_row[i]) * p.hq + h) * ROWF;
+    };
 
     // ---- G groups of threads take every G-th partial row; thread (head mh, four coordinates
     // from 4*dq) keeps up to kBatch rows in registers so that all loads of a job are in
     // flight together, and recomputes the weights of its head itself -------------------------
-    {
+    auto accumulate = [&](int lo, int hi, bool chunks) {
       const int h = h0 + mh;
       float m_run = -INFINITY, den = 0.f;
       float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c0 = grp; c0 < n_parts; c0 += G * kBatch) {
+      for (int c0 = lo + grp; c0 < hi; c0 += G * kBatch) {
         float2 ml[kBatch];
         float4 v[kBatch];
 #pragma unroll
         for (int x = 0; x < kBatch; ++x) {
           ml[x] = make_float2(-INFINITY, 0.f);
           v[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (c0 + x * G < n_parts && h < p.hq) {
-            const float* row = row_ptr(c0 + x * G, h);
+          if (c0 + x * G < hi && h < p.hq) {
+            const float* row = row_ptr(c0 + x * G, h, chunks);
             ml[x] = __ldcg(reinterpret_cast<const float2*>(row + D));
             v[x] = __ldcg(reinterpret_cast<const float4*>(row) + dq);
           }
@@ -560,25 +579,58 @@ __device__ __forceinline__ void fused_merge(const DecodeArgs& p, unsigned char* 
       }
       reinterpret_cast<float4*>(num_s + (grp * kMergeHeads + mh) * D)[dq] = num;
       if (dq == 0) ml_s[grp * kMergeHeads + mh] = make_float2(m_run, den);
-    }
-    compute_sync();
-    // ---- combine the groups; thread (head hh, coordinate d) from here on --------------------
+    };
+    // ---- combine the groups; thread (head hh, coordinate d).  `finish`: normalise and round
+    // into o_s; otherwise leave the un-normalised row of this chunk in the workspace -----------
+    auto combine = [&](bool finish) {
 #pragma unroll
-    for (int ps = 0; ps < PASSES; ++ps) {
-      const int hh = hh0 + ps * HP;
-      float m_all = -INFINITY;
+      for (int ps = 0; ps < PASSES; ++ps) {
+        const int hh = hh0 + ps * HP;
+        float m_all = -INFINITY;
 #pragma unroll
-      for (int gi = 0; gi < G; ++gi) m_all = fmaxf(m_all, ml_s[gi * kMergeHeads + hh].x);
-      float den = 0.f, num = 0.f;
+        for (int gi = 0; gi < G; ++gi) m_all = fmaxf(m_all, ml_s[gi * kMergeHeads + hh].x);
+        float den = 0.f, num = 0.f;
 #pragma unroll
-      for (int gi = 0; gi < G; ++gi) {
-        const float2 ml = ml_s[gi * kMergeHeads + hh];
-        const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - m_all);
-        den = fmaf(w, ml.y, den);
-        num = fmaf(w, num_s[(gi * kMergeHeads + hh) * D + d], num);
+        for (int gi = 0; gi < G; ++gi) {
+          const float2 ml = ml_s[gi * kMergeHeads + hh];
+          const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - m_all);
+          den = fmaf(w, ml.y, den);
+          num = fmaf(w, num_s[(gi * kMergeHeads + hh) * D + d], num);
+        }
+        if (finish) {
+          const float o = (h0 + hh < p.hq && den > 0.f) ? num / den : 0.f;
+          o_s[hh * D + d] = to_f32(from_f32<T>(o));  // the reference rounds the rotated output
+        } else {
+          float* row = p.chunk_rows + ((int64_t(job) * C + chunk) * kMergeHeads + hh) * ROWF;
+          row[d] = num;
+          if (d == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m_all, den);
+        }
       }
-      const float o = (h0 + hh < p.hq && den > 0.f) ? num / den : 0.f;
-      o_s[hh * D + d] = to_f32(from_f32<T>(o));  // the reference rounds the rotated output
+    };
+    if (C == 1) {
+      accumulate(0, n_parts, false);
+      compute_sync();
+      combine(true);
+    } else {
+      accumulate(int(int64_t(n_parts) * chunk / C), int(int64_t(n_parts) * (chunk + 1) / C), false);
+      compute_sync();
+      combine(false);
+      __threadfence();  // this thread's part of the chunk row, before the count below
+      compute_sync();
+      if (tid == 0) {
+        const bool last = atomicAdd(p.chunk_count + job, 1u) == uint32_t(C - 1);
+        if (last) p.chunk_count[job] = 0u;  // for the next call
+        __threadfence();                    // the other chunks' rows, after the count
+        *last_s = last ? 1 : 0;
+      }
+      compute_sync();
+      if (*last_s == 0) {
+        compute_sync();  // (last_s and the scratch are reused by the next job)
+        continue;
+      }
+      accumulate(0, C, true);
+      compute_sync();
+      combine(true);
     }
     compute_sync();
     if (!pi_ready) {
@@ -1485,22 +1537,40 @@ static int device_sm_count() {
 // status word at 0; three counter arrays of kMaxSeqs words (single-launch form) at 256;
 // the rotated query; the partial rows
 struct WorkspaceLayout {
-  size_t count_off, q_rot_off, slots_off, total;
+  size_t count_off, q_rot_off, slots_off, chunk_off, total;
+  int merge_chunks;
 };
 
 static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 // `splits` <= 0 sizes for the largest split count
+// Chunks that the single-launch merge cuts the rows of a (sequence, head group) into: a
+// sequence has about its share of the teams plus a row per split boundary.
+static int merge_chunks_for(int num_seqs, int hq, int splits, int workers) {
+  const int hgroups = (hq + kMergeHeads - 1) / kMergeHeads;
+  if (num_seqs <= 0 || int64_t(num_seqs) * hgroups > kMaxChunkJobs) return 1;
+  const int64_t rows = (int64_t(workers) + int64_t(num_seqs) * splits) / num_seqs + 1;
+  const int64_t c = (rows + kRowsPerMergeChunk - 1) / kRowsPerMergeChunk;
+  return c < 1 ? 1 : (c > kMaxMergeChunks ? kMaxMergeChunks : int(c));
+}
+
 static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits, int workers) {
   if (splits <= 0) splits = kMaxSplits;
   const int ctas = workers;
   WorkspaceLayout w;
   w.count_off = 256;
-  w.q_rot_off = up256(w.count_off + 3 * size_t(kMaxSeqs) * sizeof(uint32_t));
+  // three counters per sequence, then one per (sequence, head group) of a chunked merge
+  w.q_rot_off = up256(w.count_off + (3 * size_t(kMaxSeqs) + kMaxChunkJobs) * sizeof(uint32_t));
   // room for fp16(q Pi^T) and, behind it, fp16(q S^T) of the two-stage estimator
   w.slots_off = up256(w.q_rot_off + 2 * size_t(num_seqs) * hq * d * sizeof(__half));
-  w.total = up256(w.slots_off +
-                  (size_t(num_seqs) * splits + ctas) * hq * (d + kPartPad) * sizeof(float));
+  w.chunk_off = up256(w.slots_off +
+                      (size_t(num_seqs) * splits + ctas) * hq * (d + kPartPad) * sizeof(float));
+  w.merge_chunks = merge_chunks_for(num_seqs, hq, splits, workers);
+  const size_t hgroups = size_t(hq + kMergeHeads - 1) / kMergeHeads;
+  w.total = w.merge_chunks > 1
+                ? up256(w.chunk_off + size_t(num_seqs) * hgroups * w.merge_chunks * kMergeHeads *
+                                          (d + kPartPad) * sizeof(float))
+                : w.chunk_off;
   return w;
 }
 
@@ -1874,6 +1944,9 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   a.q_count = reinterpret_cast<uint32_t*>(ws + w.count_off);
   a.seg_count = a.q_count + kMaxSeqs;
   a.merge_count = a.seg_count + kMaxSeqs;
+  a.chunk_count = a.merge_count + kMaxSeqs;
+  a.chunk_rows = reinterpret_cast<float*>(ws + w.chunk_off);
+  a.merge_chunks = fused_out ? w.merge_chunks : 1;
   if (kq_cache) {
     a.kq_cache = kq_cache;
     a.qjl = qjl;

@@ -181,6 +181,24 @@ def test_short_runs_that_cross_sequences_repeat_bit_for_bit(consts):
     close(merged, run_oracle(w, cache, consts), consts, got_rot32=rows_from_partials(first))
 
 
+@pytest.mark.parametrize("hq,hkv,seq_lens", [
+    (8, 1, [9000, 5000, 40]),        # 16 one-warp teams per CTA: several hundred rows per sequence
+    (16, 2, [7000, 0, 3000, 555]),   # two head groups, an empty sequence
+    (64, 8, [30000]),                # the specialised kernel, one sequence over all teams
+])
+def test_sequences_with_hundreds_of_partial_rows(consts, hq, hkv, seq_lens):
+    """Few sequences over all teams of the GPU: the single launch cuts the rows of a sequence
+    into chunks, merges each in its own job and the chunks' rows in the job that finishes last."""
+    w = W.decode_workload(seq_lens=seq_lens, num_q_heads=hq, num_kv_heads=hkv, cfg=27)
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    for splits in (1, 8):
+        out = run_gpu(w, cache, consts, num_splits=splits)
+        close(out, ref, consts, rtol=2.0 ** -9)
+        again = run_gpu(w, cache, consts, num_splits=splits)
+        assert torch.equal(out, again)
+
+
 def test_token_ranges_on_two_groups_merge_like_one(consts):
     """What a cross-GPU split does: group 0 attends over the first pages of every sequence,
     group 1 over the rest; merging the two partial rows equals attending over everything."""
