@@ -30,6 +30,7 @@
 #include <type_traits>
 
 #include "fq_common.cuh"
+#include "centroid_scale.cuh"
 
 namespace fq {
 
@@ -171,6 +172,8 @@ struct PrefillArgs {
   int block_size;
   int64_t num_blocks;
   int round_out;  // FQ_BF16 / FQ_F16: rows are rounded to that type before they are stored
+  // beta_k, beta_v of the scaled fp16 centroid tables (centroid_scale_kernel, run just before)
+  const float* scales;
 };
 
 template <int D>
@@ -302,10 +305,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     tmem_alloc(tmem_holder, kPfTmemCols);
     tmem_relinquish();
   }
+  // tables of fp16(c / beta): beta_k folds into the score scale, beta_v into the weights
+  const float beta_k = p.scales[0], beta_v = p.scales[1];
+  const float rbk = 1.f / beta_k, rbv = 1.f / beta_v;
   for (int e = tid; e < 256; e += kPfThreads) {
     const int hi = e >> 4, lo = e & 15;
-    lut_k[e] = pack_half2(hi < p.nck ? p.cent_k[hi] : 0.f, lo < p.nck ? p.cent_k[lo] : 0.f);
-    lut_v[e] = pack_half2(hi < p.ncv ? p.cent_v[hi] : 0.f, lo < p.ncv ? p.cent_v[lo] : 0.f);
+    lut_k[e] = pack_half2(hi < p.nck ? p.cent_k[hi] * rbk : 0.f, lo < p.nck ? p.cent_k[lo] * rbk : 0.f);
+    lut_v[e] = pack_half2(hi < p.ncv ? p.cent_v[hi] * rbv : 0.f, lo < p.ncv ? p.cent_v[lo] * rbv : 0.f);
   }
   // Q tile -> [k-chunk][row][16 B]
   {
@@ -333,7 +339,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t h =
-          uint32_t(__half_as_ushort(__float2half_rn(i < p.nck ? p.cent_k[i] : 0.f)));
+          uint32_t(__half_as_ushort(__float2half_rn(i < p.nck ? p.cent_k[i] * rbk : 0.f)));
       const uint32_t lo8 = (h & 0xffu) << (8 * (i & 3)), hi8 = (h >> 8) << (8 * (i & 3));
       if (i < 4) { tl0 |= lo8; th0 |= hi8; } else { tl1 |= lo8; th1 |= hi8; }
     }
@@ -434,6 +440,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     umma_commit(bar_s + (tile & 1));
   };
 
+  const float k_scale = p.scale_log2 * beta_k, v_scale = 256.f * beta_v;
   float m_run = -INFINITY, l_run = 0.f;
   const int q_pos = m0 + row;
   bool dead = false;
@@ -449,7 +456,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     }
     if (!mbar_wait(bar_k, 0)) dead = true;
     if (!dead) {
-      if (tid < kPfN) nk_s[tid] = tile_norm(0, true) * p.scale_log2;
+      if (tid < kPfN) nk_s[tid] = tile_norm(0, true) * k_scale;
       dequantise(0, true, S::kOffK);
     }
     fence_async_smem();
@@ -471,7 +478,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (more) {
       if (!mbar_wait(bar_k, (tile + 1) & 1)) dead = true;
       if (!dead) {
-        if (tid < kPfN) nk_s[((tile + 1) & 1) * kPfN + tid] = tile_norm(tile + 1, true) * p.scale_log2;
+        if (tid < kPfN) nk_s[((tile + 1) & 1) * kPfN + tid] = tile_norm(tile + 1, true) * k_scale;
         dequantise(tile + 1, true, S::kOffK + ((tile + 1) & 1) * S::kOpKV);
       }
     }
@@ -482,7 +489,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
     if (!dead) {
       if (tid < kPfN) {
         const float nv = tile_norm(tile, false);
-        vs_s[tid] = nv * 256.f;  // 2^kPfPScaleLog2
+        vs_s[tid] = nv * v_scale;  // beta_v 2^kPfPScaleLog2
         lv_s[tid] = fmaxf(fast_log2(nv), -40.f);
       }
       dequantise(tile, false, S::kOffV);
@@ -665,6 +672,21 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   if (warp == 0) tmem_dealloc(tmem_base, kPfTmemCols);
 }
 
+__global__ void __launch_bounds__(kScaleThreads) centroid_scale_kernel(
+    const float* __restrict__ cent_k, int nck, const float* __restrict__ cent_v, int ncv,
+    uint32_t* __restrict__ cache) {
+  __shared__ __align__(16) unsigned char cent[kCentBytes];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (warp == 1) {
+    const int i = lane & 15;
+    float c = 0.f;
+    if (lane < 16) { if (i < nck) c = cent_k[i]; } else { if (i < ncv) c = cent_v[i]; }
+    stage_centroids(cent, c, nck, ncv, cache, lane);
+  }
+  __syncthreads();
+  scale_centroid_tables(cent, nck, ncv, tid, cache);
+}
+
 // Merge of the slices' partial rows: o = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i with
 // M = max_i m_i (a slice without keys has m = -inf, l = 0).  32 threads per query row.
 template <int D>
@@ -719,6 +741,15 @@ static int launch_prefill_t(const PrefillArgs& a, cudaStream_t stream) {
   prefill_merge_kernel<D><<<unsigned((a.total_rows + 7) / 8), 256, 0, stream>>>(
       a.part, a.n_splits, a.total_rows, a.o_rot);
   return check_launch("prefill merge kernel launch");
+}
+
+// beta_k, beta_v for the launch that follows: found in (or left at) bytes 64..255 of the
+// workspace head, the record the decode kernels keep in theirs
+static int centroid_scales(PrefillArgs& a, unsigned char* ws, cudaStream_t stream) {
+  uint32_t* cache = reinterpret_cast<uint32_t*>(ws + kScaleCacheOffset);
+  centroid_scale_kernel<<<1, kScaleThreads, 0, stream>>>(a.cent_k, a.nck, a.cent_v, a.ncv, cache);
+  a.scales = reinterpret_cast<const float*>(cache + 32);
+  return check_launch("centroid scale kernel launch");
 }
 
 constexpr int kPfMaxSplits = 64;  // slices of the keys for a single query token
@@ -824,6 +855,8 @@ static int attention_common(const void* q, fq_dtype dtype, const uint8_t* k_pack
       if (rotate_is_few_rows(rows)) a.o_rot = nullptr;
     }
   }
+  rc = centroid_scales(a, ws, stream);
+  if (rc != FQ_OK) return rc;
   rc = launch_prefill_t<128>(a, stream);
   if (rc != FQ_OK) return rc;
   if (a.n_splits > 1 && a.o_rot == nullptr)
@@ -930,6 +963,8 @@ extern "C" int fq_paged_tq4_prefill(const void* q, fq_dtype dtype, const uint8_t
   a.block_size = block_size;
   a.num_blocks = num_blocks;
   a.round_out = int(dtype);
+  rc = centroid_scales(a, ws, s);
+  if (rc != FQ_OK) return rc;
   rc = launch_prefill_t<128, true>(a, s);
   if (rc != FQ_OK) return rc;
   return rotate_back(o_rot, dtype, rotation, out, rows, head_dim, s);

@@ -16,10 +16,9 @@ from parity import attention_close
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-# The tensor-core attention kernel keeps plain fp16 centroid tables (no common scale): its
-# un-rounded rows agree with the reference's to 2^-8 of the entry (stated, as for the prefill
-# over contiguous buffers).
-PAGED_PREFILL_RTOL = 2.0 ** -8
+# Scaled fp16 centroid tables as in the decode kernels: the rows agree with the reference's
+# un-rounded rows to 2^-10 of the entry.
+PAGED_PREFILL_RTOL = 2.0 ** -10
 
 
 def build(consts, seq_lens, chunks, hq=32, hkv=8, cfg=31, dtype=torch.bfloat16, block_size=16):
