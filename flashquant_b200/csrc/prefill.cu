@@ -362,34 +362,43 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   };
   // Paged mode, ALL threads: the tile's codes and norms gathered through the block table, 16
   // bytes per thread (thread = (token, quarter of its 64 code bytes)) and one norm for the
-  // first 64 threads; tokens past the end arrive as zeros.
+  // first 64 threads; tokens past the end arrive as zeros.  The token rows of a tile (byte
+  // offsets into the cache, -1 past the end) are looked up one tile before its key gather, so
+  // that no gather waits for a block-table load; the value gather of the same tile, one
+  // iteration later, reuses them.
   [[maybe_unused]] bool bad_page = false;
-  [[maybe_unused]] auto gather_codes = [&](int tile, bool is_k) {
-    const int tok = tid >> 2, piece = tid & 3;
-    const int row_bytes = p.hkv * (D + 8);
+  [[maybe_unused]] auto token_row = [&](int t) -> int64_t {
+    if (t >= kv_end) return -1;
+    const int page = t / p.block_size;
+    int64_t phys = p.block_table[int64_t(b) * p.bt_stride + page];
+    if (phys < 0 || phys >= p.num_blocks) {  // reported, not followed
+      phys = 0;
+      bad_page = true;
+    }
+    return (phys * p.block_size + (t - page * p.block_size)) * int64_t(p.hkv * (D + 8));
+  };
+  struct TileRows {
+    int64_t code, norm;  // rows of token tid/4 (codes) and of token tid (norm; threads 0..63)
+  };
+  [[maybe_unused]] auto tile_rows = [&](int tile) {
+    TileRows r;
+    r.code = token_row(tile * kPfN + (tid >> 2));
+    r.norm = tid < kPfN ? token_row(tile * kPfN + tid) : -1;
+    return r;
+  };
+  [[maybe_unused]] auto gather_codes = [&](const TileRows& r, bool is_k) {
+    const int piece = tid & 3;
     const int code_off = (is_k ? 0 : p.hkv * (D / 2 + 4)) + hkv * (D / 2);
     const int norm_off = (is_k ? 0 : p.hkv * (D / 2 + 4)) + p.hkv * (D / 2) + 4 * hkv;
-    auto token_row = [&](int t, bool& valid) -> const uint8_t* {
-      valid = t < kv_end;
-      if (!valid) return p.kv_cache;
-      const int page = t / p.block_size;
-      int64_t phys = p.block_table[int64_t(b) * p.bt_stride + page];
-      if (phys < 0 || phys >= p.num_blocks) {  // reported, not followed
-        phys = 0;
-        bad_page = true;
-      }
-      return p.kv_cache + (phys * p.block_size + (t - page * p.block_size)) * int64_t(row_bytes);
-    };
-    bool valid;
-    const uint8_t* src = token_row(tile * kPfN + tok, valid);
     cp_async16(smem_u32(smem + S::kOffRaw + (is_k ? 0 : S::kRawTile)) + tid * 16,
-               src + code_off + piece * 16, valid);
-    if (tid < kPfN) {
-      const uint8_t* nsrc = token_row(tile * kPfN + tid, valid);
-      cp_async4(smem_u32(is_k ? nk_raw : nv_raw) + tid * 4, nsrc + norm_off, valid);
-    }
+               p.kv_cache + (r.code < 0 ? 0 : r.code) + code_off + piece * 16, r.code >= 0);
+    if (tid < kPfN)
+      cp_async4(smem_u32(is_k ? nk_raw : nv_raw) + tid * 4,
+                p.kv_cache + (r.norm < 0 ? 0 : r.norm) + norm_off, r.norm >= 0);
     cp_async_arrive(is_k ? bar_k : bar_v);
   };
+  // rows of the tile whose values are gathered next / whose keys are gathered next
+  [[maybe_unused]] TileRows rows_v{-1, -1}, rows_k{-1, -1};
   // all threads: codes of the landed tile -> fp16 operand tile at `op_off`
   auto dequantise = [&](int tile, bool is_k, uint32_t op_off) {
     const int n_tok = tile_tokens(tile);
@@ -448,8 +457,11 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
   // ---- prologue: K(0) -> operand, S(0) issued, K(1) and V(0) on their way ------------------
   if (n_tiles > 0) {
     if constexpr (PAGED) {
-      gather_codes(0, true);
-      gather_codes(0, false);
+      rows_v = tile_rows(0);
+      gather_codes(rows_v, true);
+      gather_codes(rows_v, false);
+      rows_v = tile_rows(1);  // keys of tile 1 below, its values in iteration 0
+      rows_k = tile_rows(2);
     } else if (tid == 0) {
       issue_codes(0, true);
       issue_codes(0, false);
@@ -467,7 +479,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
       issue_scores(0);
       if (!PAGED && n_tiles > 1) issue_codes(1, true);
     }
-    if (PAGED && n_tiles > 1) gather_codes(1, true);
+    if (PAGED && n_tiles > 1) gather_codes(rows_v, true);
   }
 
   for (int tile = 0; tile < n_tiles && !dead; ++tile) {
@@ -506,8 +518,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
       }
     }
     if constexpr (PAGED) {
-      if (tile + 2 < n_tiles) gather_codes(tile + 2, true);
-      if (more) gather_codes(tile + 1, false);
+      if (tile + 2 < n_tiles) gather_codes(rows_k, true);
+      if (more) gather_codes(rows_v, false);
+      rows_v = rows_k;                // tile + 2: its values go in the next iteration
+      rows_k = tile_rows(tile + 3);   // looked up now, used in the next iteration
     }
     // ---- S(t), issued one iteration ago -----------------------------------------------------
     if (!mbar_wait(bar_s + (tile & 1), (tile >> 1) & 1)) dead = true;
