@@ -491,6 +491,39 @@ def extra_long_context(ctx):
                   "per GPU)" if h_loc == 1 else f"{cache.numel() / 1e6:.0f} MB of cache per GPU",
             "status": K.workspace_status(ws)}
         del cache
+    # ---- (a') the same batch with whole sequences per rank (8 / N each, all 8 KV heads): the
+    # other no-communication split the decode offers; the ranks' loads differ with the lengths
+    if world > 1 and 8 % world == 0:
+        lens = W.ragged_lengths()
+        mine = D.shard_sequences(8, rank, world)
+        my_lens = lens[mine]
+        w = W.decode_workload(seq_lens=my_lens.tolist(), num_q_heads=hq, num_kv_heads=hkv, cfg=4)
+        cache = torch.zeros(w.num_blocks, bs, hkv * (d + 8), dtype=torch.uint8, device=dev)
+        at = 0
+        for i, n in enumerate(my_lens.tolist()):
+            k, v = W.make_kv(n, hkv, d, cfg=400 + mine.start + i)
+            K.tq4_compress_append(k.to(dev), v.to(dev), cache, w.slot_mapping[at:at + n].to(dev),
+                                  rot, bk, bv)
+            at += n
+        q = w.q.to(dev)
+        bt, sl = w.block_table.to(dev), w.seq_lens.to(dev)
+        out = torch.empty_like(q)
+        ws = K.decode_workspace(dev, len(my_lens), hq, hkv, d, 8)
+        g = _graph_of(lambda: K.split_k_paged_decode(q, cache, bt, sl, ck, cv, rot, hkv, d, bs,
+                                                     out=out, num_splits=8, workspace=ws),
+                      torch.cuda.Stream())
+        mine_ms = _event_loop(g.replay, 100, 5)
+        ms = _max_over_ranks(ctx, mine_ms)
+        alg = int(my_lens.sum()) * 136 * hkv + 2 * q.numel() * 2
+        res["sequence_sharded"] = {
+            "ms_per_step": ms, "tokens_per_s": 8 / (ms * 1e-3), "sequences_per_gpu": len(my_lens),
+            "rank0_ms": mine_ms, "rank0_algorithmic_bytes": alg,
+            "rank0_frac_of_peak": alg / (mine_ms * 1e-3) / 1e9 / peak,
+            "what": "configs[4]'s batch with whole sequences per rank instead of KV heads (no "
+                    "collective either); step time = slowest rank, which holds the longest "
+                    "sequences",
+            "status": K.workspace_status(ws)}
+        del cache
     # ---- (b) one long sequence, token ranges per rank ---------------------------------------------
     L = 131072
     w1 = W.decode_workload(seq_lens=[L], num_q_heads=hq, num_kv_heads=hkv, cfg=41)
