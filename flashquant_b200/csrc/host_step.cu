@@ -29,6 +29,7 @@ namespace fq {
 // overlap the copies and the launch of the compress-on-append; created on first use.
 struct StepAux {
   cudaStream_t stream = nullptr;
+  cudaStream_t branch = nullptr;  // second branch while `stream` records a graph
   cudaEvent_t fork = nullptr, join = nullptr;
 };
 
@@ -44,6 +45,7 @@ static int step_aux(StepAux** out) {
   StepAux& a = aux[dev];
   if (!a.stream) {
     e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&a.branch, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming);
     if (e != cudaSuccess) {
@@ -148,6 +150,7 @@ struct StepGraphKey {
   const void *kv, *kq, *rot, *bk, *ck, *bv, *cv, *qjl;
   int nbk, nck, nbv, ncv, num_seqs, hq, hkv, d, bs; int64_t num_blocks; float scale; int splits;
   void* staging; void* workspace; size_t workspace_bytes; cudaStream_t stream; int device;
+  int overlap;  // the recorded sequence has the second half of the copy on a branch of its own
   uint64_t settings;  // process-wide switches and limits are baked into the recorded launches
 };
 struct StepGraph {
@@ -285,7 +288,7 @@ extern "C" int fq_decode_step_host_packed(
   const unsigned char* src = static_cast<const unsigned char*>(block_host);
   StepAux* aux = nullptr;
   cudaError_t ce = cudaSuccess;
-  if (!overlap_copies && g_step_graph.load(std::memory_order_relaxed)) {
+  if (g_step_graph.load(std::memory_order_relaxed)) {
     static thread_local std::vector<StepGraph> graphs;
     StepGraphKey key;
     std::memset(&key, 0, sizeof(key));  // padding too: the key is compared byte by byte
@@ -296,7 +299,7 @@ extern "C" int fq_decode_step_host_packed(
     key.ncv = n_centroids_v; key.num_seqs = num_seqs; key.hq = num_q_heads; key.hkv = num_kv_heads;
     key.d = head_dim; key.bs = block_size; key.num_blocks = num_blocks; key.scale = sm_scale;
     key.splits = num_splits; key.staging = staging; key.workspace = workspace;
-    key.workspace_bytes = workspace_bytes; key.stream = stream;
+    key.workspace_bytes = workspace_bytes; key.stream = stream; key.overlap = overlap_copies ? 1 : 0;
     cudaGetDevice(&key.device);
     key.settings = settings_epoch();
     cudaGraphExec_t exec = nullptr;
@@ -317,16 +320,28 @@ extern "C" int fq_decode_step_host_packed(
     if (cap) {
       fq_stream_t cap_ = cap;
       const uint64_t launches_at_capture = fq_launch_count();
-      ce = cudaMemcpyAsync(st, src, L.out, cudaMemcpyHostToDevice, cap);
+      if (overlap_copies) {
+        // what the compress-on-append reads first; the rest on a branch that joins before the
+        // decode, so that it travels under the compress-on-append
+        ce = cudaMemcpyAsync(st + L.k, src + L.k, L.sl - L.k, cudaMemcpyHostToDevice, cap);
+        if (ce == cudaSuccess) ce = cudaEventRecord(aux->fork, cap);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(aux->branch, aux->fork, 0);
+        if (ce == cudaSuccess)
+          ce = cudaMemcpyAsync(st + L.sl, src + L.sl, L.out - L.sl, cudaMemcpyHostToDevice,
+                               aux->branch);
+        if (ce == cudaSuccess) ce = cudaEventRecord(aux->join, aux->branch);
+      } else {
+        ce = cudaMemcpyAsync(st, src, L.out, cudaMemcpyHostToDevice, cap);
+      }
       int rc = ce == cudaSuccess
-                   ? step_kernels_and_result(L, st, nullptr, dtype, slot_is_int64,
+                   ? step_kernels_and_result(L, st, aux, dtype, slot_is_int64,
                                              block_table_stride, kv_cache, kq_cache, rotation,
                                              boundaries_k, n_boundaries_k, centroids_k,
                                              n_centroids_k, boundaries_v, n_boundaries_v,
                                              centroids_v, n_centroids_v, qjl, num_seqs,
                                              num_q_heads, num_kv_heads, head_dim, block_size,
                                              num_blocks, sm_scale, num_splits, out_host, workspace,
-                                             workspace_bytes, cap_, false, false)
+                                             workspace_bytes, cap_, overlap_copies != 0, false)
                    : FQ_ERR_CUDA;
       const uint64_t after_issue = fq_launch_count();
       cudaGraph_t graph = nullptr;

@@ -574,9 +574,10 @@ int fq_decode_step_host(const void* q_host, const void* key_host, const void* va
  * The caller writes each step's inputs at those offsets of its block, then calls
  * fq_decode_step_host_packed(block, ...); the staging area has the same size as before.
  */
-/* With overlap_copies = 0 the packed step is captured once per distinct argument set and
- * replayed as a CUDA graph (one submission for the copy in, the two launches and the copy
- * out); 0 switches that off for the whole process, the step is then issued call by call. */
+/* The packed step is captured once per distinct argument set and replayed as a CUDA graph
+ * (one submission for the copies in, the two launches and the copy out; with overlap_copies
+ * the second half of the block is a branch of the graph that joins before the decode);
+ * 0 switches that off for the whole process, the step is then issued call by call. */
 void fq_decode_step_set_graph(int enabled);
 int fq_decode_step_offsets(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                            int64_t block_table_stride, int slot_is_int64, uint64_t offsets[8]);

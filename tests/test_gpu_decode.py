@@ -370,7 +370,7 @@ def test_host_step_equals_append_then_decode(consts, with_qjl, pinned):
                         ("seq_lens", lens), ("block_table", bt), ("q", w.q)):
             views[name].copy_(t)
         # (False, False: the second call replays the graph that the first one captured)
-        for overlap in (False, False, True):
+        for overlap in (False, False, True, True):
             views["out"].zero_()
             got = step.packed(overlap_copies=overlap)
             assert torch.equal(got.view(torch.int16), ref.cpu().view(torch.int16)), overlap
