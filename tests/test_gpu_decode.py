@@ -199,6 +199,40 @@ def test_sequences_with_hundreds_of_partial_rows(consts, hq, hkv, seq_lens):
         assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize("seed", [101, 102, 103, 104, 105, 106])
+def test_random_ragged_batches_vs_oracle(consts, seed):
+    """Seeded random batches - empty, tiny and long sequences mixed, random split counts - through
+    both streaming kernels (the specialised one and, with it switched off, the generic one):
+    every run of pages that crosses sequences, every short segment is a case of its own."""
+    g = torch.Generator().manual_seed(seed)
+    n = int(torch.randint(3, 13, (1,), generator=g))
+    kind = torch.randint(0, 4, (n,), generator=g)
+    lens = []
+    for k in kind.tolist():
+        if k == 0:
+            lens.append(0 if int(torch.randint(0, 2, (1,), generator=g)) else 1)
+        elif k == 1:
+            lens.append(int(torch.randint(1, 41, (1,), generator=g)))
+        elif k == 2:
+            lens.append(int(torch.randint(100, 700, (1,), generator=g)))
+        else:
+            lens.append(int(torch.randint(700, 3001, (1,), generator=g)))
+    splits = int(torch.randint(1, 9, (1,), generator=g))
+    w = W.decode_workload(seq_lens=lens, cfg=seed)
+    cache = fill_cache_cpu(w, consts)
+    ref = run_oracle(w, cache, consts)
+    lib = K.N.load()
+    try:
+        for fast in (1, 0):
+            lib.fq_paged_decode_set_fast_path(fast)
+            out = run_gpu(w, cache, consts, num_splits=splits)
+            close(out, ref, consts, rtol=2.0 ** -9)
+            rows = gpu_rows(w, cache, consts, num_splits=splits)
+            close(out, ref, consts, got_rot32=rows, rtol=2.0 ** -9)
+    finally:
+        lib.fq_paged_decode_set_fast_path(1)
+
+
 def test_token_ranges_on_two_groups_merge_like_one(consts):
     """What a cross-GPU split does: group 0 attends over the first pages of every sequence,
     group 1 over the rest; merging the two partial rows equals attending over everything."""
