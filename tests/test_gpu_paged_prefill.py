@@ -65,6 +65,21 @@ def test_chunks_vs_oracle(consts, seq_lens, chunks):
     run_and_check(consts, w, cache, q, cu, chunks)
 
 
+@pytest.mark.parametrize("seed", [201, 202, 203])
+def test_random_ragged_chunks_vs_oracle(consts, seed):
+    g = torch.Generator().manual_seed(seed)
+    n = int(torch.randint(2, 7, (1,), generator=g))
+    seq_lens = [int(torch.randint(1, 3001, (1,), generator=g)) for _ in range(n)]
+    chunks = []
+    for length in seq_lens:
+        c = int(torch.randint(0, min(length, 600) + 1, (1,), generator=g))
+        chunks.append(c)
+    if sum(chunks) == 0:
+        chunks[0] = 1
+    w, cache, q, cu = build(consts, seq_lens, chunks, cfg=seed)
+    run_and_check(consts, w, cache, q, cu, chunks)
+
+
 def test_sequence_without_chunk_and_gqa_layouts(consts):
     """A sequence that contributes no query tokens, 64 q heads over 8 KV heads, fp16."""
     seq_lens, chunks = [200, 96, 1030], [40, 0, 129]
