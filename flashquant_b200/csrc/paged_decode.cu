@@ -780,16 +780,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) paged_decode_kernel(DecodeA
       // than 16 described pages are left to issue; the ring slots it overwrites held pages
       // more than 16 behind the issue front, which every warp of the team has left (a warp is
       // never more than `stages` <= 16 pages behind it).
-      if (first_round) {
-        // the very first descriptors of all teams at once (32 / teams pages each), so that
-        // every team's first block-table read is in flight at the same time
-        first_round = false;
+      if (first_round || teams > 4) {
+        // All teams at once, 32 / teams pages each: every team's block-table reads are in flight
+        // at the same time.  The very first descriptors always come this way; with many small
+        // teams (few KV heads) every later chunk does too - one team after the other, each
+        // waiting for its own reads, left the last of sixteen teams without pages for a dozen
+        // microseconds.
         const int per = 32 / teams, T = lane / per, i = lane - T * per;
+        const int base = first_round ? 0 : __shfl_sync(0xffffffffu, produced, T);
+        const int iss = first_round ? 0 : __shfl_sync(0xffffffffu, issue_idx, T);
         const int n_run = __shfl_sync(0xffffffffu, my_run, T);
         const int64_t f0 = __shfl_sync(0xffffffffu, my_f0, T);
-        if (i < n_run) describe(T, i, n_run, f0);
+        const bool need = base < n_run && base - iss < 16;
+        // two pages per lane and round once the first descriptors are out (they go first so
+        // that the first copies start as early as possible)
+        const int each = first_round ? 1 : 2;
+        for (int k = 0; k < each; ++k)
+          if (need && base + k * per + i < n_run) describe(T, base + k * per + i, n_run, f0);
         __syncwarp();
-        if (has_team) produced = per;
+        const bool mine = __shfl_sync(0xffffffffu, int(need), (lane * per) & 31) != 0;
+        if (has_team && mine) produced += each * per;
+        first_round = false;
       } else {
 #pragma unroll 1
         for (int T = 0; T < teams; ++T) {
@@ -1418,15 +1429,20 @@ static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 // `splits` <= 0 sizes for the largest split count
 // Chunks that the single-launch merge cuts the rows of a (sequence, head group) into: a
 // sequence has about its share of the teams plus a row per split boundary.
-static int merge_chunks_for(int num_seqs, int hq, int splits, int workers) {
+// Never more chunk jobs than CTAs (`ctas`; a job is a CTA's work): a second round of jobs would
+// cost more than the shorter chunks save.
+static int merge_chunks_for(int num_seqs, int hq, int splits, int workers, int ctas) {
   const int hgroups = (hq + kMergeHeads - 1) / kMergeHeads;
   if (num_seqs <= 0 || int64_t(num_seqs) * hgroups > kMaxChunkJobs) return 1;
   const int64_t rows = (int64_t(workers) + int64_t(num_seqs) * splits) / num_seqs + 1;
-  const int64_t c = (rows + kRowsPerMergeChunk - 1) / kRowsPerMergeChunk;
+  int64_t c = (rows + kRowsPerMergeChunk - 1) / kRowsPerMergeChunk;
+  const int64_t fit = int64_t(ctas) / (int64_t(num_seqs) * hgroups);
+  c = c > fit ? fit : c;
   return c < 1 ? 1 : (c > kMaxMergeChunks ? kMaxMergeChunks : int(c));
 }
 
-static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits, int workers) {
+static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits, int workers,
+                                        int grid = 192) {
   if (splits <= 0) splits = kMaxSplits;
   const int ctas = workers;
   WorkspaceLayout w;
@@ -1437,7 +1453,7 @@ static WorkspaceLayout workspace_layout(int num_seqs, int hq, int d, int splits,
   w.slots_off = up256(w.q_rot_off + 2 * size_t(num_seqs) * hq * d * sizeof(__half));
   w.chunk_off = up256(w.slots_off +
                       (size_t(num_seqs) * splits + ctas) * hq * (d + kPartPad) * sizeof(float));
-  w.merge_chunks = merge_chunks_for(num_seqs, hq, splits, workers);
+  w.merge_chunks = merge_chunks_for(num_seqs, hq, splits, workers, grid);
   const size_t hgroups = size_t(hq + kMergeHeads - 1) / kMergeHeads;
   w.total = w.merge_chunks > 1
                 ? up256(w.chunk_off + size_t(num_seqs) * hgroups * w.merge_chunks * kMergeHeads *
@@ -1763,7 +1779,8 @@ static int decode_front(const void* q, fq_dtype dtype, const uint8_t* kv_cache,
   // `hq` counts the query rows of a sequence: n_q tokens x heads (n_q > 1: fast path only)
   FQ_REQUIRE(workspace && aligned(workspace, 256), FQ_ERR_WORKSPACE,
              "paged decode: workspace is null or not 256-byte aligned");
-  const WorkspaceLayout w = workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv));
+  const WorkspaceLayout w =
+      workspace_layout(num_seqs, hq, head_dim, num_splits, ctas * (kCW / hkv), ctas);
   FQ_REQUIRE(workspace_bytes >= w.total, FQ_ERR_WORKSPACE,
              "paged decode: workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
   const bool fast = fast_path_fits(hq, n_q, hkv, head_dim, block_size, kq_cache != nullptr);
