@@ -171,6 +171,7 @@ struct PrefillArgs {
   const int32_t* cu_q;
   int block_size;
   int64_t num_blocks;
+  int total_q;    // query tokens in q_rot / o_rot (chunks must lie inside)
   int round_out;  // FQ_BF16 / FQ_F16: rows are rounded to that type before they are stored
   // beta_k, beta_v of the scaled fp16 centroid tables (centroid_scale_kernel, run just before)
   const float* scales;
@@ -267,7 +268,11 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attention_kernel(Prefil
       clamped = true;
     }
     ctx = kv_len - q_len;
-    if (m0 >= q_len) return;  // the grid is sized for the longest chunk
+    // a chunk outside the query tokens is not touched; one longer than the grid covers is cut
+    const bool outside = q_first < 0 || q_len < 0 || int64_t(q_first) + q_len > p.total_q;
+    if ((outside || q_len > int(gridDim.x) * kPfM) && m_tile == 0 && tid == 0 && p.status)
+      atomicOr(p.status, FQ_DEV_BAD_LENGTH);
+    if (outside || m0 >= q_len) return;  // the grid is sized for the longest chunk
   }
   const int rows = q_len - m0 < kPfM ? q_len - m0 : kPfM;
 
@@ -977,6 +982,7 @@ extern "C" int fq_paged_tq4_prefill(const void* q, fq_dtype dtype, const uint8_t
   a.block_size = block_size;
   a.num_blocks = num_blocks;
   a.round_out = int(dtype);
+  a.total_q = total_q_tokens;
   rc = centroid_scales(a, ws, s);
   if (rc != FQ_OK) return rc;
   rc = launch_prefill_t<128, true>(a, s);

@@ -39,6 +39,9 @@ typedef enum fq_status {
 /* Bits of the device-side status word kept at the start of a decode workspace. */
 #define FQ_DEV_BAD_BLOCK_INDEX 1u /* a block_table entry was outside [0, num_blocks) */
 #define FQ_DEV_WAIT_TIMEOUT 2u    /* a bounded wait on a shared-memory barrier ran out */
+#define FQ_DEV_BAD_LENGTH 4u      /* fq_paged_tq4_prefill: a chunk of cu_seqlens_q lies outside
+                                     the query tokens or is longer than max_q_len; its rows (or
+                                     their tail) were not computed */
 
 int fq_version(void);
 const char* fq_last_error_string(void);
@@ -510,7 +513,8 @@ int fq_fused_tq_attention_kv(const void* q, fq_dtype dtype, const uint8_t* k_pac
  *   block_table     (num_seqs, block_table_stride) int32 page ids; an id outside
  *                   [0, num_blocks) or a length beyond the row sets FQ_DEV_BAD_BLOCK_INDEX in
  *                   word 0 of the workspace and is not followed
- *   max_q_len       longest chunk (sizes the grid)
+ *   max_q_len       longest chunk (sizes the grid); a longer chunk, or one that does not lie
+ *                   inside [0, total_q_tokens), sets FQ_DEV_BAD_LENGTH and is cut / skipped
  *   rounding        q Pi^T and the attention rows are rounded to the activation type before
  *                   the products with K and Pi, as the reference's two matmul + cast steps do
  *   workspace       256-byte aligned, fq_paged_tq4_prefill_workspace_bytes(...) bytes; word 0

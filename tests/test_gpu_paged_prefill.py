@@ -111,3 +111,33 @@ def test_bad_page_index_is_reported_not_followed(consts):
     K.paged_tq4_prefill(q.to(DEV), cache.to(DEV), bt.to(DEV), w.seq_lens.to(DEV), cu.to(DEV), 100,
                         ck, cv, rot, 8, 128, 16, workspace=ws)
     assert K.workspace_status(ws) & 1  # FQ_DEV_BAD_BLOCK_INDEX
+
+
+def test_chunk_bounds_are_reported_not_followed(consts):
+    """cu_seqlens_q that points past the query tokens, and a chunk longer than max_q_len: a
+    status bit, no access outside the tensors, the other sequences unaffected."""
+    seq_lens, chunks = [300, 200], [150, 100]
+    w, cache, q, cu = build(consts, seq_lens, chunks, cfg=37)
+    rot, ck, cv = consts["rotation_128_0"], consts["centroids_128_3"], consts["centroids_128_4"]
+    ref32, ref = O.paged_prefill_varlen_stages(q, cache, w.block_table, w.seq_lens, cu, ck, cv, rot,
+                                               8, 128, 16)
+    need = K.N.load().fq_paged_tq4_prefill_workspace_bytes(q.shape[0], 32, 128)
+    # (1) the second chunk claims 50 tokens more than there are
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    bad = cu.clone()
+    bad[2] += 50
+    out = torch.zeros_like(q, device=DEV)
+    K.paged_tq4_prefill(q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+                        bad.to(DEV), 150, ck, cv, rot, 8, 128, 16, out=out, workspace=ws)
+    assert K.workspace_status(ws) & 4  # FQ_DEV_BAD_LENGTH
+    attention_close(out[:150], ref[:150], ref32[:150], rot, rtol=PAGED_PREFILL_RTOL)
+    assert (out[150:] == 0).all()
+    # (2) max_q_len smaller than the longest chunk: its tail is not computed
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    out = torch.zeros_like(q, device=DEV)
+    K.paged_tq4_prefill(q.to(DEV), cache.to(DEV), w.block_table.to(DEV), w.seq_lens.to(DEV),
+                        cu.to(DEV), 128, ck, cv, rot, 8, 128, 16, out=out, workspace=ws)
+    assert K.workspace_status(ws) & 4
+    attention_close(out[:128], ref[:128], ref32[:128], rot, rtol=PAGED_PREFILL_RTOL)
+    attention_close(out[150:], ref[150:], ref32[150:], rot, rtol=PAGED_PREFILL_RTOL)
+    assert (out[128:150] == 0).all()
