@@ -18,15 +18,15 @@
 // chain, and every CTA would fetch them over the bus.)
 #include <atomic>
 #include <cstring>
-#include <mutex>
 #include <vector>
 
 #include "fq_common.cuh"
 
 namespace fq {
 
-// A second stream per device, so that the copies the decode needs (query, block table, lengths)
-// overlap the copies and the launch of the compress-on-append; created on first use.
+// Side streams per host thread and device, so that the copies the decode needs (query, block
+// table, lengths) overlap the copies and the launch of the compress-on-append, and for
+// recording the packed step as a graph; created on first use.
 struct StepAux {
   cudaStream_t stream = nullptr;
   cudaStream_t branch = nullptr;  // second branch while `stream` records a graph
@@ -34,14 +34,14 @@ struct StepAux {
 };
 
 static int step_aux(StepAux** out) {
+  // per host thread: two threads that step on one GPU must not record into each other's
+  // events, and a thread that records a graph must have the recording streams to itself
   constexpr int kMaxDevices = 64;
-  static StepAux aux[kMaxDevices];
-  static std::mutex mu;
+  static thread_local StepAux aux[kMaxDevices];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(FQ_ERR_CUDA, "decode step: cudaGetDevice: %s", cudaGetErrorString(e));
-  std::lock_guard<std::mutex> lock(mu);
   StepAux& a = aux[dev];
   if (!a.stream) {
     e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
